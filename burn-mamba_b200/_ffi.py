@@ -1,0 +1,114 @@
+"""ctypes binding of libbm_b200.so (the C ABI declared in include/bm_b200.h).
+
+The library is the product; this module only loads it and describes its structs.  There is no
+fallback: if the shared library is missing, importing this module raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libbm_b200.so")
+
+BM_OK = 0
+BM_ERR_NULL_POINTER, BM_ERR_BAD_SHAPE, BM_ERR_BAD_ALIGNMENT, BM_ERR_UNSUPPORTED = -1, -2, -3, -4
+BM_ERR_WORKSPACE_TOO_SMALL, BM_ERR_CUDA, BM_ERR_TIMEOUT = -5, -6, -7
+BM_DTYPE_F32, BM_DTYPE_BF16 = 0, 1
+BM_PATH_AUTO, BM_PATH_EXACT, BM_PATH_TENSOR = 0, 1, 2
+
+_i32, _f32, _vp = C.c_int32, C.c_float, C.c_void_p
+
+
+class Ssd2FwdArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "headdim", "state_rank", "ngroups", "chunk_len",
+                                    "dtype", "path", "reserved")] + [
+        ("x", _vp), ("dt", _vp), ("a", _vp), ("b", _vp), ("c", _vp), ("d", _vp), ("h0", _vp), ("dt_bias", _vp),
+        ("dt_min", _f32), ("dt_max", _f32), ("z", _vp), ("y", _vp), ("h_final", _vp), ("chunk_states", _vp)]
+
+
+class Step2Args(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "nheads", "headdim", "state_rank", "ngroups", "dtype")] + [
+        ("state", _vp), ("x", _vp), ("dt", _vp), ("a", _vp), ("b", _vp), ("c", _vp), ("d", _vp), ("dt_bias", _vp),
+        ("dt_min", _f32), ("dt_max", _f32), ("z", _vp), ("y", _vp)]
+
+
+class ConvStepArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "channels", "kernel", "dtype")] + [
+        ("window", _vp), ("xin", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp)]
+
+
+class Selscan1Args(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "d_inner", "state_rank", "dtype", "delta_softplus")] + [
+        ("u", _vp), ("delta", _vp), ("a", _vp), ("b", _vp), ("c", _vp), ("d", _vp), ("delta_bias", _vp), ("z", _vp),
+        ("h0", _vp), ("y", _vp), ("h_final", _vp)]
+
+
+class Step1Args(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "d_inner", "state_rank", "dtype", "delta_softplus")] + [
+        ("state", _vp), ("u", _vp), ("delta", _vp), ("a", _vp), ("b", _vp), ("c", _vp), ("d", _vp),
+        ("delta_bias", _vp), ("z", _vp), ("y", _vp)]
+
+
+class Ssd3FwdArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "headdim", "state_rank", "mimo_rank", "chunk_len",
+                                    "dtype", "path", "rope_dim")] + [
+        ("v", _vp), ("da", _vp), ("b", _vp), ("c", _vp), ("gamma", _vp), ("scale", _vp), ("h0", _vp), ("angles", _vp),
+        ("y", _vp), ("h_final", _vp)]
+
+
+class AngleCumsumArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "nangles")] + [
+        ("range", _f32), ("rot", _vp), ("dt", _vp), ("prev", _vp), ("theta", _vp), ("last", _vp)]
+
+
+class Step3Args(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "nheads", "headdim", "state_rank", "mimo_rank", "rope_dim")] + [
+        ("range", _f32), ("state", _vp), ("k_state", _vp), ("v_state", _vp), ("angle", _vp), ("x", _vp), ("b", _vp),
+        ("c", _vp), ("rot", _vp), ("dt", _vp), ("alpha", _vp), ("beta", _vp), ("gamma", _vp), ("mimo_x", _vp),
+        ("y", _vp)]
+
+
+# symbol -> (restype, argtypes); every function include/bm_b200.h declares
+SYMBOLS = {
+    "bm_version": (_i32, []),
+    "bm_build_info": (C.c_char_p, []),
+    "bm_last_error_string": (C.c_char_p, []),
+    "bm_ssd2_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd2FwdArgs)]),
+    "bm_ssd2_fwd": (_i32, [C.POINTER(Ssd2FwdArgs), _vp, C.c_size_t, _vp]),
+    "bm_step2": (_i32, [C.POINTER(Step2Args), _vp]),
+    "bm_conv_step": (_i32, [C.POINTER(ConvStepArgs), _vp]),
+    "bm_selscan1_fwd": (_i32, [C.POINTER(Selscan1Args), _vp]),
+    "bm_step1": (_i32, [C.POINTER(Step1Args), _vp]),
+    "bm_ssd3_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd3FwdArgs)]),
+    "bm_ssd3_single_fwd": (_i32, [C.POINTER(Ssd3FwdArgs), _vp, C.c_size_t, _vp]),
+    "bm_ssd3_double_fwd": (_i32, [C.POINTER(Ssd3FwdArgs), _vp, C.c_size_t, _vp]),
+    "bm_angle_cumsum": (_i32, [C.POINTER(AngleCumsumArgs), _vp]),
+    "bm_step3": (_i32, [C.POINTER(Step3Args), _vp]),
+}
+
+
+def load(path=LIB_PATH):
+    if not os.path.exists(path):
+        raise ImportError(f"{path} is missing: build it with `python burn-mamba_b200/build.py` "
+                          "(there is no fallback implementation)")
+    lib = C.CDLL(path)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = load()
+
+
+class BmError(RuntimeError):
+    """A non-zero bm_status; mirrors the reference's panics (assert!/unwrap) at the same call sites."""
+
+    def __init__(self, code, where):
+        self.code = code
+        msg = lib.bm_last_error_string().decode()
+        super().__init__(f"{where} failed with status {code}: {msg}")
+
+
+def check(code, where):
+    if code != BM_OK:
+        raise BmError(code, where)

@@ -1,0 +1,205 @@
+// Mamba-1 selective scan over a sequence (replaces the per-token op loop of
+// src/mamba1/mamba1.rs:422-523).  HBM-bound: u, delta, z are read once and y written once.
+//
+// Work split: one CTA per (batch row, tile of CH channels); a thread owns RPT consecutive states of
+// one channel and keeps them in registers for the whole sequence.  Tokens are staged through shared
+// memory in chunks of TCH with a two-stage cp.async pipeline, so global traffic is coalesced along
+// the channel axis while the recurrence itself runs out of shared memory and registers.
+#include "common.cuh"
+
+using namespace bm;
+
+namespace {
+
+constexpr int CH = 32;    // channels per CTA
+constexpr int TCH = 64;   // tokens per staged chunk
+constexpr int RPT = 4;    // states per thread
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <typename T>
+struct Stage {
+    T delta[TCH][CH];
+    T u[TCH][CH];
+    T z[TCH][CH];
+    T bmat[TCH * 64];  // [TCH][R], R <= 64
+    T cmat[TCH * 64];
+};
+
+// Fast kernel: d_inner % CH == 0, state_rank % RPT == 0, state_rank <= 64, 16-byte-aligned rows.
+template <typename T>
+__global__ void selscan1_kernel(bm_selscan1_args a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    Stage<T>* stages = reinterpret_cast<Stage<T>*>(smem_raw);
+    T* ytile = reinterpret_cast<T*>(smem_raw + 2 * sizeof(Stage<T>));  // [TCH][CH]
+    const int R = a.state_rank, I = a.d_inner, S = a.seqlen;
+    const int tpc = R / RPT;  // threads per channel
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int cl = tid / tpc, q = tid % tpc;  // channel in tile, state quarter
+    const int ntile = I / CH;
+    const int b = blockIdx.x / ntile, c0 = (blockIdx.x % ntile) * CH;
+    const int ch = c0 + cl;
+    constexpr int EPV = 16 / sizeof(T);  // elements per 16-byte vector
+
+    float h[RPT], av[RPT];
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) {
+        av[k] = a.a[(int64_t)ch * R + q * RPT + k];
+        h[k] = a.h0 ? a.h0[((int64_t)b * I + ch) * R + q * RPT + k] : 0.f;
+    }
+    const float dskip = a.d ? a.d[ch] : 0.f;
+    const float dbias = (a.delta_softplus && a.delta_bias) ? a.delta_bias[ch] : 0.f;
+    const T* ug = static_cast<const T*>(a.u) + (int64_t)b * S * I + c0;
+    const T* dg = static_cast<const T*>(a.delta) + (int64_t)b * S * I + c0;
+    const T* zg = a.z ? static_cast<const T*>(a.z) + (int64_t)b * S * I + c0 : nullptr;
+    const T* bg = static_cast<const T*>(a.b) + (int64_t)b * S * R;
+    const T* cg = static_cast<const T*>(a.c) + (int64_t)b * S * R;
+    T* yg = static_cast<T*>(a.y) + (int64_t)b * S * I + c0;
+
+    auto issue = [&](int chunk, int stg) {
+        const int t0 = chunk * TCH;
+        const int nt = min(TCH, S - t0);
+        Stage<T>& st = stages[stg];
+        constexpr int VPR = CH / EPV;  // vectors per token row
+        for (int e = tid; e < nt * VPR; e += nthreads) {
+            int t = e / VPR, vv = (e % VPR) * EPV;
+            cp_async16(&st.delta[t][vv], dg + (int64_t)(t0 + t) * I + vv);
+            cp_async16(&st.u[t][vv], ug + (int64_t)(t0 + t) * I + vv);
+            if (zg) cp_async16(&st.z[t][vv], zg + (int64_t)(t0 + t) * I + vv);
+        }
+        const int bcv = nt * R / EPV;  // B / C rows of a chunk are contiguous in memory
+        for (int e = tid; e < bcv; e += nthreads) {
+            cp_async16(&st.bmat[e * EPV], bg + (int64_t)t0 * R + e * EPV);
+            cp_async16(&st.cmat[e * EPV], cg + (int64_t)t0 * R + e * EPV);
+        }
+    };
+
+    const int nchunks = (S + TCH - 1) / TCH;
+    issue(0, 0);
+    cp_async_commit();
+    for (int chunk = 0; chunk < nchunks; ++chunk) {
+        const int stg = chunk & 1;
+        if (chunk + 1 < nchunks) issue(chunk + 1, stg ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        Stage<T>& st = stages[stg];
+        const int t0 = chunk * TCH, nt = min(TCH, S - t0);
+        for (int t = 0; t < nt; ++t) {
+            float delta = to_f32(st.delta[t][cl]);
+            if (a.delta_softplus) delta = softplus_stock(delta + dbias);
+            const float u = to_f32(st.u[t][cl]);
+            const float du = delta * u;
+            float part = 0.f;
+#pragma unroll
+            for (int k = 0; k < RPT; ++k) {
+                const float bk = to_f32(st.bmat[t * R + q * RPT + k]);
+                const float ck = to_f32(st.cmat[t * R + q * RPT + k]);
+                h[k] = fmaf(h[k], __expf(delta * av[k]), du * bk);
+                part = fmaf(h[k], ck, part);
+            }
+            for (int o = tpc >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (q == 0) {
+                float y = fmaf(dskip, u, part);
+                if (zg) y *= silu_f32(to_f32(st.z[t][cl]));
+                ytile[t * CH + cl] = from_f32<T>(y);
+            }
+        }
+        __syncthreads();
+        constexpr int VPR = CH / EPV;
+        for (int e = tid; e < nt * VPR; e += nthreads) {
+            int t = e / VPR, vv = (e % VPR) * EPV;
+            *reinterpret_cast<uint4*>(yg + (int64_t)(t0 + t) * I + vv) = *reinterpret_cast<const uint4*>(&ytile[t * CH + vv]);
+        }
+        // the next iteration's barrier (after its cp.async wait) orders these reads of ytile and of
+        // stage `stg` before they are overwritten: ytile is rewritten only after that barrier, and
+        // stage `stg` is refilled by issue() of iteration chunk + 1, i.e. after this point for every
+        // thread, but other threads may still be reading it -> explicit barrier.
+        __syncthreads();
+    }
+#pragma unroll
+    for (int k = 0; k < RPT; ++k) a.h_final[((int64_t)b * I + ch) * R + q * RPT + k] = h[k];
+}
+
+// Generic kernel: any d_inner / state_rank; one thread per (b, i) channel, states in local memory
+// when state_rank is large.  Correct for every shape; used when the fast kernel's tiling does not fit.
+template <typename T>
+__global__ void selscan1_generic_kernel(bm_selscan1_args a) {
+    constexpr int RMAX = 256;
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int I = a.d_inner, R = a.state_rank, S = a.seqlen;
+    if (idx >= (int64_t)a.batch * I) return;
+    const int i = idx % I, b = idx / I;
+    float h[RMAX];
+    for (int r = 0; r < R; ++r) h[r] = a.h0 ? a.h0[idx * R + r] : 0.f;
+    const float* arow = a.a + (int64_t)i * R;
+    const float dskip = a.d ? a.d[i] : 0.f;
+    const float dbias = (a.delta_softplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    for (int t = 0; t < S; ++t) {
+        int64_t gi = ((int64_t)b * S + t) * I + i;
+        float delta = to_f32(static_cast<const T*>(a.delta)[gi]);
+        if (a.delta_softplus) delta = softplus_stock(delta + dbias);
+        const float u = to_f32(static_cast<const T*>(a.u)[gi]);
+        const T* bv = static_cast<const T*>(a.b) + ((int64_t)b * S + t) * R;
+        const T* cv = static_cast<const T*>(a.c) + ((int64_t)b * S + t) * R;
+        float part = 0.f;
+        for (int r = 0; r < R; ++r) {
+            h[r] = fmaf(h[r], expf(delta * arow[r]), delta * u * to_f32(bv[r]));
+            part = fmaf(h[r], to_f32(cv[r]), part);
+        }
+        float y = fmaf(dskip, u, part);
+        if (a.z) y *= silu_f32(to_f32(static_cast<const T*>(a.z)[gi]));
+        static_cast<T*>(a.y)[gi] = from_f32<T>(y);
+    }
+    for (int r = 0; r < R; ++r) a.h_final[idx * R + r] = h[r];
+}
+
+template <typename T>
+int32_t launch(const bm_selscan1_args& a, cudaStream_t st) {
+    const int R = a.state_rank, I = a.d_inner;
+    const int tpc = R / RPT;
+    const bool pow2 = tpc > 0 && (tpc & (tpc - 1)) == 0;
+    constexpr int EPV = 16 / sizeof(T);
+    const bool fast = I % CH == 0 && R % RPT == 0 && R <= 64 && pow2 && tpc <= 32 && (R % EPV == 0);
+    if (fast) {
+        size_t smem = 2 * sizeof(Stage<T>) + sizeof(T) * TCH * CH;
+        cudaError_t e = cudaFuncSetAttribute(selscan1_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(selscan1)");
+        unsigned grid = (unsigned)((int64_t)a.batch * (I / CH));
+        selscan1_kernel<T><<<grid, CH * tpc, smem, st>>>(a);
+        return check_launch("selscan1");
+    }
+    if (R > 256) return fail(BM_ERR_UNSUPPORTED, "state_rank %d above 256", R);
+    int64_t total = (int64_t)a.batch * I;
+    selscan1_generic_kernel<T><<<(unsigned)cdiv(total, 64), 64, 0, st>>>(a);
+    return check_launch("selscan1_generic");
+}
+
+}  // namespace
+
+extern "C" int32_t bm_selscan1_fwd(const bm_selscan1_args* a, void* stream) {
+    clear_error();
+    if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
+    BM_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->d_inner > 0 && a->state_rank > 0, BM_ERR_BAD_SHAPE,
+               "batch, seqlen, d_inner, state_rank must be positive");
+    BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
+    BM_REQUIRE_PTR(a->u);
+    BM_REQUIRE_PTR(a->delta);
+    BM_REQUIRE_PTR(a->a);
+    BM_REQUIRE_PTR(a->b);
+    BM_REQUIRE_PTR(a->c);
+    BM_REQUIRE_PTR(a->y);
+    BM_REQUIRE_PTR(a->h_final);
+    BM_OPTIONAL_PTR(a->d);
+    BM_OPTIONAL_PTR(a->delta_bias);
+    BM_OPTIONAL_PTR(a->z);
+    BM_OPTIONAL_PTR(a->h0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return a->dtype == BM_DTYPE_F32 ? launch<float>(*a, st) : launch<__nv_bfloat16>(*a, st);
+}

@@ -1,0 +1,16 @@
+// Tensor-core (tcgen05 / TMEM / TMA) path of the Mamba-2 SSD forward.
+#pragma once
+#include "common.cuh"
+
+namespace bm {
+namespace tc {
+
+// True when the tensor-core kernel covers this dtype/shape (bf16, headdim 64, state_rank 128, ...).
+bool ssd2_supported(const bm_ssd2_fwd_args* a);
+// Human-readable reason for ssd2_supported() == false.
+const char* ssd2_why_not(const bm_ssd2_fwd_args* a);
+size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args* a);
+int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
+}  // namespace tc
+}  // namespace bm

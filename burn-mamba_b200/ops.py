@@ -1,0 +1,213 @@
+"""Tensor-level calls into libbm_b200 (torch supplies device memory and the CUDA stream only).
+
+Every function validates dtypes/contiguity on the host, fills the C args struct with raw device
+pointers and launches on torch's current stream.  Outputs are freshly allocated, like the tensors a
+Burn backend returns from the reference's slot (src/mamba2/ssd/serial_recalculated/serial_recalculated.rs:86-98).
+"""
+import ctypes as C
+
+import torch
+
+from . import _ffi
+from ._ffi import lib, check
+
+_DT = {torch.float32: _ffi.BM_DTYPE_F32, torch.bfloat16: _ffi.BM_DTYPE_BF16}
+PATHS = {"auto": _ffi.BM_PATH_AUTO, "exact": _ffi.BM_PATH_EXACT, "tensor": _ffi.BM_PATH_TENSOR}
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _chk(t, name, dtype=None, shape=None, optional=False):
+    if t is None:
+        if optional:
+            return None
+        raise ValueError(f"{name} is required")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must have shape {tuple(shape)}, got {tuple(t.shape)}")
+    return t
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+_ws_cache = {}
+
+
+def _workspace(nbytes, device):
+    """Grow-only per-device scratch buffer (the C ABI never allocates; the caller -- this wrapper -- does)."""
+    key = (device.index, torch.cuda.current_stream().cuda_stream)
+    buf = _ws_cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _ws_cache[key] = buf
+    return buf
+
+
+def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bias=None, dt_limit=(0.0, 65504.0),
+             z=None, return_chunk_states=False):
+    """Mamba-2 chunked SSD forward.  x [b,s,h,p], dt [b,s,h] f32, a [h] f32, b/c [b,s,g,r], d [h] f32,
+    h0 [b,h,p,r] f32 -> (y [b,s,h,p], h_final [b,h,p,r] f32[, chunk_states [b,n,h,p,r]])."""
+    bsz, s, h, p = x.shape
+    g, r = b.shape[2], b.shape[3]
+    act = x.dtype
+    if act not in _DT:
+        raise ValueError(f"unsupported activation dtype {act}")
+    _chk(x, "x"); _chk(dt, "dt", torch.float32, (bsz, s, h)); _chk(a, "a", torch.float32, (h,))
+    _chk(b, "b", act, (bsz, s, g, r)); _chk(c, "c", act, (bsz, s, g, r))
+    _chk(d, "d", torch.float32, (h,), optional=True); _chk(h0, "h0", torch.float32, (bsz, h, p, r), optional=True)
+    _chk(dt_bias, "dt_bias", torch.float32, (h,), optional=True); _chk(z, "z", act, x.shape, optional=True)
+    y = torch.empty_like(x)
+    h_final = torch.empty((bsz, h, p, r), dtype=torch.float32, device=x.device)
+    nchunks = -(-s // chunk_len)
+    states = torch.empty((bsz, nchunks, h, p, r), dtype=torch.float32, device=x.device) if return_chunk_states else None
+    args = _ffi.Ssd2FwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, chunk_len=chunk_len,
+                            dtype=_DT[act], path=PATHS[path], reserved=0, x=_ptr(x), dt=_ptr(dt), a=_ptr(a),
+                            b=_ptr(b), c=_ptr(c), d=_ptr(d), h0=_ptr(h0), dt_bias=_ptr(dt_bias),
+                            dt_min=dt_limit[0], dt_max=dt_limit[1], z=_ptr(z), y=_ptr(y), h_final=_ptr(h_final),
+                            chunk_states=_ptr(states))
+    nbytes = lib.bm_ssd2_fwd_workspace_bytes(C.byref(args))
+    ws = _workspace(nbytes, x.device)
+    check(lib.bm_ssd2_fwd(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_ssd2_fwd")
+    return (y, h_final, states) if return_chunk_states else (y, h_final)
+
+
+def step2(state, x, dt, a, b, c, d=None, dt_bias=None, dt_limit=(0.0, 65504.0), z=None):
+    """Mamba-2 recurrent step; `state` [b,h,p,r] f32 is updated in place.  Returns y [b,h,p]."""
+    bsz, h, p, r = state.shape
+    g = b.shape[1]
+    act = x.dtype
+    _chk(state, "state", torch.float32); _chk(x, "x", act, (bsz, h, p)); _chk(dt, "dt", torch.float32, (bsz, h))
+    _chk(a, "a", torch.float32, (h,)); _chk(b, "b", act, (bsz, g, r)); _chk(c, "c", act, (bsz, g, r))
+    _chk(d, "d", torch.float32, (h,), optional=True); _chk(dt_bias, "dt_bias", torch.float32, (h,), optional=True)
+    _chk(z, "z", act, (bsz, h, p), optional=True)
+    y = torch.empty_like(x)
+    args = _ffi.Step2Args(batch=bsz, nheads=h, headdim=p, state_rank=r, ngroups=g, dtype=_DT[act], state=_ptr(state),
+                          x=_ptr(x), dt=_ptr(dt), a=_ptr(a), b=_ptr(b), c=_ptr(c), d=_ptr(d), dt_bias=_ptr(dt_bias),
+                          dt_min=dt_limit[0], dt_max=dt_limit[1], z=_ptr(z), y=_ptr(y))
+    check(lib.bm_step2(C.byref(args), _stream()), "bm_step2")
+    return y
+
+
+def conv_step(window, xin, weight, bias=None):
+    """Causal depthwise conv, one token: slides `window` [b,v,k] f32 in place, returns silu(conv) [b,v]."""
+    bsz, v, k = window.shape
+    _chk(window, "window", torch.float32); _chk(xin, "xin", None, (bsz, v))
+    _chk(weight, "weight", torch.float32, (v, k)); _chk(bias, "bias", torch.float32, (v,), optional=True)
+    out = torch.empty_like(xin)
+    args = _ffi.ConvStepArgs(batch=bsz, channels=v, kernel=k, dtype=_DT[xin.dtype], window=_ptr(window),
+                             xin=_ptr(xin), weight=_ptr(weight), bias=_ptr(bias), out=_ptr(out))
+    check(lib.bm_conv_step(C.byref(args), _stream()), "bm_conv_step")
+    return out
+
+
+def selscan1_fwd(u, delta, a, b, c, d=None, z=None, h0=None, delta_bias=None, delta_softplus=False):
+    """Mamba-1 selective scan.  u/delta/z [b,s,i], a [i,r] f32, b/c [b,s,r] -> (y [b,s,i], h_final [b,i,r] f32)."""
+    bsz, s, di = u.shape
+    r = a.shape[1]
+    act = u.dtype
+    _chk(u, "u"); _chk(delta, "delta", act, (bsz, s, di)); _chk(a, "a", torch.float32, (di, r))
+    _chk(b, "b", act, (bsz, s, r)); _chk(c, "c", act, (bsz, s, r)); _chk(d, "d", torch.float32, (di,), optional=True)
+    _chk(z, "z", act, (bsz, s, di), optional=True); _chk(h0, "h0", torch.float32, (bsz, di, r), optional=True)
+    _chk(delta_bias, "delta_bias", torch.float32, (di,), optional=True)
+    y = torch.empty_like(u)
+    h_final = torch.empty((bsz, di, r), dtype=torch.float32, device=u.device)
+    args = _ffi.Selscan1Args(batch=bsz, seqlen=s, d_inner=di, state_rank=r, dtype=_DT[act],
+                             delta_softplus=int(delta_softplus), u=_ptr(u), delta=_ptr(delta), a=_ptr(a), b=_ptr(b),
+                             c=_ptr(c), d=_ptr(d), delta_bias=_ptr(delta_bias), z=_ptr(z), h0=_ptr(h0), y=_ptr(y),
+                             h_final=_ptr(h_final))
+    check(lib.bm_selscan1_fwd(C.byref(args), _stream()), "bm_selscan1_fwd")
+    return y, h_final
+
+
+def step1(state, u, delta, a, b, c, d=None, z=None, delta_bias=None, delta_softplus=False):
+    """Mamba-1 recurrent step; `state` [b,i,r] f32 updated in place.  Returns y [b,i]."""
+    bsz, di, r = state.shape
+    act = u.dtype
+    _chk(state, "state", torch.float32); _chk(u, "u", act, (bsz, di)); _chk(delta, "delta", act, (bsz, di))
+    _chk(a, "a", torch.float32, (di, r)); _chk(b, "b", act, (bsz, r)); _chk(c, "c", act, (bsz, r))
+    _chk(d, "d", torch.float32, (di,), optional=True); _chk(z, "z", act, (bsz, di), optional=True)
+    _chk(delta_bias, "delta_bias", torch.float32, (di,), optional=True)
+    y = torch.empty_like(u)
+    args = _ffi.Step1Args(batch=bsz, d_inner=di, state_rank=r, dtype=_DT[act], delta_softplus=int(delta_softplus),
+                          state=_ptr(state), u=_ptr(u), delta=_ptr(delta), a=_ptr(a), b=_ptr(b), c=_ptr(c), d=_ptr(d),
+                          delta_bias=_ptr(delta_bias), z=_ptr(z), y=_ptr(y))
+    check(lib.bm_step1(C.byref(args), _stream()), "bm_step1")
+    return y
+
+
+def _ssd3(fn_name, v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, path):
+    bsz, s, m, h, p = v.shape
+    r = b.shape[-1]
+    act = v.dtype
+    _chk(v, "v"); _chk(da, "da", torch.float32, (bsz, s, h)); _chk(b, "b", act, (bsz, s, m, h, r))
+    _chk(c, "c", act, (bsz, s, m, h, r)); _chk(gamma, "gamma", torch.float32, (bsz, s, h), optional=True)
+    _chk(scale, "scale", torch.float32, (bsz, s, h), optional=True)
+    _chk(h0, "h0", torch.float32, (bsz, h, p, r), optional=True)
+    if angles is not None:
+        _chk(angles, "angles", torch.float32, (bsz, s, h, max(rope_dim // 2, 1)))
+    y = torch.empty_like(v)
+    h_final = torch.empty((bsz, h, p, r), dtype=torch.float32, device=v.device)
+    args = _ffi.Ssd3FwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, mimo_rank=m, chunk_len=chunk_len,
+                            dtype=_DT[act], path=PATHS[path], rope_dim=rope_dim, v=_ptr(v), da=_ptr(da), b=_ptr(b),
+                            c=_ptr(c), gamma=_ptr(gamma), scale=_ptr(scale), h0=_ptr(h0), angles=_ptr(angles),
+                            y=_ptr(y), h_final=_ptr(h_final))
+    nbytes = lib.bm_ssd3_fwd_workspace_bytes(C.byref(args))
+    ws = _workspace(nbytes, v.device)
+    check(getattr(lib, fn_name)(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), fn_name)
+    return y, h_final
+
+
+def ssd3_single_fwd(v, da, b, c, gamma, scale, h0=None, chunk_len=64, angles=None, rope_dim=0, path="auto"):
+    """Mamba-3 single-pass SSD.  v [b,s,m,h,p], da/gamma/scale [b,s,h] f32, b/c [b,s,m,h,r]."""
+    return _ssd3("bm_ssd3_single_fwd", v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, path)
+
+
+def ssd3_double_fwd(v, da, b, c, h0=None, chunk_len=64, angles=None, rope_dim=0, path="auto"):
+    """Generic MIMO SSD on pre-scaled v (one pass of Mamba-3's double-SSD pathway)."""
+    return _ssd3("bm_ssd3_double_fwd", v, da, b, c, None, None, h0, chunk_len, angles, rope_dim, path)
+
+
+def angle_cumsum(rot, dt, prev=None, rng=2.0):
+    """theta [b,s,h,a] = prev + cumsum_s(dt * range * pi * tanh(rot)); also returns wrap(theta[:, -1])."""
+    bsz, s, na = rot.shape
+    h = dt.shape[2]
+    _chk(rot, "rot", torch.float32); _chk(dt, "dt", torch.float32, (bsz, s, h))
+    _chk(prev, "prev", torch.float32, (bsz, h, na), optional=True)
+    theta = torch.empty((bsz, s, h, na), dtype=torch.float32, device=rot.device)
+    last = torch.empty((bsz, h, na), dtype=torch.float32, device=rot.device)
+    args = _ffi.AngleCumsumArgs(batch=bsz, seqlen=s, nheads=h, nangles=na, range=rng, rot=_ptr(rot), dt=_ptr(dt),
+                                prev=_ptr(prev), theta=_ptr(theta), last=_ptr(last))
+    check(lib.bm_angle_cumsum(C.byref(args), _stream()), "bm_angle_cumsum")
+    return theta, last
+
+
+def step3(state, k_state, v_state, angle, x, b, c, rot, dt, alpha, beta, gamma, mimo_x=None, rope_dim=None, rng=2.0):
+    """Mamba-3 recurrent step; state / k_state / v_state / angle are updated in place.  Returns y [b,m,h,p]."""
+    bsz, h, p, r = state.shape
+    m = b.shape[1]
+    if rope_dim is None:
+        rope_dim = r
+    na = max(rope_dim // 2, 1)
+    f = torch.float32
+    _chk(state, "state", f); _chk(k_state, "k_state", f, (bsz, m, h, r)); _chk(v_state, "v_state", f, (bsz, h, p))
+    _chk(angle, "angle", f, (bsz, h, na)); _chk(x, "x", f, (bsz, h, p)); _chk(b, "b", f, (bsz, m, h, r))
+    _chk(c, "c", f, (bsz, m, h, r)); _chk(rot, "rot", f, (bsz, na))
+    for n_, t_ in (("dt", dt), ("alpha", alpha), ("beta", beta), ("gamma", gamma)):
+        _chk(t_, n_, f, (bsz, h))
+    _chk(mimo_x, "mimo_x", f, (h, m, p), optional=True)
+    y = torch.empty((bsz, m, h, p), dtype=f, device=state.device)
+    args = _ffi.Step3Args(batch=bsz, nheads=h, headdim=p, state_rank=r, mimo_rank=m, rope_dim=rope_dim, range=rng,
+                          state=_ptr(state), k_state=_ptr(k_state), v_state=_ptr(v_state), angle=_ptr(angle),
+                          x=_ptr(x), b=_ptr(b), c=_ptr(c), rot=_ptr(rot), dt=_ptr(dt), alpha=_ptr(alpha),
+                          beta=_ptr(beta), gamma=_ptr(gamma), mimo_x=_ptr(mimo_x), y=_ptr(y))
+    check(lib.bm_step3(C.byref(args), _stream()), "bm_step3")
+    return y

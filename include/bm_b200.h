@@ -1,0 +1,254 @@
+/*
+ * bm_b200.h -- C ABI of libbm_b200.so: the burn-mamba SSM hot path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point
+ *   - takes DEVICE pointers owned by the caller (plain pointers and sizes, no framework types),
+ *   - is asynchronous on the CUDA stream passed as `stream` (a cudaStream_t cast to void*; NULL =
+ *     the legacy default stream) and runs on the caller's current device,
+ *   - allocates nothing: scratch memory is a caller-provided workspace whose size the matching
+ *     *_workspace_bytes() function reports (a pure host function),
+ *   - returns a bm_status (0 = OK, negative = error) and never aborts or throws; the message of the
+ *     last error on the calling thread is available from bm_last_error_string().
+ *
+ * Layouts are dense row-major with the last-listed axis contiguous.  Shape letters follow the
+ * reference crate: b batch, s sequence, h heads, p per-head dim, r state rank, g groups,
+ * m MIMO rank, a rope angles, i d_inner (Mamba-1), v conv channels, k conv kernel.
+ * "act dtype" tensors are float32 or bfloat16 as selected by the `dtype` field; decay inputs
+ * (dt, da, A, D, gamma, scale, angles) and every recurrent state are always float32.
+ * Pointers must be 16-byte aligned.  Head h reads B/C group h / (nheads / ngroups).
+ *
+ * Citations are file:line inside swfsql/burn-mamba.
+ */
+#ifndef BM_B200_H
+#define BM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    BM_OK = 0,
+    BM_ERR_NULL_POINTER = -1,
+    BM_ERR_BAD_SHAPE = -2,
+    BM_ERR_BAD_ALIGNMENT = -3,
+    BM_ERR_UNSUPPORTED = -4,
+    BM_ERR_WORKSPACE_TOO_SMALL = -5,
+    BM_ERR_CUDA = -6,
+    BM_ERR_TIMEOUT = -7
+} bm_status;
+
+typedef enum { BM_DTYPE_F32 = 0, BM_DTYPE_BF16 = 1 } bm_dtype;
+
+/* Kernel-family selection for the SSD forward entry points. */
+typedef enum {
+    BM_PATH_AUTO = 0,    /* tensor-core path when dtype/shape allow it, else the exact path */
+    BM_PATH_EXACT = 1,   /* CUDA-core float32 arithmetic for any shape and dtype */
+    BM_PATH_TENSOR = 2   /* tcgen05/TMEM/TMA path; BM_ERR_UNSUPPORTED if the shape is not covered */
+} bm_path;
+
+/* ABI version (major << 16 | minor) and a human-readable build string. */
+int32_t bm_version(void);
+const char* bm_build_info(void);
+/* Message of the last error raised on the calling thread ("" if none). */
+const char* bm_last_error_string(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * Mamba-2 chunked SSD forward.
+ * Replaces Mamba2BackendExt::ssd_serial_recalculated
+ *   (src/mamba2/ssd/serial_recalculated/serial_recalculated.rs:86-156) and the K1..K5 chain of
+ *   ssd_serial (src/mamba2/ssd/serial.rs:34-506); call site src/mamba2/mamba2.rs:737-748.
+ * seqlen need not be a multiple of chunk_len: the tail chunk behaves as if padded with dt = 0
+ *   (src/mamba2/mamba2.rs:703-722).
+ * y = exp(cum) (C . h^T) + ((C B^T) * exp(cum_t - cum_s)[s<=t] * dt_s) X + D X; h_final = state after
+ * the last token.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t batch, seqlen, nheads, headdim, state_rank, ngroups, chunk_len;
+    int32_t dtype;            /* bm_dtype of x, b, c, y, z */
+    int32_t path;             /* bm_path */
+    int32_t reserved;
+    const void* x;            /* [b, s, h, p] act dtype */
+    const float* dt;          /* [b, s, h]   discretised step (post softplus/clamp), or raw when dt_bias set */
+    const float* a;           /* [h]         A_h = -exp(a_log_h) */
+    const void* b;            /* [b, s, g, r] act dtype */
+    const void* c;            /* [b, s, g, r] act dtype */
+    const float* d;           /* [h] skip weight; NULL = no skip */
+    const float* h0;          /* [b, h, p, r] initial state; NULL = zeros */
+    const float* dt_bias;     /* [h] optional: dt := clamp(softplus(dt + dt_bias), dt_min, dt_max)
+                                 (src/mamba2/mamba2.rs:692-697); NULL = dt used as given */
+    float dt_min, dt_max;     /* clamp limits used with dt_bias (reference default 0, 65504) */
+    const void* z;            /* [b, s, h, p] optional gate: y := y * silu(z)
+                                 (the gate half of src/modules/norm/rms_norm_gated.rs:70-135); NULL = none */
+    void* y;                  /* [b, s, h, p] act dtype */
+    float* h_final;           /* [b, h, p, r] */
+    float* chunk_states;      /* optional [b, ceil(s/chunk_len), h, p, r]: state entering every chunk
+                                 (what K4 emits, src/mamba2/ssd/serial.rs:275-343); NULL = not wanted */
+} bm_ssd2_fwd_args;
+
+size_t bm_ssd2_fwd_workspace_bytes(const bm_ssd2_fwd_args* args);
+int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Mamba-2 recurrent step: state update + readout for one token, state updated in place.
+ * Replaces the body of Mamba2::step between the conv and the gated norm
+ *   (src/mamba2/mamba2.rs:907-991): h = exp(dt A) h + dt B (x) x ; y = sum_r C h + D x.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t batch, nheads, headdim, state_rank, ngroups;
+    int32_t dtype;            /* bm_dtype of x, b, c, y, z */
+    float* state;             /* [b, h, p, r] in/out (Mamba2Cache.ssm_bhpr, src/mamba2/cache.rs:98-122) */
+    const void* x;            /* [b, h, p] */
+    const float* dt;          /* [b, h] discretised step, or raw when dt_bias set */
+    const float* a;           /* [h] */
+    const void* b;            /* [b, g, r] */
+    const void* c;            /* [b, g, r] */
+    const float* d;           /* [h] or NULL */
+    const float* dt_bias;     /* [h] optional fused softplus(dt + bias) + clamp */
+    float dt_min, dt_max;
+    const void* z;            /* [b, h, p] optional gate y *= silu(z) */
+    void* y;                  /* [b, h, p] */
+} bm_step2_args;
+
+int32_t bm_step2(const bm_step2_args* args, void* stream);
+
+/* Causal depthwise conv window slide + dot + bias + SiLU for one token
+ * (src/mamba2/mamba2.rs:865-902; Mamba-1 twin src/mamba1/mamba1.rs:556-590).
+ * window: [b, v, k] float32, newest column last (src/mamba2/cache.rs:98-110); updated in place. */
+typedef struct {
+    int32_t batch, channels, kernel;
+    int32_t dtype;            /* bm_dtype of xin / out */
+    float* window;            /* [b, v, k] in/out */
+    const void* xin;          /* [b, v] new pre-conv column */
+    const float* weight;      /* [v, k] */
+    const float* bias;        /* [v] or NULL */
+    void* out;                /* [b, v] = silu(sum_k window * weight + bias) */
+} bm_conv_step_args;
+
+int32_t bm_conv_step(const bm_conv_step_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Mamba-1 selective scan (sequence) and single-token step.
+ * Replace Mamba1::selective_scan (src/mamba1/mamba1.rs:422-523) and
+ *   Mamba1::selective_scan_step (src/mamba1/mamba1.rs:666-733):
+ *   h = h exp(delta (x) A) + delta B u ; y = h . C + D u ; optional y *= silu(z) (the block's gate,
+ *   src/mamba1/mamba1.rs:348).  All sequence tensors are batch-major [b, s, ...].
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t batch, seqlen, d_inner, state_rank;
+    int32_t dtype;            /* bm_dtype of u, delta, b, c, z, y */
+    int32_t delta_softplus;   /* 1: delta := softplus(delta + delta_bias) (stock softplus, mamba1.rs:394) */
+    const void* u;            /* [b, s, i] */
+    const void* delta;        /* [b, s, i] */
+    const float* a;           /* [i, r]  A = -exp(a_log) */
+    const void* b;            /* [b, s, r] */
+    const void* c;            /* [b, s, r] */
+    const float* d;           /* [i] or NULL */
+    const float* delta_bias;  /* [i] or NULL (only read when delta_softplus) */
+    const void* z;            /* [b, s, i] or NULL */
+    const float* h0;          /* [b, i, r] or NULL */
+    void* y;                  /* [b, s, i] */
+    float* h_final;           /* [b, i, r] */
+} bm_selscan1_args;
+
+int32_t bm_selscan1_fwd(const bm_selscan1_args* args, void* stream);
+
+typedef struct {
+    int32_t batch, d_inner, state_rank;
+    int32_t dtype;
+    int32_t delta_softplus;
+    float* state;             /* [b, i, r] in/out (Mamba1Cache.ssm_bir, src/mamba1/cache.rs:30-47) */
+    const void* u;            /* [b, i] */
+    const void* delta;        /* [b, i] */
+    const float* a;           /* [i, r] */
+    const void* b;            /* [b, r] */
+    const void* c;            /* [b, r] */
+    const float* d;           /* [i] or NULL */
+    const float* delta_bias;  /* [i] or NULL */
+    const void* z;            /* [b, i] or NULL */
+    void* y;                  /* [b, i] */
+} bm_step1_args;
+
+int32_t bm_step1(const bm_step1_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Mamba-3 SSD forward (single-pass and generic/double-pass cores).
+ * bm_ssd3_single_fwd replaces Mamba3SingleSsdBackendExt::single_ssd_serial_recalculated
+ *   (src/mamba3/single_ssd/ssd/serial_recalculated/serial_recalculated.rs:86-163; math in
+ *   src/mamba3/single_ssd/ssd/serial.rs:56-268 and src/mamba3/single_ssd/ssd/diag.rs:50-100).
+ * bm_ssd3_double_fwd replaces Mamba3DoubleSsdBackendExt::double_ssd_serial_recalculated
+ *   (src/mamba3/double_ssd/ssd/serial_recalculated/serial_recalculated.rs:76-97; math in
+ *   src/mamba3/double_ssd/ssd/serial.rs:56-409): gamma = scale = NULL, non-strict mask.
+ * B and C are per head.  When `angles` is given, B and C are the *un-rotated* (normed + biased)
+ * tensors and the data-dependent rotation of src/mamba3/rotation/mod.rs:653-679 /
+ * src/modules/misc/rope.rs:50-170 is applied as they are loaded.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t batch, seqlen, nheads, headdim, state_rank, mimo_rank, chunk_len;
+    int32_t dtype;            /* bm_dtype of v, b, c, y */
+    int32_t path;             /* bm_path */
+    int32_t rope_dim;         /* number of leading B/C entries that rotate (even, <= r); used with angles */
+    const void* v;            /* [b, s, m, h, p] */
+    const float* da;          /* [b, s, h]  dt * A_t */
+    const void* b;            /* [b, s, m, h, r] */
+    const void* c;            /* [b, s, m, h, r] */
+    const float* gamma;       /* [b, s, h] (single) or NULL (double) */
+    const float* scale;       /* [b, s, h] (single) or NULL (double) */
+    const float* h0;          /* [b, h, p, r] or NULL */
+    const float* angles;      /* [b, s, h, a] cumulative angles, a = rope_dim / 2; NULL = B/C already rotated */
+    void* y;                  /* [b, s, m, h, p] */
+    float* h_final;           /* [b, h, p, r] */
+} bm_ssd3_fwd_args;
+
+size_t bm_ssd3_fwd_workspace_bytes(const bm_ssd3_fwd_args* args);
+int32_t bm_ssd3_single_fwd(const bm_ssd3_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
+int32_t bm_ssd3_double_fwd(const bm_ssd3_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Cumulative rotation angles (Complex2D), replacing the angle part of rotate_bc_forward
+ * (src/mamba3/rotation/mod.rs:653-679, increment :559-567):
+ *   theta[b,s,h,a] = prev[b,h,a] + cumsum_s( dt[b,s,h] * range * pi * tanh(rot[b,s,a]) ),
+ *   last[b,h,a] = wrap(theta[b,S-1,h,a]) (src/modules/misc/rope.rs:23-27). */
+typedef struct {
+    int32_t batch, seqlen, nheads, nangles;
+    float range;
+    const float* rot;         /* [b, s, a] */
+    const float* dt;          /* [b, s, h] */
+    const float* prev;        /* [b, h, a] or NULL */
+    float* theta;             /* [b, s, h, a] */
+    float* last;              /* [b, h, a] or NULL */
+} bm_angle_cumsum_args;
+
+int32_t bm_angle_cumsum(const bm_angle_cumsum_args* args, void* stream);
+
+/* Mamba-3 recurrent step: rotation of B/C by the updated angle, state update, readout.
+ * Replaces the core of Mamba3::step_double_ssd (src/mamba3/double_ssd/double_ssd/mod.rs:672-757;
+ * rotation src/mamba3/rotation/mod.rs:729-764):
+ *   h = alpha h + sum_m (gamma x*mx_m) (x) B_m + sum_m (beta x_prev*mx_m) (x) Bprev_m ; y_m = C_m . h
+ * and rolls the cache: k_state := rotated B, v_state := x, angle := wrapped new angle. */
+typedef struct {
+    int32_t batch, nheads, headdim, state_rank, mimo_rank, rope_dim;
+    float range;
+    float* state;             /* [b, h, p, r] in/out */
+    float* k_state;           /* [b, m, h, r] in/out: rotated B of the previous token */
+    float* v_state;           /* [b, h, p]    in/out: x of the previous token */
+    float* angle;             /* [b, h, a]    in/out, a = max(rope_dim / 2, 1) */
+    const float* x;           /* [b, h, p] */
+    const float* b;           /* [b, m, h, r] normed + biased, un-rotated */
+    const float* c;           /* [b, m, h, r] normed + biased, un-rotated */
+    const float* rot;         /* [b, a] raw rotation channels */
+    const float* dt;          /* [b, h] */
+    const float* alpha;       /* [b, h] */
+    const float* beta;        /* [b, h] */
+    const float* gamma;       /* [b, h] */
+    const float* mimo_x;      /* [h, m, p] or NULL (treated as ones) */
+    float* y;                 /* [b, m, h, p] = C_m . h (before the D skip) */
+} bm_step3_args;
+
+int32_t bm_step3(const bm_step3_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BM_B200_H */

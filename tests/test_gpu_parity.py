@@ -1,0 +1,262 @@
+"""GPU parity tests: every C-ABI entry point against the CPU oracle on the same seeded inputs.
+
+Tolerances (rel-L2, stated by the benchmark definition): 1e-4 for float32, 2e-2 for bfloat16, on
+outputs and on final states.  The reference's own tolerances at tiny shapes are max-abs 1e-4.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import inputs, mamba1, mamba2, mamba3
+from oracle.numerics import rel_l2, bf16_round
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2}
+
+
+def dev(x, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.float().cpu().numpy()
+
+
+def q(x, dtype):
+    """The values the kernel actually sees for an activation tensor of `dtype`."""
+    return bf16_round(x) if dtype == torch.bfloat16 else x
+
+
+# ------------------------------------------------------------------ Mamba-2 SSD (exact path)
+def _ssd2_case(bm, cfg, chunk_len, dtype, path="exact", use_h0=True, tol=None, **kw):
+    x, b, c = (q(cfg[k], dtype) for k in ("x", "b", "c"))
+    h0 = cfg["h0"] if use_h0 else None
+    want_y, want_h = mamba2.ssd_serial(x, cfg["dt"], cfg["a"], b, c, cfg["d"],
+                                       cfg["h0"] if use_h0 else np.zeros_like(cfg["h0"]), chunk_len)
+    y, h = bm.ops.ssd2_fwd(dev(x, dtype), dev(cfg["dt"]), dev(cfg["a"]), dev(b, dtype), dev(c, dtype), dev(cfg["d"]),
+                           None if h0 is None else dev(h0), chunk_len=chunk_len, path=path, **kw)
+    torch.cuda.synchronize()
+    tol = tol or TOL[dtype]
+    ey, eh = rel_l2(host(y), want_y), rel_l2(host(h), want_h)
+    assert ey <= tol and eh <= tol, (ey, eh)
+    return y, h
+
+
+@pytest.mark.parametrize("b,s,h,p,r,g,Q", [
+    (2, 4, 2, 8, 8, 1, 4),      # the reference's tiny shapes (src/mamba2/ssd/ssd_path/tests.rs:15-68)
+    (2, 12, 4, 8, 8, 2, 4),
+    (2, 10, 4, 8, 8, 1, 4),     # ragged tail chunk
+    (1, 37, 3, 16, 24, 3, 16),  # odd everything
+    (2, 512, 8, 64, 64, 1, 64),  # the CPU-runnable configuration's SSD shape
+    (1, 300, 4, 64, 128, 2, 256),
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ssd2_exact_matches_oracle(bm, b, s, h, p, r, g, Q, dtype):
+    cfg = inputs.ssd2_prefill(seed=100 + s, batch=b, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g,
+                              h0_std=0.1)
+    _ssd2_case(bm, cfg, Q, dtype)
+
+
+def test_ssd2_exact_zero_state_and_chunk_states(bm):
+    cfg = inputs.ssd2_prefill(seed=7, batch=2, seqlen=96, nheads=4, headdim=16, state_rank=16)
+    _ssd2_case(bm, cfg, 32, torch.float32, use_h0=False)
+    t = {k: dev(v) for k, v in cfg.items()}
+    y, hf, st = bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=32, path="exact",
+                                return_chunk_states=True)
+    _, _, want = mamba2.ssd_serial(cfg["x"], cfg["dt"], cfg["a"], cfg["b"], cfg["c"], cfg["d"], cfg["h0"], 32,
+                                   return_chunk_states=True)
+    assert rel_l2(host(st), want) <= 1e-4
+
+
+def test_ssd2_fused_dt_bias_and_gate(bm):
+    cfg = inputs.ssd2_prefill(seed=8, batch=2, seqlen=70, nheads=4, headdim=16, state_rank=16, h0_std=0.1)
+    rng = np.random.default_rng(0)
+    raw = rng.standard_normal(cfg["dt"].shape).astype(np.float32)
+    z = rng.standard_normal(cfg["x"].shape).astype(np.float32)
+    from oracle.numerics import softplus, silu
+    dt = np.clip(softplus(raw + cfg["dt_bias"], "f32"), 0.0, 65504.0).astype(np.float32)
+    want_y, want_h = mamba2.ssd_serial(cfg["x"], dt, cfg["a"], cfg["b"], cfg["c"], cfg["d"], cfg["h0"], 32)
+    y, h = bm.ops.ssd2_fwd(dev(cfg["x"]), dev(raw), dev(cfg["a"]), dev(cfg["b"]), dev(cfg["c"]), dev(cfg["d"]),
+                           dev(cfg["h0"]), chunk_len=32, path="exact", dt_bias=dev(cfg["dt_bias"]), z=dev(z))
+    assert rel_l2(host(y), want_y * silu(z)) <= 1e-4 and rel_l2(host(h), want_h) <= 1e-4
+
+
+def test_ssd2_split_prefill_equals_full(bm):
+    """split == full (src/mamba2/mamba2/tests.rs:343-392) at the slot level, CUDA vs CUDA."""
+    cfg = inputs.ssd2_prefill(seed=9, batch=2, seqlen=200, nheads=4, headdim=32, state_rank=32, h0_std=0.1)
+    t = {k: dev(v) for k, v in cfg.items()}
+    y, h = bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=64, path="exact")
+    cut = 77
+    y1, h1 = bm.ops.ssd2_fwd(t["x"][:, :cut].contiguous(), t["dt"][:, :cut].contiguous(), t["a"],
+                             t["b"][:, :cut].contiguous(), t["c"][:, :cut].contiguous(), t["d"], t["h0"],
+                             chunk_len=64, path="exact")
+    y2, h2 = bm.ops.ssd2_fwd(t["x"][:, cut:].contiguous(), t["dt"][:, cut:].contiguous(), t["a"],
+                             t["b"][:, cut:].contiguous(), t["c"][:, cut:].contiguous(), t["d"], h1,
+                             chunk_len=64, path="exact")
+    assert rel_l2(host(torch.cat([y1, y2], 1)), host(y)) <= 1e-5 and rel_l2(host(h2), host(h)) <= 1e-5
+
+
+def test_ssd2_forward_equals_unrolled_step(bm):
+    """forward == unrolled step (src/mamba2/mamba2/tests.rs:202-252), CUDA SSD vs CUDA step kernel."""
+    cfg = inputs.ssd2_prefill(seed=10, batch=2, seqlen=48, nheads=4, headdim=32, state_rank=64, ngroups=2, h0_std=0.1)
+    t = {k: dev(v) for k, v in cfg.items()}
+    y, h = bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=16, path="exact")
+    state = t["h0"].clone()
+    for s in range(48):
+        ys = bm.ops.step2(state, t["x"][:, s].contiguous(), t["dt"][:, s].contiguous(), t["a"],
+                          t["b"][:, s].contiguous(), t["c"][:, s].contiguous(), t["d"])
+        assert torch.max(torch.abs(ys - y[:, s])).item() <= 1e-4
+    assert torch.max(torch.abs(state - h)).item() <= 1e-4
+
+
+def test_ssd2_rejects_bad_arguments(bm):
+    cfg = inputs.ssd2_prefill(seed=1, batch=1, seqlen=8, nheads=2, headdim=8, state_rank=8)
+    t = {k: dev(v) for k, v in cfg.items()}
+    with pytest.raises(bm.BmError) as e:
+        bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=0, path="exact")
+    assert e.value.code == bm._ffi.BM_ERR_BAD_SHAPE
+    with pytest.raises(bm.BmError) as e:
+        bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=4, path="tensor")
+    assert e.value.code == bm._ffi.BM_ERR_UNSUPPORTED
+
+
+# ------------------------------------------------------------------ Mamba-2 step / conv step
+@pytest.mark.parametrize("b,h,p,r,g", [(2, 4, 8, 8, 1), (3, 4, 64, 128, 2), (2, 2, 16, 256, 1), (2, 2, 5, 6, 1),
+                                       (4, 8, 64, 64, 1), (2, 3, 7, 16, 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_step2_matches_oracle(bm, b, h, p, r, g, dtype):
+    cfg = inputs.step2_decode(seed=5, batch=b, nheads=h, headdim=p, state_rank=r, ngroups=g, steps=3)
+    state = dev(cfg["state"])
+    ref = cfg["state"].copy()
+    for s in range(3):
+        x, bb, cc = (q(cfg[k][s], dtype) for k in ("x", "b", "c"))
+        want_y, ref = mamba2.ssm_step(ref, x, cfg["dt"][s], cfg["a"], bb, cc, cfg["d"])
+        y = bm.ops.step2(state, dev(x, dtype), dev(cfg["dt"][s]), dev(cfg["a"]), dev(bb, dtype), dev(cc, dtype),
+                         dev(cfg["d"]))
+        assert rel_l2(host(y), want_y) <= TOL[dtype]
+    assert rel_l2(host(state), ref) <= 1e-5
+
+
+def test_conv_step_matches_oracle(bm):
+    rng = np.random.default_rng(3)
+    b, v, k = 3, 40, 4
+    win = rng.standard_normal((b, v, k)).astype(np.float32)
+    w = rng.standard_normal((v, k)).astype(np.float32)
+    bias = rng.standard_normal(v).astype(np.float32)
+    window = dev(win)
+    from oracle.numerics import silu
+    for _ in range(3):
+        xin = rng.standard_normal((b, v)).astype(np.float32)
+        win = np.concatenate([win[:, :, 1:], xin[:, :, None]], axis=2)
+        want = silu((win * w[None]).sum(-1) + bias[None])
+        out = bm.ops.conv_step(window, dev(xin), dev(w), dev(bias))
+        assert rel_l2(host(out), want) <= 1e-5
+    assert np.array_equal(host(window), win)
+
+
+# ------------------------------------------------------------------ Mamba-1
+@pytest.mark.parametrize("b,s,i,r", [(2, 9, 24, 4), (2, 200, 64, 16), (1, 130, 96, 8), (2, 33, 10, 3)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_selscan1_matches_oracle(bm, b, s, i, r, dtype):
+    cfg = inputs.selscan1(seed=1, batch=b, seqlen=s, d_inner=i, state_rank=r)
+    rng = np.random.default_rng(2)
+    h0 = (0.1 * rng.standard_normal(cfg["h0"].shape)).astype(np.float32)
+    u, delta, bb, cc, z = (q(cfg[k], dtype) for k in ("u", "delta", "b", "c", "z"))
+    want_y, want_h = mamba1.selective_scan(delta, cfg["a"], bb, cc, cfg["d"], u, h0, dtype=np.float64)
+    from oracle.numerics import silu
+    want_y = want_y * silu(z.astype(np.float64))
+    y, hf = bm.ops.selscan1_fwd(dev(u, dtype), dev(delta, dtype), dev(cfg["a"]), dev(bb, dtype), dev(cc, dtype),
+                                dev(cfg["d"]), z=dev(z, dtype), h0=dev(h0))
+    assert rel_l2(host(y), want_y) <= TOL[dtype] and rel_l2(host(hf), want_h) <= TOL[dtype]
+
+
+def test_selscan1_forward_equals_unrolled_step(bm):
+    """src/mamba1/mamba1/tests.rs:216-265 at the scan level, CUDA vs CUDA."""
+    cfg = inputs.selscan1(seed=4, batch=2, seqlen=40, d_inner=64, state_rank=16)
+    t = {k: dev(v) for k, v in cfg.items()}
+    y, hf = bm.ops.selscan1_fwd(t["u"], t["delta"], t["a"], t["b"], t["c"], t["d"], h0=t["h0"])
+    state = t["h0"].clone()
+    for s in range(40):
+        ys = bm.ops.step1(state, t["u"][:, s].contiguous(), t["delta"][:, s].contiguous(), t["a"],
+                          t["b"][:, s].contiguous(), t["c"][:, s].contiguous(), t["d"])
+        assert torch.max(torch.abs(ys - y[:, s])).item() <= 1e-4
+    assert torch.max(torch.abs(state - hf)).item() <= 1e-4
+
+
+def test_selscan1_fused_softplus(bm):
+    cfg = inputs.selscan1(seed=6, batch=2, seqlen=70, d_inner=32, state_rank=16)
+    rng = np.random.default_rng(1)
+    raw = rng.standard_normal(cfg["delta"].shape).astype(np.float32)
+    bias = rng.standard_normal(32).astype(np.float32)
+    from oracle.numerics import softplus_stock
+    delta = softplus_stock(raw + bias)
+    want_y, want_h = mamba1.selective_scan(delta, cfg["a"], cfg["b"], cfg["c"], cfg["d"], cfg["u"], cfg["h0"])
+    y, hf = bm.ops.selscan1_fwd(dev(cfg["u"]), dev(raw), dev(cfg["a"]), dev(cfg["b"]), dev(cfg["c"]), dev(cfg["d"]),
+                                delta_bias=dev(bias), delta_softplus=True)
+    assert rel_l2(host(y), want_y) <= 1e-4 and rel_l2(host(hf), want_h) <= 1e-4
+
+
+# ------------------------------------------------------------------ Mamba-3
+@pytest.mark.parametrize("b,s,h,p,r,m,Q", [(2, 12, 2, 8, 8, 1, 4), (2, 12, 4, 8, 8, 2, 4), (2, 10, 2, 8, 8, 2, 4),
+                                           (1, 100, 2, 64, 128, 4, 64), (1, 70, 3, 16, 32, 3, 16)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ssd3_single_and_double_match_oracle(bm, b, s, h, p, r, m, Q, dtype):
+    cfg = inputs.ssd3_single(seed=40 + s, batch=b, seqlen=s, nheads=h, headdim=p, state_rank=r, mimo_rank=m,
+                             h0_std=0.1)
+    pairwise = m == 1
+    ang = cfg["angles"][:, :, None]
+    b_rot = mamba3.apply_rope_partial(q(cfg["b"], dtype), ang, r, pairwise)
+    c_rot = mamba3.apply_rope_partial(q(cfg["c"], dtype), ang, r, pairwise)
+    v = q(cfg["v"], dtype)
+    want_y, want_h = mamba3.single_ssd_serial(v, cfg["da"], b_rot, c_rot, cfg["gamma"], cfg["scale"], cfg["h0"], Q)
+    # rotation fused at load: raw B/C + angles
+    y, hf = bm.ops.ssd3_single_fwd(dev(v, dtype), dev(cfg["da"]), dev(cfg["b"], dtype), dev(cfg["c"], dtype),
+                                   dev(cfg["gamma"]), dev(cfg["scale"]), dev(cfg["h0"]), chunk_len=Q,
+                                   angles=dev(cfg["angles"]), rope_dim=r)
+    assert rel_l2(host(y), want_y) <= TOL[dtype] and rel_l2(host(hf), want_h) <= TOL[dtype]
+    if dtype == torch.float32:
+        # pre-rotated B/C, no angles
+        y2, hf2 = bm.ops.ssd3_single_fwd(dev(v), dev(cfg["da"]), dev(b_rot), dev(c_rot), dev(cfg["gamma"]),
+                                         dev(cfg["scale"]), dev(cfg["h0"]), chunk_len=Q)
+        assert rel_l2(host(y2), want_y) <= 1e-4 and rel_l2(host(hf2), want_h) <= 1e-4
+        want_yd, want_hd = mamba3.double_ssd_serial(v, cfg["da"], b_rot, c_rot, cfg["h0"], Q)
+        y3, hf3 = bm.ops.ssd3_double_fwd(dev(v), dev(cfg["da"]), dev(b_rot), dev(c_rot), dev(cfg["h0"]), chunk_len=Q)
+        assert rel_l2(host(y3), want_yd) <= 1e-4 and rel_l2(host(hf3), want_hd) <= 1e-4
+
+
+@pytest.mark.parametrize("m,rope_fraction", [(1, 1.0), (2, 1.0), (2, 0.5), (1, 0.5), (1, 0.0)])
+def test_angle_cumsum_and_step3_match_oracle_block(bm, m, rope_fraction):
+    """The oracle's Mamba-3 block supplies slot tensors; the CUDA angle scan and step kernel must
+    reproduce its rotation state, state update and readout token by token."""
+    rng = np.random.default_rng(12)
+    w = mamba3.Mamba3Weights(rng, d_model=16, d_inner=32, nheads=4, state_rank=16, mimo_rank=m,
+                             rope_fraction=rope_fraction, dtype=np.float32)
+    if m > 1:
+        w.mimo_x = (w.mimo_x + 0.2 * rng.standard_normal(w.mimo_x.shape)).astype(np.float32)
+    bsz, s = 2, 9
+    u = rng.standard_normal((bsz, s, 16)).astype(np.float32)
+    cache = {k: (v + 0.1 * rng.standard_normal(v.shape)).astype(np.float32)
+             for k, v in mamba3.zero_cache(w, bsz).items()}
+    z, x, bm_, cm_, co, rot = mamba3._project(w, u, "f32")
+    theta, last = bm.ops.angle_cumsum(dev(rot), dev(co["dt"]), dev(cache["angle"]), rng=w.rotation_range)
+    _, _, want_last, want_theta = mamba3.rotate_bc_forward(rot, co["dt"], cache["angle"], bm_, cm_, w.rope_dim,
+                                                           w.rotation_range)
+    assert np.max(np.abs(host(theta) - want_theta)) <= 1e-4
+    assert np.max(np.abs(np.angle(np.exp(1j * (host(last) - want_last))))) <= 1e-4
+    state, k_state, v_state, angle = (dev(cache[k]) for k in ("ssm", "k", "v", "angle"))
+    c = dict(cache)
+    for t in range(s):
+        br, cr, new_angle = mamba3.rotate_bc_step(rot[:, t], co["dt"][:, t], c["angle"], bm_[:, t], cm_[:, t],
+                                                  w.rope_dim, w.rotation_range)
+        want_y, h_new, _ = mamba3.ssm_step3(c["ssm"], x[:, t], c["v"], br, c["k"], cr, co["alpha"][:, t],
+                                            co["beta"][:, t], co["gamma"][:, t], w.mimo_x)
+        c = dict(ssm=h_new, k=br, v=x[:, t], angle=new_angle)
+        y = bm.ops.step3(state, k_state, v_state, angle, dev(x[:, t]), dev(bm_[:, t]), dev(cm_[:, t]),
+                         dev(rot[:, t]), dev(co["dt"][:, t]), dev(co["alpha"][:, t]), dev(co["beta"][:, t]),
+                         dev(co["gamma"][:, t]), None if w.mimo_x is None else dev(w.mimo_x), rope_dim=w.rope_dim,
+                         rng=w.rotation_range)
+        assert rel_l2(host(y), want_y) <= 1e-4
+    assert rel_l2(host(state), c["ssm"]) <= 1e-4 and rel_l2(host(k_state), c["k"]) <= 1e-4
+    assert np.array_equal(host(v_state), c["v"])
+    assert np.max(np.abs(np.angle(np.exp(1j * (host(angle) - c["angle"]))))) <= 1e-4
