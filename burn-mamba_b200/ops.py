@@ -67,7 +67,7 @@ def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bia
     _chk(dt_bias, "dt_bias", torch.float32, (h,), optional=True); _chk(z, "z", act, x.shape, optional=True)
     y = torch.empty_like(x)
     h_final = torch.empty((bsz, h, p, r), dtype=torch.float32, device=x.device)
-    nchunks = -(-s // chunk_len)
+    nchunks = -(-s // max(chunk_len, 1))
     states = torch.empty((bsz, nchunks, h, p, r), dtype=torch.float32, device=x.device) if return_chunk_states else None
     args = _ffi.Ssd2FwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, chunk_len=chunk_len,
                             dtype=_DT[act], path=PATHS[path], reserved=0, x=_ptr(x), dt=_ptr(dt), a=_ptr(a),
