@@ -74,6 +74,7 @@ SYMBOLS = {
     "bm_last_error_string": (C.c_char_p, []),
     "bm_ssd2_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd2FwdArgs)]),
     "bm_ssd2_fwd": (_i32, [C.POINTER(Ssd2FwdArgs), _vp, C.c_size_t, _vp]),
+    "bm_workspace_status": (_i32, [_vp, _vp]),
     "bm_step2": (_i32, [C.POINTER(Step2Args), _vp]),
     "bm_conv_step": (_i32, [C.POINTER(ConvStepArgs), _vp]),
     "bm_selscan1_fwd": (_i32, [C.POINTER(Selscan1Args), _vp]),

@@ -1,14 +1,558 @@
-// Tensor-core path of the Mamba-2 SSD forward (placeholder until the tcgen05 kernel lands).
+// Mamba-2 chunked SSD forward on the Blackwell tensor cores (tcgen05 / TMEM / TMA), bf16 operands
+// with float32 accumulation and float32 recurrent state.
+//
+// One persistent CTA per SM walks (batch, head) units; inside a unit it walks the sequence in tiles of
+// T = 128 tokens, keeping the head's state [r = 128, p = 64] in registers (float32) for the whole
+// sequence, so no per-chunk state ever goes to HBM.  Per tile (reference formulas:
+// src/mamba2/ssd/serial.rs:138-506, restated with the tile as the chunk):
+//     CB   = C B^T                                   tcgen05 SS   (K1/K2)
+//     P    = bf16(CB * exp(cum_t - cum_s)[s<=t] dt_s) in TMEM     (the mask of K5)
+//     Y1   = P X            Y2 = C h^T               tcgen05 TS / SS (K5)
+//     y    = Y1 + exp(cum_t) Y2 + D x                epilogue, TMA store
+//     S    = B^T (X * dt exp(cum_end - cum))         tcgen05 SS   (K3)
+//     h   <- exp(cum_end) h + S                      registers    (K4)
+// Warp roles: warp 0 TMA loads, warp 1 MMA issue, warp 2 TMEM allocation, warp 3 decay scan of dt,
+// warps 4-7 mask pass (CB -> P), warps 8-11 X scaling, state update and epilogue.
+// Every barrier wait is bounded; a wait that gives up stores BM_ERR_TIMEOUT in the status word of the
+// workspace and all roles leave their loops.
 #include "ssd2_tc.cuh"
+#include "tc_common.cuh"
 
 namespace bm {
 namespace tc {
 
-bool ssd2_supported(const bm_ssd2_fwd_args*) { return false; }
-const char* ssd2_why_not(const bm_ssd2_fwd_args*) { return "tensor-core kernel not built"; }
-size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args*) { return 0; }
-int32_t ssd2_run(const bm_ssd2_fwd_args*, void*, size_t, cudaStream_t) {
-    return fail(BM_ERR_UNSUPPORTED, "tensor-core kernel not built");
+namespace {
+
+constexpr int T = 128;        // tokens per tile
+constexpr int P = 64;         // head dim
+constexpr int R = 128;        // state rank
+constexpr int kThreads = 384;
+constexpr int kCumStages = 4;
+
+// shared-memory map (bytes from a 1024-aligned base)
+constexpr uint32_t kPanel = 16384;               // [128 rows x 128 B]
+constexpr uint32_t kOffC = 0;                    // 2 stages x 2 panels
+constexpr uint32_t kOffB = 65536;                // 2 stages x 2 panels
+constexpr uint32_t kOffX = 131072;               // 2 stages x 1 panel
+constexpr uint32_t kOffXw = 163840;
+constexpr uint32_t kOffH = 180224;
+constexpr uint32_t kOffY = 196608;
+constexpr uint32_t kOffCum = 212992;             // kCumStages x 5 arrays x 128 floats
+constexpr uint32_t kCumStageBytes = 5 * T * 4;
+constexpr uint32_t kOffBar = kOffCum + kCumStages * kCumStageBytes;
+constexpr uint32_t kSmemBytes = kOffBar + 512 + 1024;  // barriers + alignment slack
+constexpr uint32_t kLoadBytes = 2 * 2 * kPanel + kPanel;  // C + B + X per tile
+
+// TMEM columns
+constexpr uint32_t kColCB = 0;     // 2 buffers x 128 columns; P (bf16 pairs) aliases the first 64 of each
+constexpr uint32_t kColY1 = 256;
+constexpr uint32_t kColY2 = 320;
+constexpr uint32_t kColS = 384;
+
+struct Barriers {
+    uint64_t ld_full[2], ld_empty[2];
+    uint64_t cum_full[kCumStages], cum_empty[kCumStages];
+    uint64_t cb_full[2], p_ready[2];
+    uint64_t y_full, y_empty, h_ready, h_free, xw_ready, s_full, s_empty;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct alignas(64) Params {
+    CUtensorMap tm_x, tm_b, tm_c, tm_y;
+    const float* dt;
+    const float* a;
+    const float* d;
+    const float* h0;
+    const float* dt_bias;
+    float dt_min, dt_max;
+    float* h_final;
+    float* chunk_states;
+    int* status;
+    int B, S, H, G, Q, NC, tiles_per_unit, num_units;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+
+// Bounded wait used by single-thread roles (TMA producer, MMA issuer).
+#define BM_WAIT(bar, par)                                                        \
+    do {                                                                         \
+        if (!mbar_wait((bar), (par))) {                                          \
+            atomicExch(prm.status, (int)BM_ERR_TIMEOUT);                         \
+            *abort_flag = 1;                                                     \
+            goto done;                                                           \
+        }                                                                        \
+        if (*abort_flag) goto done;                                              \
+    } while (0)
+// Bounded wait executed by a whole warp; the leave/stay decision is made warp-uniform so that no lane
+// is left behind at a later __syncwarp or .aligned tcgen05 instruction.
+#define BM_WAIT_WARP(bar, par)                                                   \
+    do {                                                                         \
+        const bool ok_ = mbar_wait((bar), (par));                                \
+        const bool ab_ = *abort_flag != 0;                                       \
+        if (!__all_sync(0xffffffffu, ok_ && !ab_)) {                             \
+            if (!ok_) {                                                          \
+                atomicExch(prm.status, (int)BM_ERR_TIMEOUT);                     \
+                *abort_flag = 1;                                                 \
+            }                                                                    \
+            goto done;                                                           \
+        }                                                                        \
+    } while (0)
+
+__global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_constant__ Params prm) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kOffBar);
+    volatile uint32_t* abort_flag = &bars->abort_flag;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars->ld_full[i], 1);
+            mbar_init(&bars->ld_empty[i], 5);
+            mbar_init(&bars->cb_full[i], 1);
+            mbar_init(&bars->p_ready[i], 4);
+        }
+        for (int i = 0; i < kCumStages; ++i) {
+            mbar_init(&bars->cum_full[i], 1);
+            mbar_init(&bars->cum_empty[i], 8);
+        }
+        mbar_init(&bars->y_full, 1);
+        mbar_init(&bars->y_empty, 4);
+        mbar_init(&bars->h_ready, 4);
+        mbar_init(&bars->h_free, 1);
+        mbar_init(&bars->xw_ready, 4);
+        mbar_init(&bars->s_full, 1);
+        mbar_init(&bars->s_empty, 4);
+        bars->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 2) {
+        tmem_alloc(&bars->tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    const int tpu = prm.tiles_per_unit;
+    int my_units = 0;
+    for (int u = blockIdx.x; u < prm.num_units; u += gridDim.x) ++my_units;
+    const int total = my_units * tpu;
+    const int hpg = prm.H / prm.G;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&prm.tm_x);
+            tma_prefetch_desc(&prm.tm_b);
+            tma_prefetch_desc(&prm.tm_c);
+            tma_prefetch_desc(&prm.tm_y);
+            for (int it = 0; it < total; ++it) {
+                const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
+                const int b = unit / prm.H, h = unit % prm.H, g = h / hpg;
+                const int st = it & 1, s0 = i * T;
+                BM_WAIT(&bars->ld_empty[st], ((it >> 1) & 1) ^ 1);
+                mbar_expect_tx(&bars->ld_full[st], kLoadBytes);
+                unsigned char* cs = smem + kOffC + st * 2 * kPanel;
+                unsigned char* bs = smem + kOffB + st * 2 * kPanel;
+                tma_load_4d(cs, &prm.tm_c, &bars->ld_full[st], 0, g, s0, b);
+                tma_load_4d(cs + kPanel, &prm.tm_c, &bars->ld_full[st], 64, g, s0, b);
+                tma_load_4d(bs, &prm.tm_b, &bars->ld_full[st], 0, g, s0, b);
+                tma_load_4d(bs + kPanel, &prm.tm_b, &bars->ld_full[st], 64, g, s0, b);
+                tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->ld_full[st], 0, h, s0, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && total > 0) {
+            const uint32_t id_cb = umma_idesc_bf16(128, 128, false, false);
+            const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
+            const uint32_t id_mnmn = umma_idesc_bf16(128, 64, true, true);
+            const uint32_t c_base = smem_u32(smem + kOffC), b_base = smem_u32(smem + kOffB);
+            const uint32_t x_base = smem_u32(smem + kOffX), xw_base = smem_u32(smem + kOffXw), h_base = smem_u32(smem + kOffH);
+            auto mma_cb = [&](int it) {
+                const int st = it & 1;
+                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                    umma_ss(tmem + kColCB + st * 128, umma_desc_kmajor(cs + off), umma_desc_kmajor(bs + off), id_cb, k > 0);
+                }
+                umma_commit(&bars->cb_full[st]);
+            };
+            BM_WAIT(&bars->ld_full[0], 0);
+            mma_cb(0);
+            for (int it = 0; it < total; ++it) {
+                const int st = it & 1;
+                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel, xs = x_base + st * kPanel;
+                // Y2 = C . h^T
+                BM_WAIT(&bars->h_ready, it & 1);
+                BM_WAIT(&bars->y_empty, (it & 1) ^ 1);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                    umma_ss(tmem + kColY2, umma_desc_kmajor(cs + off), umma_desc_mnmajor(h_base + k * 2048, kPanel), id_kmn, k > 0);
+                }
+                umma_commit(&bars->h_free);
+                // S = B^T . Xw
+                BM_WAIT(&bars->xw_ready, it & 1);
+                BM_WAIT(&bars->s_empty, (it & 1) ^ 1);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_ss(tmem + kColS, umma_desc_mnmajor(bs + k * 2048, kPanel), umma_desc_mnmajor(xw_base + k * 2048, kPanel),
+                            id_mnmn, k > 0);
+                umma_commit(&bars->s_full);
+                // CB of the next tile (keeps the tensor pipe busy while the mask pass of this tile runs)
+                if (it + 1 < total) {
+                    BM_WAIT(&bars->ld_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
+                    mma_cb(it + 1);
+                }
+                // Y1 = P . X
+                BM_WAIT(&bars->p_ready[st], (it >> 1) & 1);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_ts(tmem + kColY1, tmem + kColCB + st * 128 + k * 8, umma_desc_mnmajor(xs + k * 2048, kPanel), id_kmn, k > 0);
+                umma_commit(&bars->y_full);
+                umma_commit(&bars->ld_empty[st]);
+            }
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------------ decay scan of dt
+        // log2-domain cumulative sum of dt*A over the tile, plus the derived per-token factors.
+        const float log2e = 1.4426950408889634f;
+        for (int it = 0; it < total; ++it) {
+            const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
+            const int b = unit / prm.H, h = unit % prm.H;
+            const int cst = it % kCumStages;
+            BM_WAIT_WARP(&bars->cum_empty[cst], ((it / kCumStages) & 1) ^ 1);
+            float* cum2 = reinterpret_cast<float*>(smem + kOffCum + cst * kCumStageBytes);
+            float *dtv = cum2 + T, *erow = cum2 + 2 * T, *wv = cum2 + 3 * T, *colf = cum2 + 4 * T;
+            const float ah = prm.a[h] * log2e;
+            const float bias = prm.dt_bias ? prm.dt_bias[h] : 0.f;
+            float d4[4], c4[4];
+            float run = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int s = i * T + lane * 4 + k;
+                float v = 0.f;
+                if (s < prm.S) {
+                    v = prm.dt[((int64_t)b * prm.S + s) * prm.H + h];
+                    if (prm.dt_bias) v = fminf(fmaxf(softplus_f32(v + bias), prm.dt_min), prm.dt_max);
+                }
+                d4[k] = v;
+                run += v * ah;
+                c4[k] = run;
+            }
+            float incl = run;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                float up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const float excl = incl - run;
+            const float cend_tile = __shfl_sync(0xffffffffu, incl, 31);
+            // end-of-32-block cumulative value: lane 8*blk+7 holds it as its inclusive total
+            const float cend_blk = __shfl_sync(0xffffffffu, incl, (lane & ~7) | 7);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int t = lane * 4 + k;
+                const float c = excl + c4[k];
+                cum2[t] = c;
+                dtv[t] = d4[k];
+                erow[t] = ex2(c);
+                wv[t] = d4[k] * ex2(cend_tile - c);
+                colf[t] = d4[k] * ex2(cend_blk - c);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->cum_full[cst]);
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ------------------------------------------------------------------ mask pass: CB -> P
+        const int q = warp & 3, t = q * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        for (int it = 0; it < total; ++it) {
+            const int st = it & 1, cst = it % kCumStages;
+            const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
+            const float *dtv = cum2 + T, *colf = cum2 + 4 * T;
+            BM_WAIT_WARP(&bars->cum_full[cst], (it / kCumStages) & 1);
+            BM_WAIT_WARP(&bars->cb_full[st], (it >> 1) & 1);
+            tc_fence_after();
+            const float ct = cum2[t];
+            const uint32_t cb = lane_addr + kColCB + st * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t out[16];
+                if (c > q) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) out[j] = 0u;
+                } else {
+                    uint32_t r[32];
+                    tmem_ld32(cb + c * 32, r);
+                    tmem_wait_ld();
+                    if (c < q) {
+                        const float rf = ex2(ct - cum2[c * 32 + 31]);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float m0 = __uint_as_float(r[2 * j]) * (rf * colf[c * 32 + 2 * j]);
+                            const float m1 = __uint_as_float(r[2 * j + 1]) * (rf * colf[c * 32 + 2 * j + 1]);
+                            out[j] = pack_bf16x2(m0, m1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int s0 = c * 32 + 2 * j, s1 = s0 + 1;
+                            // masked entries take exp2(-inf) = 0, like the reference's -inf fill before exp
+                            const float a0 = s0 <= t ? ct - cum2[s0] : -INFINITY;
+                            const float a1 = s1 <= t ? ct - cum2[s1] : -INFINITY;
+                            const float m0 = __uint_as_float(r[2 * j]) * (ex2(a0) * dtv[s0]);
+                            const float m1 = __uint_as_float(r[2 * j + 1]) * (ex2(a1) * dtv[s1]);
+                            out[j] = pack_bf16x2(m0, m1);
+                        }
+                    }
+                }
+                tmem_st16(cb + c * 16, out);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bars->p_ready[st]);
+                mbar_arrive(&bars->cum_empty[cst]);
+            }
+        }
+    } else if (warp >= 8) {
+        // ------------------------------------------------------------------ X scaling, state, epilogue
+        const int q = warp & 3, t = q * 32 + lane;  // t doubles as the state row r
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        float hst[P];
+        for (int it = 0; it < total; ++it) {
+            const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
+            const int b = unit / prm.H, h = unit % prm.H;
+            const int st = it & 1, cst = it % kCumStages;
+            const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
+            const float *erow = cum2 + 2 * T, *wv = cum2 + 3 * T;
+            unsigned char* xs = smem + kOffX + st * kPanel;
+            unsigned char* xw = smem + kOffXw;
+            unsigned char* hs = smem + kOffH;
+            unsigned char* ys = smem + kOffY;
+            const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
+            if (i == 0) {
+                // unit start: initial state -> registers -> bf16 operand tile for the first readout
+#pragma unroll
+                for (int p = 0; p < P; ++p) hst[p] = prm.h0 ? prm.h0[state_base + (int64_t)p * R + t] : 0.f;
+                if (it > 0) BM_WAIT_WARP(&bars->h_free, (it - 1) & 1);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    uint4 v;
+                    v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
+                    v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
+                    v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
+                    v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
+                    *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->h_ready);
+            }
+            if (prm.chunk_states && (i * T) % prm.Q == 0) {
+                const int n = (i * T) / prm.Q;
+                float* cs = prm.chunk_states + (((int64_t)b * prm.NC + n) * prm.H + h) * P * R;
+#pragma unroll
+                for (int p = 0; p < P; ++p) cs[(int64_t)p * R + t] = hst[p];
+            }
+            // ---- Xw = X * dt * exp(cum_end - cum)
+            BM_WAIT_WARP(&bars->ld_full[st], (it >> 1) & 1);
+            BM_WAIT_WARP(&bars->cum_full[cst], (it / kCumStages) & 1);
+            {
+                const float w = wv[t];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t off = sw128_offset(t, k);
+                    uint4 v = *reinterpret_cast<const uint4*>(xs + off);
+                    float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+                    v.x = pack_bf16x2(f0.x * w, f0.y * w);
+                    v.y = pack_bf16x2(f1.x * w, f1.y * w);
+                    v.z = pack_bf16x2(f2.x * w, f2.y * w);
+                    v.w = pack_bf16x2(f3.x * w, f3.y * w);
+                    *reinterpret_cast<uint4*>(xw + off) = v;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->xw_ready);
+            }
+            // ---- state update h <- exp(cum_end) h + S
+            BM_WAIT_WARP(&bars->s_full, it & 1);
+            tc_fence_after();
+            {
+                const float decay = erow[T - 1];
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t sv[32];
+                    tmem_ld32(lane_addr + kColS + half * 32, sv);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) hst[half * 32 + j] = fmaf(decay, hst[half * 32 + j], __uint_as_float(sv[j]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->s_empty);
+            }
+            if (i + 1 < tpu) {
+                BM_WAIT_WARP(&bars->h_free, it & 1);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    uint4 v;
+                    v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
+                    v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
+                    v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
+                    v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
+                    *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->h_ready);
+            } else {
+#pragma unroll
+                for (int p = 0; p < P; ++p) prm.h_final[state_base + (int64_t)p * R + t] = hst[p];
+            }
+            // ---- epilogue: y = Y1 + exp(cum_t) Y2 + D x
+            BM_WAIT_WARP(&bars->y_full, it & 1);
+            tc_fence_after();
+            {
+                const float e = erow[t];
+                const float dskip = prm.d ? prm.d[h] : 0.f;
+                if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has drained its Ysm rows
+                __syncwarp();
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t y1[32], y2[32];
+                    tmem_ld32(lane_addr + kColY1 + half * 32, y1);
+                    tmem_ld32(lane_addr + kColY2 + half * 32, y2);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t off = sw128_offset(t, half * 4 + k);
+                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + off);
+                        const float2 x0 = unpack_bf16x2(xv.x), x1 = unpack_bf16x2(xv.y), x2 = unpack_bf16x2(xv.z), x3 = unpack_bf16x2(xv.w);
+                        const int j = k * 8;
+                        uint4 o;
+                        o.x = pack_bf16x2(fmaf(dskip, x0.x, fmaf(e, __uint_as_float(y2[j + 0]), __uint_as_float(y1[j + 0]))),
+                                          fmaf(dskip, x0.y, fmaf(e, __uint_as_float(y2[j + 1]), __uint_as_float(y1[j + 1]))));
+                        o.y = pack_bf16x2(fmaf(dskip, x1.x, fmaf(e, __uint_as_float(y2[j + 2]), __uint_as_float(y1[j + 2]))),
+                                          fmaf(dskip, x1.y, fmaf(e, __uint_as_float(y2[j + 3]), __uint_as_float(y1[j + 3]))));
+                        o.z = pack_bf16x2(fmaf(dskip, x2.x, fmaf(e, __uint_as_float(y2[j + 4]), __uint_as_float(y1[j + 4]))),
+                                          fmaf(dskip, x2.y, fmaf(e, __uint_as_float(y2[j + 5]), __uint_as_float(y1[j + 5]))));
+                        o.w = pack_bf16x2(fmaf(dskip, x3.x, fmaf(e, __uint_as_float(y2[j + 6]), __uint_as_float(y1[j + 6]))),
+                                          fmaf(dskip, x3.y, fmaf(e, __uint_as_float(y2[j + 7]), __uint_as_float(y1[j + 7]))));
+                        *reinterpret_cast<uint4*>(ys + off) = o;
+                    }
+                }
+                tc_fence_before();
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars->y_empty);
+                    mbar_arrive(&bars->ld_empty[st]);
+                    mbar_arrive(&bars->cum_empty[cst]);
+                }
+                if (lane == 0) {
+                    // each warp stores its own 32 rows: no cross-warp barrier on this path
+                    tma_store_4d(&prm.tm_y, ys + q * 4096, 0, h, i * T + q * 32, b);
+                    tma_store_commit();
+                }
+            }
+        }
+    }
+done:
+    if (warp >= 8 && lane == 0) tma_store_wait_all<0>();
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem, 512);
+}
+
+int num_sms() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+}  // namespace
+
+const char* ssd2_why_not(const bm_ssd2_fwd_args* a) {
+    if (a->dtype != BM_DTYPE_BF16) return "activations must be bf16";
+    if (a->headdim != P) return "headdim must be 64";
+    if (a->state_rank != R) return "state_rank must be 128";
+    if (a->z != nullptr) return "fused z gate is only on the exact path";
+    if (a->chunk_states != nullptr && a->chunk_len % T != 0) return "chunk_states needs chunk_len % 128 == 0";
+    return nullptr;
+}
+
+bool ssd2_supported(const bm_ssd2_fwd_args* a) { return ssd2_why_not(a) == nullptr; }
+
+size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args*) { return 256; }  // status word only
+
+int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (workspace == nullptr || workspace_bytes < 256)
+        return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, 256 needed", workspace_bytes);
+    Params prm{};
+    const char* err = nullptr;
+    const uint64_t S = a->seqlen, H = a->nheads, G = a->ngroups, B = a->batch;
+    const uint32_t box[4] = {64, 1, (uint32_t)T, 1};
+    {
+        const uint64_t dims[4] = {(uint64_t)P, H, S, B};
+        const uint64_t strides[3] = {(uint64_t)P * 2, H * P * 2, S * H * P * 2};
+        const uint32_t box_y[4] = {64, 1, 32, 1};  // one warp's rows per store
+        if (!make_tensor_map_bf16(&prm.tm_x, a->x, 4, dims, strides, box, true, &err) ||
+            !make_tensor_map_bf16(&prm.tm_y, a->y, 4, dims, strides, box_y, true, &err))
+            return fail(BM_ERR_CUDA, "tensor map (x/y): %s", err);
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)R, G, S, B};
+        const uint64_t strides[3] = {(uint64_t)R * 2, G * R * 2, S * G * R * 2};
+        if (!make_tensor_map_bf16(&prm.tm_b, a->b, 4, dims, strides, box, true, &err) ||
+            !make_tensor_map_bf16(&prm.tm_c, a->c, 4, dims, strides, box, true, &err))
+            return fail(BM_ERR_CUDA, "tensor map (b/c): %s", err);
+    }
+    prm.dt = a->dt, prm.a = a->a, prm.d = a->d, prm.h0 = a->h0, prm.dt_bias = a->dt_bias;
+    prm.dt_min = a->dt_min, prm.dt_max = a->dt_max;
+    prm.h_final = a->h_final, prm.chunk_states = a->chunk_states;
+    prm.status = static_cast<int*>(workspace);
+    prm.B = a->batch, prm.S = a->seqlen, prm.H = a->nheads, prm.G = a->ngroups, prm.Q = a->chunk_len;
+    prm.NC = (int)cdiv(a->seqlen, a->chunk_len);
+    prm.tiles_per_unit = (int)cdiv(a->seqlen, T);
+    prm.num_units = a->batch * a->nheads;
+    {
+        cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd2_tc_kernel)");
+    }
+    if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, 256, stream), "cudaMemsetAsync(status)")) return e;
+    const int grid = prm.num_units < num_sms() ? prm.num_units : num_sms();
+    ssd2_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(prm);
+    return check_launch("ssd2_tc_kernel");
 }
 
 }  // namespace tc

@@ -126,3 +126,15 @@ extern "C" int32_t bm_ssd3_double_fwd(const bm_ssd3_fwd_args* a, void* ws, size_
     if (int32_t e = validate_ssd3(a, false)) return e;
     return exact::run(ssd3_exact_params(a, false), ws, ws_bytes, static_cast<cudaStream_t>(stream));
 }
+
+extern "C" int32_t bm_workspace_status(const void* workspace, void* stream) {
+    clear_error();
+    if (workspace == nullptr) return fail(BM_ERR_NULL_POINTER, "workspace is NULL");
+    int32_t word = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (int32_t e = check_cuda(cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)"))
+        return e;
+    if (int32_t e = check_cuda(cudaStreamSynchronize(st), "cudaStreamSynchronize")) return e;
+    if (word == BM_ERR_TIMEOUT) return fail(BM_ERR_TIMEOUT, "a bounded barrier wait inside the SSD kernel ran out");
+    return BM_OK;
+}

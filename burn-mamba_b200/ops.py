@@ -53,7 +53,7 @@ def _workspace(nbytes, device):
 
 
 def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bias=None, dt_limit=(0.0, 65504.0),
-             z=None, return_chunk_states=False):
+             z=None, return_chunk_states=False, check_status=False):
     """Mamba-2 chunked SSD forward.  x [b,s,h,p], dt [b,s,h] f32, a [h] f32, b/c [b,s,g,r], d [h] f32,
     h0 [b,h,p,r] f32 -> (y [b,s,h,p], h_final [b,h,p,r] f32[, chunk_states [b,n,h,p,r]])."""
     bsz, s, h, p = x.shape
@@ -77,6 +77,8 @@ def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bia
     nbytes = lib.bm_ssd2_fwd_workspace_bytes(C.byref(args))
     ws = _workspace(nbytes, x.device)
     check(lib.bm_ssd2_fwd(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_ssd2_fwd")
+    if check_status:  # synchronises: the tensor-core kernel's bounded waits report through the workspace
+        check(lib.bm_workspace_status(ws.data_ptr(), _stream()), "bm_ssd2_fwd (device status)")
     return (y, h_final, states) if return_chunk_states else (y, h_final)
 
 

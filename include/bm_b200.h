@@ -91,6 +91,13 @@ typedef struct {
 size_t bm_ssd2_fwd_workspace_bytes(const bm_ssd2_fwd_args* args);
 int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Device-side status of the last SSD call that used `workspace` (no counterpart in the reference, whose
+ * ops cannot time out).  The tensor-core kernels bound every wait on a barrier; a wait that gives up
+ * records BM_ERR_TIMEOUT in the first word of the workspace and the kernel returns early with
+ * unspecified outputs.  This call synchronises `stream`, reads that word and returns it (BM_OK when
+ * the kernel ran to completion, or for paths that cannot time out). */
+int32_t bm_workspace_status(const void* workspace, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Mamba-2 recurrent step: state update + readout for one token, state updated in place.
  * Replaces the body of Mamba2::step between the conv and the gated norm

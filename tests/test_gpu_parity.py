@@ -260,3 +260,59 @@ def test_angle_cumsum_and_step3_match_oracle_block(bm, m, rope_fraction):
     assert rel_l2(host(state), c["ssm"]) <= 1e-4 and rel_l2(host(k_state), c["k"]) <= 1e-4
     assert np.array_equal(host(v_state), c["v"])
     assert np.max(np.abs(np.angle(np.exp(1j * (host(angle) - c["angle"]))))) <= 1e-4
+
+
+# ------------------------------------------------------------------ Mamba-2 SSD (tensor-core path)
+@pytest.mark.parametrize("b,s,h,g,Q", [
+    (1, 128, 1, 1, 128),     # one tile
+    (1, 256, 2, 1, 256),     # one chunk = two tiles
+    (2, 512, 4, 2, 256),     # groups
+    (1, 300, 3, 3, 128),     # ragged tail (zero-filled rows, clipped store)
+    (1, 100, 2, 1, 64),      # shorter than one tile
+    (2, 1024, 8, 1, 256),
+    (3, 384, 160, 1, 256),   # more units than SMs: several units per CTA
+])
+def test_ssd2_tensor_path_matches_oracle(bm, b, s, h, g, Q):
+    cfg = inputs.ssd2_prefill(seed=200 + s, batch=b, seqlen=s, nheads=h, headdim=64, state_rank=128, ngroups=g,
+                              h0_std=0.1)
+    dt = torch.bfloat16
+    if b * s * h <= 64 * 1024:
+        y, hf = _ssd2_case(bm, cfg, Q, dt, path="tensor", check_status=True)
+    else:
+        x, bb, cc = (dev(cfg[k], dt) for k in ("x", "b", "c"))
+        y, hf = bm.ops.ssd2_fwd(x, dev(cfg["dt"]), dev(cfg["a"]), bb, cc, dev(cfg["d"]), dev(cfg["h0"]), chunk_len=Q,
+                                path="tensor", check_status=True)
+    # on-device cross-check against the exact path (same bf16 inputs, float32 arithmetic)
+    x, bb, cc = (dev(cfg[k], dt) for k in ("x", "b", "c"))
+    ye, he = bm.ops.ssd2_fwd(x, dev(cfg["dt"]), dev(cfg["a"]), bb, cc, dev(cfg["d"]), dev(cfg["h0"]), chunk_len=Q,
+                             path="exact")
+    assert rel_l2(host(y), host(ye)) <= 2e-2 and rel_l2(host(hf), host(he)) <= 2e-2
+
+
+def test_ssd2_tensor_path_chunk_states_and_fused_dt(bm):
+    cfg = inputs.ssd2_prefill(seed=31, batch=2, seqlen=768, nheads=4, headdim=64, state_rank=128, h0_std=0.1)
+    dt = torch.bfloat16
+    x, bb, cc = (q(cfg[k], dt) for k in ("x", "b", "c"))
+    _, _, want = mamba2.ssd_serial(x, cfg["dt"], cfg["a"], bb, cc, cfg["d"], cfg["h0"], 256, return_chunk_states=True)
+    y, hf, st = bm.ops.ssd2_fwd(dev(x, dt), dev(cfg["dt"]), dev(cfg["a"]), dev(bb, dt), dev(cc, dt), dev(cfg["d"]),
+                                dev(cfg["h0"]), chunk_len=256, path="tensor", return_chunk_states=True,
+                                check_status=True)
+    assert rel_l2(host(st), want) <= 2e-2
+    rng = np.random.default_rng(5)
+    raw = rng.standard_normal(cfg["dt"].shape).astype(np.float32)
+    from oracle.numerics import softplus
+    dtv = np.clip(softplus(raw + cfg["dt_bias"], "f32"), 0.0, 65504.0).astype(np.float32)
+    want_y, want_h = mamba2.ssd_serial(x, dtv, cfg["a"], bb, cc, cfg["d"], cfg["h0"], 256)
+    y, hf = bm.ops.ssd2_fwd(dev(x, dt), dev(raw), dev(cfg["a"]), dev(bb, dt), dev(cc, dt), dev(cfg["d"]),
+                            dev(cfg["h0"]), chunk_len=256, path="tensor", dt_bias=dev(cfg["dt_bias"]),
+                            check_status=True)
+    assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
+
+
+def test_ssd2_tensor_path_strong_decay_is_finite(bm):
+    """Large dt*|A| (state forgotten within a few tokens): the factored decay mask must not overflow."""
+    cfg = inputs.ssd2_prefill(seed=32, batch=1, seqlen=256, nheads=2, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["dt"] = (cfg["dt"] * 0 + 3.0).astype(np.float32)
+    cfg["a"] = np.float32([-16.0, -0.001])
+    y, hf = _ssd2_case(bm, cfg, 256, torch.bfloat16, path="tensor", check_status=True)
+    assert torch.isfinite(y.float()).all() and torch.isfinite(hf).all()
