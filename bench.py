@@ -1,0 +1,302 @@
+#!/usr/bin/env python
+"""Benchmark of the SSM hot path: Mamba-2 SSD prefill at the 2.7B layer shape.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One "step" = one pass of the Mamba-2 SSD forward (bm_ssd2_fwd) over one synthetic batch of the
+2.7B-shape prefill configuration: batch 8, L 4096, H 80, P 64, N 128, G 1, chunk 256, bf16
+activations, float32 decay/state.  `value` is tokens/s with inputs resident in HBM; `e2e` is the same
+call made with HOST buffers (pinned -> device copies of x, dt, B, C and device -> host copies of y and
+the final state inside the timed region).  With N > 1 (torchrun, one rank per GPU) every rank runs the
+same per-GPU workload -- (batch x head) units are independent, there is no data-path collective --
+and the aggregate is reported ("scaling": "weak").
+
+`--impl reference` times the CPU restatement of the reference's algorithm (oracle/csrc, C with
+pthreads over batch x head) on a bounded sample of the same configuration: the reference itself
+(Rust + un-vendored Burn) cannot be built without a Rust toolchain.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(batch=8, seqlen=4096, nheads=80, headdim=64, state_rank=128, ngroups=1, chunk_len=256)
+WORKLOAD = "mamba2_ssd_prefill_2.7B_b8_L4096_H80_P64_N128_G1_Q256"
+METRIC = "mamba2_ssd_prefill_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def algorithmic_bytes(c):
+    """x + y (bf16), B + C (bf16), dt (f32) per token, plus initial and final state (f32)."""
+    per_token = 2 * c["nheads"] * c["headdim"] * 2 + 2 * 2 * c["ngroups"] * c["state_rank"] + 4 * c["nheads"]
+    states = 2 * c["batch"] * c["nheads"] * c["headdim"] * c["state_rank"] * 4
+    return per_token * c["batch"] * c["seqlen"] + states
+
+
+def measured_peak_hbm():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([p.strip() for p in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+                for n, v in zip(names, r[2:6]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                continue
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(torch, seed, c):
+    """Seeded synthetic inputs with the configuration's distributions (host, pinned)."""
+    g = torch.Generator().manual_seed(seed)
+    b, s, h, p, r, ng = c["batch"], c["seqlen"], c["nheads"], c["headdim"], c["state_rank"], c["ngroups"]
+    x = torch.randn((b, s, h, p), generator=g).to(torch.bfloat16)
+    dt0 = torch.exp(torch.rand(h, generator=g) * (torch.log(torch.tensor(0.1)) - torch.log(torch.tensor(1e-3)))
+                    + torch.log(torch.tensor(1e-3)))
+    dt_bias = dt0 + torch.log(-torch.expm1(-dt0))
+    dt = torch.nn.functional.softplus(torch.randn((b, s, h), generator=g) + dt_bias).float()
+    a = -(torch.rand(h, generator=g) * 15.0 + 1.0)
+    bm_ = (torch.randn((b, s, ng, r), generator=g) / r ** 0.5).to(torch.bfloat16)
+    cm_ = (torch.randn((b, s, ng, r), generator=g) / r ** 0.5).to(torch.bfloat16)
+    d = torch.rand(h, generator=g)
+    out = dict(x=x, dt=dt, a=a.float(), b=bm_, c=cm_, d=d.float())
+    return {k: v.contiguous().pin_memory() for k, v in out.items()}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    bm = ge.load_package()
+    c = dict(CFG, batch=args.batch)
+    host = make_inputs(torch, 2 + rank, c)
+    devt = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+    y_host = torch.empty(host["x"].shape, dtype=torch.bfloat16).pin_memory()
+    h_host = torch.empty((c["batch"], c["nheads"], c["headdim"], c["state_rank"]), dtype=torch.float32).pin_memory()
+    torch.cuda.synchronize()
+
+    def step_resident():
+        return bm.ops.ssd2_fwd(devt["x"], devt["dt"], devt["a"], devt["b"], devt["c"], devt["d"], None,
+                               chunk_len=c["chunk_len"], path="auto")
+
+    def step_e2e():
+        t = {k: host[k].to(dev, non_blocking=True) for k in ("x", "dt", "b", "c")}
+        y, hf = bm.ops.ssd2_fwd(t["x"], t["dt"], devt["a"], t["b"], t["c"], devt["d"], None,
+                                chunk_len=c["chunk_len"], path="auto")
+        y_host.copy_(y, non_blocking=True)
+        h_host.copy_(hf, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    # device status of the tensor-core kernel (bounded waits) -- checked once, outside the timed region
+    y, hf = bm.ops.ssd2_fwd(devt["x"], devt["dt"], devt["a"], devt["b"], devt["c"], devt["d"], None,
+                            chunk_len=c["chunk_len"], path="auto", check_status=True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms = timed(step_resident, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_steps = max(1, min(args.steps, 10))
+    if args.profile:  # kernel-only run for ncu captures: no end-to-end leg, no CPU arm
+        ms_e2e = float("nan")
+    else:
+        for _ in range(2):
+            step_e2e()
+        ms_e2e = timed(step_e2e, e2e_steps)
+
+    tokens = c["batch"] * c["seqlen"]
+    ms_step = ms / args.steps
+    value = tokens * world / (ms_step * 1e-3)
+    e2e_value = tokens * world / (ms_e2e / e2e_steps * 1e-3)
+    peak, peak_src = measured_peak_hbm()
+    abytes = algorithmic_bytes(c)
+    achieved = abytes / (ms_step * 1e-3) / 1e9
+    h2d = sum(host[k].numel() * host[k].element_size() for k in ("x", "dt", "b", "c"))
+    d2h = y_host.numel() * 2 + h_host.numel() * 4
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu": dict(c), "parallelism": f"replicated_units_x{world}",
+                   "l2": "inputs larger than L2 (x + y = 671 MB per step)", "path": "tcgen05 tensor-core kernel"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)", "algorithmic_bytes": abytes,
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH},
+    }
+    if rank == 0:
+        line["cpu_baseline"] = None if args.profile else cpu_baseline(budget_s=20.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one ssd2_tc_kernel launch, from the ncu capture
+# summarised under profiles/ (None until a capture exists).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def cpu_sample(batch, nheads):
+    """A bounded sample of the benchmark configuration for the CPU arm: full sequence length, full
+    head shape, fewer (batch x head) units -- units are independent, so tokens/s scales by units."""
+    import numpy as np
+    rng = np.random.Generator(np.random.PCG64(2))
+    c = dict(CFG, batch=batch, nheads=nheads)
+    f = np.float32
+    b, s, h, p, r, g = c["batch"], c["seqlen"], c["nheads"], c["headdim"], c["state_rank"], c["ngroups"]
+    x = rng.standard_normal((b, s, h, p), dtype=f)
+    dt = np.log1p(np.exp(rng.standard_normal((b, s, h), dtype=f) - 4.0)).astype(f)
+    a = (-rng.uniform(1.0, 16.0, h)).astype(f)
+    bb = (rng.standard_normal((b, s, g, r), dtype=f) / np.sqrt(r)).astype(f)
+    cc = (rng.standard_normal((b, s, g, r), dtype=f) / np.sqrt(r)).astype(f)
+    d = rng.uniform(0.0, 1.0, h).astype(f)
+    return c, (x, dt, a, bb, cc, d)
+
+
+def cpu_baseline(budget_s=20.0, steps=1, warmup=0):
+    """Times the C restatement of the reference's serial SSD on the host cores (all of them) on a
+    sample of `units` (batch x head) problems; reported as whole-configuration tokens/s equivalents:
+    tokens/s = (sample token-heads / s) / nheads of the full configuration."""
+    from oracle import cport
+    cores = cport.max_threads()
+    # probe with one unit per core, then size the timed sample (whole waves of units) to the budget
+    c, arrs = cpu_sample(1, min(cores, CFG["nheads"]))
+    t0 = time.perf_counter()
+    cport.ssd2_serial(*arrs, None, c["chunk_len"], nthreads=cores)
+    wave_s = time.perf_counter() - t0
+    waves = int(max(1, min(budget_s / (wave_s * (steps + warmup)), CFG["batch"] * CFG["nheads"] / cores)))
+    units = waves * min(cores, CFG["nheads"])
+    heads = min(units, CFG["nheads"])
+    batch = max(1, units // heads)
+    c, arrs = cpu_sample(batch, heads)
+    for _ in range(warmup):
+        cport.ssd2_serial(*arrs, None, c["chunk_len"], nthreads=cores)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cport.ssd2_serial(*arrs, None, c["chunk_len"], nthreads=cores)
+    dt = (time.perf_counter() - t0) / steps
+    token_heads_per_s = c["batch"] * c["seqlen"] * c["nheads"] / dt
+    return {"value": token_heads_per_s / CFG["nheads"], "unit": UNIT, "cores": cores, "kind": "port",
+            "seconds_per_step": dt,
+            "sample": f"{c['batch']} x {c['nheads']} (batch x head) units of the {CFG['batch']} x {CFG['nheads']} "
+                      f"configuration at full L={c['seqlen']}, float32, C restatement of ssd_serial "
+                      f"(reference backend-flex unavailable: no Rust toolchain)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    steps, warmup = max(args.steps, 1), max(args.warmup, 0)
+    base = cpu_baseline(budget_s=90.0, steps=steps, warmup=min(warmup, 1))
+    tokens = CFG["batch"] * CFG["seqlen"]
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": min(warmup, 1), "ms_per_step": tokens / base["value"] * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu": dict(CFG), "note": "CPU arm runs on rank 0's host cores only"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=CFG["batch"],
+                    help="per-GPU batch rows (default: the benchmark configuration; smaller only for profiler captures)")
+    ap.add_argument("--profile", action="store_true", help="kernel-only run for ncu: skips the e2e and CPU legs")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
