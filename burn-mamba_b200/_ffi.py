@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbm_b200.so")
+# BM_B200_LIB selects another build of the same library (e.g. an instrumented development build)
+LIB_PATH = os.environ.get("BM_B200_LIB") or os.path.join(_HERE, "libbm_b200.so")
 
 BM_OK = 0
 BM_ERR_NULL_POINTER, BM_ERR_BAD_SHAPE, BM_ERR_BAD_ALIGNMENT, BM_ERR_UNSUPPORTED = -1, -2, -3, -4

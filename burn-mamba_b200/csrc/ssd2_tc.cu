@@ -5,15 +5,20 @@
 // T = 128 tokens, keeping the head's state [r = 128, p = 64] in registers (float32) for the whole
 // sequence, so no per-chunk state ever goes to HBM.  Per tile (reference formulas:
 // src/mamba2/ssd/serial.rs:138-506, restated with the tile as the chunk):
-//     CB   = C B^T                                   tcgen05 SS   (K1/K2)
-//     P    = bf16(CB * exp(cum_t - cum_s)[s<=t] dt_s) in TMEM     (the mask of K5)
-//     Y1   = P X            Y2 = C h^T               tcgen05 TS / SS (K5)
-//     y    = Y1 + exp(cum_t) Y2 + D x                epilogue, TMA store
-//     S    = B^T (X * dt exp(cum_end - cum))         tcgen05 SS   (K3)
-//     h   <- exp(cum_end) h + S                      registers    (K4)
-// Warp roles: warp 0 TMA loads, warp 1 MMA issue, warp 2 TMEM allocation, warp 3 decay scan of dt,
-// warps 4-7 mask pass (CB -> P), warps 8-11 X scaling, state update and epilogue.
-// Every barrier wait is bounded; a wait that gives up stores BM_ERR_TIMEOUT in the status word of the
+//     CB   = C B^T                                          tcgen05 SS   (K1/K2)
+//     P    = bf16(CB * exp(cum_t - cum_s)[s<=t] dt_s + D [s==t])  in TMEM (mask + skip of K5)
+//     Y1   = P X            Y2 = C h^T                      tcgen05 TS / SS (K5)
+//     y    = Y1 + exp(cum_t) Y2                             epilogue, TMA store
+//     S    = B^T (X * dt exp(cum_end - cum))                tcgen05 SS   (K3)
+//     h   <- exp(cum_end) h + S                             registers    (K4)
+// Two dependency chains run concurrently and are software-pipelined across tiles:
+//     scan chain   CB(i+1) | mask(i) -> Y1(i) -> epilogue(i)
+//     state chain  Xw(i+1) | S(i) -> h(i+1) -> Y2(i+1)
+// Warp roles (512 threads): warp 0 TMA loads, warp 1 MMA issue for the scan chain, warp 2 TMEM
+// allocation + MMA issue for the state chain, warp 3 decay scan of dt, warps 4-7 mask pass (CB -> P),
+// warps 8-11 X scaling and state update, warps 12-15 epilogue.  The MMA issuers poll their input
+// barriers and issue whichever GEMM is ready, so neither chain blocks the other.
+// Every wait is bounded; a wait that gives up stores BM_ERR_TIMEOUT in the status word of the
 // workspace and all roles leave their loops.
 #include "ssd2_tc.cuh"
 #include "tc_common.cuh"
@@ -26,34 +31,40 @@ namespace {
 constexpr int T = 128;        // tokens per tile
 constexpr int P = 64;         // head dim
 constexpr int R = 128;        // state rank
-constexpr int kThreads = 384;
+constexpr int kThreads = 512;
 constexpr int kCumStages = 4;
+constexpr uint32_t kPollBudget = 1u << 24;
+// Tiles whose total log2 decay |cend| stays below this use the factored mask: every factor
+// exp2(+-cend) then stays far inside the float32 / bfloat16 exponent range.
+constexpr float kFactoredMaxLog2Decay = 100.f;  // non-blocking polls of an idle issuer before it gives up (~ seconds)
 
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kPanel = 16384;               // [128 rows x 128 B]
 constexpr uint32_t kOffC = 0;                    // 2 stages x 2 panels
 constexpr uint32_t kOffB = 65536;                // 2 stages x 2 panels
 constexpr uint32_t kOffX = 131072;               // 2 stages x 1 panel
-constexpr uint32_t kOffXw = 163840;
-constexpr uint32_t kOffH = 180224;
-constexpr uint32_t kOffY = 196608;
-constexpr uint32_t kOffCum = 212992;             // kCumStages x 5 arrays x 128 floats
-constexpr uint32_t kCumStageBytes = 5 * T * 4;
+constexpr uint32_t kOffXw = 163840;              // 2 buffers x 1 panel (each reused as the y staging tile)
+constexpr uint32_t kOffH = 196608;
+constexpr uint32_t kOffCum = 212992;             // kCumStages x (5 arrays x 128 floats + flag)
+constexpr uint32_t kCumStageBytes = 5 * T * 4 + 16;  // + the tile's factored-path flag
 constexpr uint32_t kOffBar = kOffCum + kCumStages * kCumStageBytes;
 constexpr uint32_t kSmemBytes = kOffBar + 512 + 1024;  // barriers + alignment slack
-constexpr uint32_t kLoadBytes = 2 * 2 * kPanel + kPanel;  // C + B + X per tile
+constexpr uint32_t kLoadBytesCB = 4 * kPanel;
+constexpr uint32_t kLoadBytesX = kPanel;
 
 // TMEM columns
 constexpr uint32_t kColCB = 0;     // 2 buffers x 128 columns; P (bf16 pairs) aliases the first 64 of each
 constexpr uint32_t kColY1 = 256;
-constexpr uint32_t kColY2 = 320;
-constexpr uint32_t kColS = 384;
+constexpr uint32_t kColY2 = 320;   // 2 buffers x 64 columns
+constexpr uint32_t kColS = 448;
 
 struct Barriers {
-    uint64_t ld_full[2], ld_empty[2];
+    uint64_t cbld_full[2], cbld_empty[2];   // C + B tiles
+    uint64_t xld_full[2], xld_empty[2];     // X tile (later the y staging tile)
     uint64_t cum_full[kCumStages], cum_empty[kCumStages];
     uint64_t cb_full[2], p_ready[2];
-    uint64_t y_full, y_empty, h_ready, h_free, xw_ready, s_full, s_empty;
+    uint64_t y1_full, y1_empty, y2_full[2], y2_empty[2];
+    uint64_t h_ready, h_free, xw_ready[2], xw_free[2], ystage_free[2], s_full, s_empty;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -69,6 +80,7 @@ struct alignas(64) Params {
     float* h_final;
     float* chunk_states;
     int* status;
+    long long* trace;
     int B, S, H, G, Q, NC, tiles_per_unit, num_units;
 };
 
@@ -84,34 +96,114 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
 
-// Bounded wait used by single-thread roles (TMA producer, MMA issuer).
-#define BM_WAIT(bar, par)                                                        \
-    do {                                                                         \
-        if (!mbar_wait((bar), (par))) {                                          \
-            atomicExch(prm.status, (int)BM_ERR_TIMEOUT);                         \
-            *abort_flag = 1;                                                     \
-            goto done;                                                           \
-        }                                                                        \
-        if (*abort_flag) goto done;                                              \
+// Optional timeline instrumentation (development builds only, -DBM_SSD2_TRACE): CTA 0 records
+// clock64() at role milestones of its first tiles into prm.trace[role][tile][event].
+#ifdef BM_SSD2_TRACE
+#define BM_TRACE(role, it, ev)                                                                     \
+    do {                                                                                           \
+        if (blockIdx.x == 0 && (it) < 64 && lane == 0 && ((role) < 4 || (warp & 3) == 3))           \
+            prm.trace[((role) * 64 + (it)) * 4 + (ev)] = clock64();                                \
+    } while (0)
+#else
+#define BM_TRACE(role, it, ev) do { } while (0)
+#endif
+
+#define BM_ABORT()                                           \
+    do {                                                     \
+        atomicExch(prm.status, (int)BM_ERR_TIMEOUT);         \
+        *abort_flag = 1;                                     \
+        goto done;                                           \
+    } while (0)
+// Bounded wait used by single-thread roles.
+#define BM_WAIT(bar, par)                                    \
+    do {                                                     \
+        if (!mbar_wait((bar), (par))) BM_ABORT();            \
+        if (*abort_flag) goto done;                          \
     } while (0)
 // Bounded wait executed by a whole warp; the leave/stay decision is made warp-uniform so that no lane
-// is left behind at a later __syncwarp or .aligned tcgen05 instruction.
-#define BM_WAIT_WARP(bar, par)                                                   \
-    do {                                                                         \
-        const bool ok_ = mbar_wait((bar), (par));                                \
-        const bool ab_ = *abort_flag != 0;                                       \
-        if (!__all_sync(0xffffffffu, ok_ && !ab_)) {                             \
-            if (!ok_) {                                                          \
-                atomicExch(prm.status, (int)BM_ERR_TIMEOUT);                     \
-                *abort_flag = 1;                                                 \
-            }                                                                    \
-            goto done;                                                           \
-        }                                                                        \
+// is left behind at a later __syncwarp or .aligned tcgen05 instruction.  Kept out of line: the kernel
+// has many wait sites and its hot loops should stay resident in the instruction cache.
+__device__ __noinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, int* status) {
+    const bool ok = mbar_wait(bar, parity);
+    const bool ab = *abort_flag != 0;
+    if (!__all_sync(0xffffffffu, ok && !ab)) {
+        if (!ok) {
+            atomicExch(status, (int)BM_ERR_TIMEOUT);
+            *abort_flag = 1;
+        }
+        return false;
+    }
+    return true;
+}
+#define BM_WAIT_WARP(bar, par)                                            \
+    do {                                                                  \
+        if (!wait_warp((bar), (par), abort_flag, prm.status)) goto done;  \
     } while (0)
+
+// One 32-column block of the decay mask: out = bf16 pairs of P for columns [32c, 32c + 32).
+// Exact form (any decay): the kernel exp(cum_t - cum_s) dt_s is applied here.
+//   below the diagonal block:  rowfac * colf[s]   (both factors <= 1, reference = end of column block)
+//   diagonal block:            exp2(cum_t - cum_s) dt_s for s <= t, 0 above (the reference's -inf fill),
+//                              plus the skip weight D at s == t (y += D x rides along in P X)
+// Factored form (tiles whose total decay stays far inside the float32 exponent range): the whole
+// kernel factors as exp2(cum_t - cend) * [dt_s exp2(cend - cum_s)]; the column factor is already in
+// the scaled tile Xw and the row factor is applied in the epilogue, so P is just the causally masked
+// CB (plus D / dt_t on the diagonal, which the two factors turn back into D).
+__device__ __forceinline__ void mask_block(const uint32_t (&r)[32], uint32_t (&out)[16], bool factored, bool diagonal, int c,
+                                           int t, float ct, float dskip, const float* cum2, const float* dtv,
+                                           const float* colf) {
+    if (factored) {
+        if (!diagonal) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) out[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        } else {
+            const float dt_t = dtv[t];
+            const float dd = dt_t > 0.f ? dskip / dt_t : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int s0 = c * 32 + 2 * j, s1 = s0 + 1;
+                float m0 = s0 <= t ? __uint_as_float(r[2 * j]) : 0.f;
+                float m1 = s1 <= t ? __uint_as_float(r[2 * j + 1]) : 0.f;
+                if (s0 == t) m0 += dd;
+                if (s1 == t) m1 += dd;
+                out[j] = pack_bf16x2(m0, m1);
+            }
+        }
+    } else if (!diagonal) {
+        const float rf = ex2(ct - cum2[c * 32 + 31]);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float2 cf = *reinterpret_cast<const float2*>(colf + c * 32 + 2 * j);
+            out[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * (rf * cf.x), __uint_as_float(r[2 * j + 1]) * (rf * cf.y));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int s0 = c * 32 + 2 * j, s1 = s0 + 1;
+            const float2 cs = *reinterpret_cast<const float2*>(cum2 + s0);
+            const float2 ds = *reinterpret_cast<const float2*>(dtv + s0);
+            const float a0 = s0 <= t ? ct - cs.x : -INFINITY;
+            const float a1 = s1 <= t ? ct - cs.y : -INFINITY;
+            float m0 = __uint_as_float(r[2 * j]) * (ex2(a0) * ds.x);
+            float m1 = __uint_as_float(r[2 * j + 1]) * (ex2(a1) * ds.y);
+            if (s0 == t) m0 += dskip;
+            if (s1 == t) m1 += dskip;
+            out[j] = pack_bf16x2(m0, m1);
+        }
+    }
+}
 
 __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_constant__ Params prm) {
     extern __shared__ unsigned char smem_raw[];
@@ -122,20 +214,26 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
-            mbar_init(&bars->ld_full[i], 1);
-            mbar_init(&bars->ld_empty[i], 5);
+            mbar_init(&bars->cbld_full[i], 1);
+            mbar_init(&bars->cbld_empty[i], 2);   // commits of both MMA issuers
+            mbar_init(&bars->xld_full[i], 1);
+            mbar_init(&bars->xld_empty[i], 5);    // Y1 commit + 4 scaling warps
+            mbar_init(&bars->xw_free[i], 1);      // S commit: the scaled tile may be overwritten by y
+            mbar_init(&bars->ystage_free[i], 4);  // epilogue warps: their y store has drained the tile
             mbar_init(&bars->cb_full[i], 1);
             mbar_init(&bars->p_ready[i], 4);
+            mbar_init(&bars->y2_full[i], 1);
+            mbar_init(&bars->y2_empty[i], 4);
+            mbar_init(&bars->xw_ready[i], 4);
         }
         for (int i = 0; i < kCumStages; ++i) {
             mbar_init(&bars->cum_full[i], 1);
-            mbar_init(&bars->cum_empty[i], 8);
+            mbar_init(&bars->cum_empty[i], 13);   // 12 consumer warps + the scan-chain MMA issuer
         }
-        mbar_init(&bars->y_full, 1);
-        mbar_init(&bars->y_empty, 4);
+        mbar_init(&bars->y1_full, 1);
+        mbar_init(&bars->y1_empty, 4);
         mbar_init(&bars->h_ready, 4);
         mbar_init(&bars->h_free, 1);
-        mbar_init(&bars->xw_ready, 4);
         mbar_init(&bars->s_full, 1);
         mbar_init(&bars->s_empty, 4);
         bars->abort_flag = 0;
@@ -155,6 +253,8 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
     for (int u = blockIdx.x; u < prm.num_units; u += gridDim.x) ++my_units;
     const int total = my_units * tpu;
     const int hpg = prm.H / prm.G;
+    const uint32_t c_base = smem_u32(smem + kOffC), b_base = smem_u32(smem + kOffB);
+    const uint32_t x_base = smem_u32(smem + kOffX), xw_base = smem_u32(smem + kOffXw), h_base = smem_u32(smem + kOffH);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -163,76 +263,163 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             tma_prefetch_desc(&prm.tm_b);
             tma_prefetch_desc(&prm.tm_c);
             tma_prefetch_desc(&prm.tm_y);
-            for (int it = 0; it < total; ++it) {
-                const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
-                const int b = unit / prm.H, h = unit % prm.H, g = h / hpg;
-                const int st = it & 1, s0 = i * T;
-                BM_WAIT(&bars->ld_empty[st], ((it >> 1) & 1) ^ 1);
-                mbar_expect_tx(&bars->ld_full[st], kLoadBytes);
-                unsigned char* cs = smem + kOffC + st * 2 * kPanel;
-                unsigned char* bs = smem + kOffB + st * 2 * kPanel;
-                tma_load_4d(cs, &prm.tm_c, &bars->ld_full[st], 0, g, s0, b);
-                tma_load_4d(cs + kPanel, &prm.tm_c, &bars->ld_full[st], 64, g, s0, b);
-                tma_load_4d(bs, &prm.tm_b, &bars->ld_full[st], 0, g, s0, b);
-                tma_load_4d(bs + kPanel, &prm.tm_b, &bars->ld_full[st], 64, g, s0, b);
-                tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->ld_full[st], 0, h, s0, b);
+            // two independent load streams (C + B tiles, X tiles), each as far ahead as its ring allows
+            int cb_next = 0, x_next = 0;
+            uint32_t idle = 0;
+            while (cb_next < total || x_next < total) {
+                bool progressed = false;
+                if (cb_next < total && mbar_test(&bars->cbld_empty[cb_next & 1], ((cb_next >> 1) & 1) ^ 1)) {
+                    const int unit = blockIdx.x + (cb_next / tpu) * gridDim.x, i = cb_next % tpu;
+                    const int b = unit / prm.H, g = (unit % prm.H) / hpg;
+                    const int st = cb_next & 1, s0 = i * T;
+                    BM_TRACE(0, cb_next, 0);
+                    mbar_expect_tx(&bars->cbld_full[st], kLoadBytesCB);
+                    unsigned char* cs = smem + kOffC + st * 2 * kPanel;
+                    unsigned char* bs = smem + kOffB + st * 2 * kPanel;
+                    tma_load_4d(cs, &prm.tm_c, &bars->cbld_full[st], 0, g, s0, b);
+                    tma_load_4d(cs + kPanel, &prm.tm_c, &bars->cbld_full[st], 64, g, s0, b);
+                    tma_load_4d(bs, &prm.tm_b, &bars->cbld_full[st], 0, g, s0, b);
+                    tma_load_4d(bs + kPanel, &prm.tm_b, &bars->cbld_full[st], 64, g, s0, b);
+                    ++cb_next;
+                    progressed = true;
+                }
+                if (x_next < total && mbar_test(&bars->xld_empty[x_next & 1], ((x_next >> 1) & 1) ^ 1)) {
+                    const int unit = blockIdx.x + (x_next / tpu) * gridDim.x, i = x_next % tpu;
+                    const int b = unit / prm.H, h = unit % prm.H;
+                    const int st = x_next & 1;
+                    BM_TRACE(0, x_next, 1);
+                    mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
+                    tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, i * T, b);
+                    ++x_next;
+                    progressed = true;
+                }
+                if (progressed) idle = 0;
+                else {
+                    if (++idle > kPollBudget) BM_ABORT();
+                    __nanosleep(64);  // keep the idle poller off the issue ports and the shared-memory pipe
+                }
+                if (*abort_flag) goto done;
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0 && total > 0) {
+        // ------------------------------------------------------------------ MMA issuer, scan chain
+        // Two job streams, CB(i) = C B^T and Y1(i) = P X; each is issued as soon as its inputs are
+        // ready.  CB(i) reuses the TMEM buffer of P(i-2), so it may run at most one tile ahead of Y1.
+        if (lane == 0) {
             const uint32_t id_cb = umma_idesc_bf16(128, 128, false, false);
             const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
+            int cb_next = 0, y_next = 0;
+#ifdef BM_SSD2_TRACE
+            int cb_seen = 0;
+#endif
+            uint32_t idle = 0;
+            while (y_next < total) {
+                bool progressed = false;
+                if (cb_next < total && cb_next <= y_next + 1) {
+                    const int st = cb_next & 1;
+                    if (mbar_test(&bars->cbld_full[st], (cb_next >> 1) & 1)) {
+                        BM_TRACE(1, cb_next, 0);
+                        const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
+#pragma unroll 1
+                        for (int k = 0; k < 8; ++k) {
+                            const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                            umma_ss(tmem + kColCB + st * 128, umma_desc_kmajor(cs + off), umma_desc_kmajor(bs + off), id_cb, k > 0);
+                        }
+                        umma_commit(&bars->cb_full[st]);
+                        umma_commit(&bars->cbld_empty[st]);
+                        ++cb_next;
+                        progressed = true;
+                    }
+                }
+                if (y_next < cb_next) {
+                    const int st = y_next & 1, cst = y_next % kCumStages;
+                    if (mbar_test(&bars->p_ready[st], (y_next >> 1) & 1) && mbar_test(&bars->y1_empty, (y_next & 1) ^ 1) &&
+                        mbar_test(&bars->xld_full[st], (y_next >> 1) & 1) && mbar_test(&bars->xw_ready[st], (y_next >> 1) & 1) &&
+                        mbar_test(&bars->cum_full[cst], (y_next / kCumStages) & 1)) {
+                        BM_TRACE(1, y_next, 1);
+                        tc_fence_after();
+                        // factored tiles multiply by the scaled tile Xw, exact tiles by X itself
+                        const float* flag = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 5 * T;
+                        const bool factored = *reinterpret_cast<const volatile float*>(flag) != 0.f;
+                        mbar_arrive(&bars->cum_empty[cst]);
+                        const uint32_t xs = factored ? xw_base + st * kPanel : x_base + st * kPanel;
+#pragma unroll 1
+                        for (int k = 0; k < 8; ++k)
+                            umma_ts(tmem + kColY1, tmem + kColCB + st * 128 + k * 8, umma_desc_mnmajor(xs + k * 2048, kPanel), id_kmn, k > 0);
+                        umma_commit(&bars->y1_full);
+                        umma_commit(&bars->xld_empty[st]);
+                        ++y_next;
+                        progressed = true;
+                    }
+                }
+#ifdef BM_SSD2_TRACE
+                if (cb_seen < cb_next && mbar_test(&bars->cb_full[cb_seen & 1], (cb_seen >> 1) & 1)) {
+                    BM_TRACE(1, cb_seen, 2);
+                    ++cb_seen;
+                }
+#endif
+                if (progressed) idle = 0;
+                else {
+                    if (++idle > kPollBudget) BM_ABORT();
+                    __nanosleep(64);  // keep the idle poller off the issue ports and the shared-memory pipe
+                }
+                if (*abort_flag) goto done;
+            }
+        }
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ MMA issuer, state chain
+        // Two job streams, Y2(i) = C h^T and S(i) = B^T Xw; issued as their inputs become ready.
+        if (lane == 0) {
+            const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
             const uint32_t id_mnmn = umma_idesc_bf16(128, 64, true, true);
-            const uint32_t c_base = smem_u32(smem + kOffC), b_base = smem_u32(smem + kOffB);
-            const uint32_t x_base = smem_u32(smem + kOffX), xw_base = smem_u32(smem + kOffXw), h_base = smem_u32(smem + kOffH);
-            auto mma_cb = [&](int it) {
-                const int st = it & 1;
-                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                    umma_ss(tmem + kColCB + st * 128, umma_desc_kmajor(cs + off), umma_desc_kmajor(bs + off), id_cb, k > 0);
+            int y2_next = 0, s_next = 0;
+            uint32_t idle = 0;
+            while (y2_next < total || s_next < total) {
+                bool progressed = false;
+                if (s_next < total) {
+                    const int st = s_next & 1;
+                    if (mbar_test(&bars->cbld_full[st], (s_next >> 1) & 1) && mbar_test(&bars->xw_ready[st], (s_next >> 1) & 1) &&
+                        mbar_test(&bars->s_empty, (s_next & 1) ^ 1)) {
+                        BM_TRACE(2, s_next, 1);
+                        tc_fence_after();
+                        const uint32_t bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
+#pragma unroll 1
+                        for (int k = 0; k < 8; ++k)
+                            umma_ss(tmem + kColS, umma_desc_mnmajor(bs + k * 2048, kPanel), umma_desc_mnmajor(xw + k * 2048, kPanel),
+                                    id_mnmn, k > 0);
+                        umma_commit(&bars->s_full);
+                        umma_commit(&bars->xw_free[st]);
+                        // the later of the tile's two GEMMs releases the C / B stage
+                        if (y2_next > s_next) umma_commit(&bars->cbld_empty[st]);
+                        ++s_next;
+                        progressed = true;
+                    }
                 }
-                umma_commit(&bars->cb_full[st]);
-            };
-            BM_WAIT(&bars->ld_full[0], 0);
-            mma_cb(0);
-            for (int it = 0; it < total; ++it) {
-                const int st = it & 1;
-                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel, xs = x_base + st * kPanel;
-                // Y2 = C . h^T
-                BM_WAIT(&bars->h_ready, it & 1);
-                BM_WAIT(&bars->y_empty, (it & 1) ^ 1);
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                    umma_ss(tmem + kColY2, umma_desc_kmajor(cs + off), umma_desc_mnmajor(h_base + k * 2048, kPanel), id_kmn, k > 0);
+                if (y2_next < total) {
+                    const int st = y2_next & 1;
+                    if (mbar_test(&bars->cbld_full[st], (y2_next >> 1) & 1) && mbar_test(&bars->h_ready, y2_next & 1) &&
+                        mbar_test(&bars->y2_empty[st], ((y2_next >> 1) & 1) ^ 1)) {
+                        BM_TRACE(2, y2_next, 0);
+                        tc_fence_after();
+                        const uint32_t cs = c_base + st * 2 * kPanel;
+#pragma unroll 1
+                        for (int k = 0; k < 8; ++k) {
+                            const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                            umma_ss(tmem + kColY2 + st * 64, umma_desc_kmajor(cs + off), umma_desc_mnmajor(h_base + k * 2048, kPanel), id_kmn, k > 0);
+                        }
+                        umma_commit(&bars->y2_full[st]);
+                        umma_commit(&bars->h_free);
+                        if (s_next > y2_next) umma_commit(&bars->cbld_empty[st]);
+                        ++y2_next;
+                        progressed = true;
+                    }
                 }
-                umma_commit(&bars->h_free);
-                // S = B^T . Xw
-                BM_WAIT(&bars->xw_ready, it & 1);
-                BM_WAIT(&bars->s_empty, (it & 1) ^ 1);
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    umma_ss(tmem + kColS, umma_desc_mnmajor(bs + k * 2048, kPanel), umma_desc_mnmajor(xw_base + k * 2048, kPanel),
-                            id_mnmn, k > 0);
-                umma_commit(&bars->s_full);
-                // CB of the next tile (keeps the tensor pipe busy while the mask pass of this tile runs)
-                if (it + 1 < total) {
-                    BM_WAIT(&bars->ld_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
-                    mma_cb(it + 1);
+                if (progressed) idle = 0;
+                else {
+                    if (++idle > kPollBudget) BM_ABORT();
+                    __nanosleep(64);  // keep the idle poller off the issue ports and the shared-memory pipe
                 }
-                // Y1 = P . X
-                BM_WAIT(&bars->p_ready[st], (it >> 1) & 1);
-                tc_fence_after();
-#pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    umma_ts(tmem + kColY1, tmem + kColCB + st * 128 + k * 8, umma_desc_mnmajor(xs + k * 2048, kPanel), id_kmn, k > 0);
-                umma_commit(&bars->y_full);
-                umma_commit(&bars->ld_empty[st]);
+                if (*abort_flag) goto done;
             }
         }
     } else if (warp == 3) {
@@ -282,208 +469,231 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 wv[t] = d4[k] * ex2(cend_tile - c);
                 colf[t] = d4[k] * ex2(cend_blk - c);
             }
+            if (lane == 0) cum2[5 * T] = fabsf(cend_tile) <= kFactoredMaxLog2Decay ? 1.f : 0.f;
             __syncwarp();
+            BM_TRACE(3, it, 0);
             if (lane == 0) mbar_arrive(&bars->cum_full[cst]);
         }
-    } else if (warp >= 4 && warp < 8) {
+    } else if (warp < 8) {
         // ------------------------------------------------------------------ mask pass: CB -> P
         const int q = warp & 3, t = q * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
         for (int it = 0; it < total; ++it) {
+            const int unit = blockIdx.x + (it / tpu) * gridDim.x;
             const int st = it & 1, cst = it % kCumStages;
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + T, *colf = cum2 + 4 * T;
+            const float dskip = prm.d ? prm.d[unit % prm.H] : 0.f;
+            BM_TRACE(4, it, 0);
             BM_WAIT_WARP(&bars->cum_full[cst], (it / kCumStages) & 1);
             BM_WAIT_WARP(&bars->cb_full[st], (it >> 1) & 1);
+            BM_TRACE(4, it, 1);
             tc_fence_after();
             const float ct = cum2[t];
+            const bool factored = cum2[5 * T] != 0.f;
             const uint32_t cb = lane_addr + kColCB + st * 128;
-#pragma unroll
+            // blocks 0..q carry data (block q holds the diagonal), blocks above are zero
+#pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t out[16];
-                if (c > q) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) out[j] = 0u;
-                } else {
+                if (c <= q) {
                     uint32_t r[32];
                     tmem_ld32(cb + c * 32, r);
                     tmem_wait_ld();
-                    if (c < q) {
-                        const float rf = ex2(ct - cum2[c * 32 + 31]);
+                    mask_block(r, out, factored, c == q, c, t, ct, dskip, cum2, dtv, colf);
+                } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const float m0 = __uint_as_float(r[2 * j]) * (rf * colf[c * 32 + 2 * j]);
-                            const float m1 = __uint_as_float(r[2 * j + 1]) * (rf * colf[c * 32 + 2 * j + 1]);
-                            out[j] = pack_bf16x2(m0, m1);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int s0 = c * 32 + 2 * j, s1 = s0 + 1;
-                            // masked entries take exp2(-inf) = 0, like the reference's -inf fill before exp
-                            const float a0 = s0 <= t ? ct - cum2[s0] : -INFINITY;
-                            const float a1 = s1 <= t ? ct - cum2[s1] : -INFINITY;
-                            const float m0 = __uint_as_float(r[2 * j]) * (ex2(a0) * dtv[s0]);
-                            const float m1 = __uint_as_float(r[2 * j + 1]) * (ex2(a1) * dtv[s1]);
-                            out[j] = pack_bf16x2(m0, m1);
-                        }
-                    }
+                    for (int j = 0; j < 16; ++j) out[j] = 0u;
                 }
                 tmem_st16(cb + c * 16, out);
             }
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
+            BM_TRACE(4, it, 3);
             if (lane == 0) {
                 mbar_arrive(&bars->p_ready[st]);
                 mbar_arrive(&bars->cum_empty[cst]);
             }
         }
-    } else if (warp >= 8) {
-        // ------------------------------------------------------------------ X scaling, state, epilogue
+    } else if (warp < 12) {
+        // ------------------------------------------------------------------ X scaling and state update
         const int q = warp & 3, t = q * 32 + lane;  // t doubles as the state row r
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        unsigned char* hs = smem + kOffH;
         float hst[P];
+        auto scale_x = [&](int it) {
+            // Xw = X * dt * exp(cum_end - cum) for tile `it` (rows keep their swizzled positions)
+            const int st = it & 1, cst = it % kCumStages;
+            const float* wv = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 3 * T;
+            const unsigned char* xs = smem + kOffX + st * kPanel;
+            unsigned char* xw = smem + kOffXw + st * kPanel;
+            const float w = wv[t];
+#pragma unroll 2
+            for (int k = 0; k < 8; ++k) {
+                const uint32_t off = sw128_offset(t, k);
+                uint4 v = *reinterpret_cast<const uint4*>(xs + off);
+                float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+                v.x = pack_bf16x2(f0.x * w, f0.y * w);
+                v.y = pack_bf16x2(f1.x * w, f1.y * w);
+                v.z = pack_bf16x2(f2.x * w, f2.y * w);
+                v.w = pack_bf16x2(f3.x * w, f3.y * w);
+                *reinterpret_cast<uint4*>(xw + off) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bars->xw_ready[st]);
+                mbar_arrive(&bars->xld_empty[st]);
+            }
+        };
+        auto publish_state = [&]() {
+            // bf16 copy of the state as the MN-major B operand of the readout GEMM
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                uint4 v;
+                v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
+                v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
+                v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
+                v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
+                *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->h_ready);
+        };
+        // Iteration `it` publishes the state entering tile it, scales the X tile of tile it+1 (one
+        // tile ahead, so S(it+1) can be issued early) and then folds S(it) into the state.
+        for (int it = -1; it < total; ++it) {
+            const int itc = it < 0 ? 0 : it;
+            const int unit = blockIdx.x + (itc / tpu) * gridDim.x, i = itc % tpu;
+            const int b = unit / prm.H, h = unit % prm.H;
+            const int cst = itc % kCumStages;
+            const float* erow = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 2 * T;
+            const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
+            if (it >= 0) {
+                if (i == 0) {
+                    // unit start: initial state -> registers
+#pragma unroll
+                    for (int p = 0; p < P; ++p) hst[p] = prm.h0 ? prm.h0[state_base + (int64_t)p * R + t] : 0.f;
+                }
+                if (prm.chunk_states && (i * T) % prm.Q == 0) {
+                    const int n = (i * T) / prm.Q;
+                    float* cs = prm.chunk_states + (((int64_t)b * prm.NC + n) * prm.H + h) * P * R;
+#pragma unroll
+                    for (int p = 0; p < P; ++p) cs[(int64_t)p * R + t] = hst[p];
+                }
+                // the operand tile is free once Y2(it-1) has completed
+                if (it > 0) BM_WAIT_WARP(&bars->h_free, (it - 1) & 1);
+                publish_state();
+                BM_TRACE(5, it, 3);
+            }
+            if (it + 1 < total) {
+                // scaled X of the next tile: its buffer was last read by S(it-1) (observed through
+                // s_full in the previous iteration) and, as y staging tile, by the store of tile it-1
+                BM_WAIT_WARP(&bars->xld_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
+                BM_WAIT_WARP(&bars->cum_full[(it + 1) % kCumStages], ((it + 1) / kCumStages) & 1);
+                BM_WAIT_WARP(&bars->ystage_free[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
+                BM_TRACE(5, itc, 0);
+                scale_x(it + 1);
+                BM_TRACE(3, itc, 1);
+            }
+            if (it >= 0) {
+                // state update h <- exp(cum_end) h + S
+                BM_WAIT_WARP(&bars->s_full, it & 1);
+                BM_TRACE(5, it, 1);
+                tc_fence_after();
+                const float decay = erow[T - 1];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t sv[16];
+                    tmem_ld16(lane_addr + kColS + c * 16, sv);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) hst[c * 16 + j] = fmaf(decay, hst[c * 16 + j], __uint_as_float(sv[j]));
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars->s_empty);
+                    mbar_arrive(&bars->cum_empty[cst]);
+                }
+                BM_TRACE(5, it, 2);
+                if (i + 1 == tpu) {
+#pragma unroll
+                    for (int p = 0; p < P; ++p) prm.h_final[state_base + (int64_t)p * R + t] = hst[p];
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        // y = Y1 + exp(cum_t) Y2, staged in the scaled-X tile of the same parity (dead once S(it) has
+        // completed) and written with one TMA store per warp (its own 32 rows).
+        const int q = warp & 3, t = q * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
         for (int it = 0; it < total; ++it) {
             const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
             const int b = unit / prm.H, h = unit % prm.H;
             const int st = it & 1, cst = it % kCumStages;
-            const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
-            const float *erow = cum2 + 2 * T, *wv = cum2 + 3 * T;
-            unsigned char* xs = smem + kOffX + st * kPanel;
-            unsigned char* xw = smem + kOffXw;
-            unsigned char* hs = smem + kOffH;
-            unsigned char* ys = smem + kOffY;
-            const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
-            if (i == 0) {
-                // unit start: initial state -> registers -> bf16 operand tile for the first readout
-#pragma unroll
-                for (int p = 0; p < P; ++p) hst[p] = prm.h0 ? prm.h0[state_base + (int64_t)p * R + t] : 0.f;
-                if (it > 0) BM_WAIT_WARP(&bars->h_free, (it - 1) & 1);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    uint4 v;
-                    v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
-                    v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
-                    v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
-                    v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
-                    *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->h_ready);
-            }
-            if (prm.chunk_states && (i * T) % prm.Q == 0) {
-                const int n = (i * T) / prm.Q;
-                float* cs = prm.chunk_states + (((int64_t)b * prm.NC + n) * prm.H + h) * P * R;
-#pragma unroll
-                for (int p = 0; p < P; ++p) cs[(int64_t)p * R + t] = hst[p];
-            }
-            // ---- Xw = X * dt * exp(cum_end - cum)
-            BM_WAIT_WARP(&bars->ld_full[st], (it >> 1) & 1);
+            const float* erow = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 2 * T;
+            unsigned char* ys = smem + kOffXw + st * kPanel;
             BM_WAIT_WARP(&bars->cum_full[cst], (it / kCumStages) & 1);
-            {
-                const float w = wv[t];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t off = sw128_offset(t, k);
-                    uint4 v = *reinterpret_cast<const uint4*>(xs + off);
-                    float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-                    v.x = pack_bf16x2(f0.x * w, f0.y * w);
-                    v.y = pack_bf16x2(f1.x * w, f1.y * w);
-                    v.z = pack_bf16x2(f2.x * w, f2.y * w);
-                    v.w = pack_bf16x2(f3.x * w, f3.y * w);
-                    *reinterpret_cast<uint4*>(xw + off) = v;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->xw_ready);
-            }
-            // ---- state update h <- exp(cum_end) h + S
-            BM_WAIT_WARP(&bars->s_full, it & 1);
+            const float e = erow[t];
+            // row factor of the factored mask: exp2(cum_t - cend); 1 for exact tiles
+            const float* cum2 = erow - 2 * T;
+            const float e1 = cum2[5 * T] != 0.f ? ex2(cum2[t] - cum2[T - 1]) : 1.f;
+            BM_WAIT_WARP(&bars->xw_free[st], (it >> 1) & 1);
+            BM_WAIT_WARP(&bars->y2_full[st], (it >> 1) & 1);
+            BM_WAIT_WARP(&bars->y1_full, it & 1);
+            BM_TRACE(6, it, 0);
             tc_fence_after();
-            {
-                const float decay = erow[T - 1];
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t sv[32];
-                    tmem_ld32(lane_addr + kColS + half * 32, sv);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) hst[half * 32 + j] = fmaf(decay, hst[half * 32 + j], __uint_as_float(sv[j]));
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->s_empty);
-            }
-            if (i + 1 < tpu) {
-                BM_WAIT_WARP(&bars->h_free, it & 1);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    uint4 v;
-                    v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
-                    v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
-                    v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
-                    v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
-                    *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->h_ready);
-            } else {
-#pragma unroll
-                for (int p = 0; p < P; ++p) prm.h_final[state_base + (int64_t)p * R + t] = hst[p];
-            }
-            // ---- epilogue: y = Y1 + exp(cum_t) Y2 + D x
-            BM_WAIT_WARP(&bars->y_full, it & 1);
-            tc_fence_after();
-            {
-                const float e = erow[t];
-                const float dskip = prm.d ? prm.d[h] : 0.f;
-                if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has drained its Ysm rows
-                __syncwarp();
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t y1[32], y2[32];
-                    tmem_ld32(lane_addr + kColY1 + half * 32, y1);
-                    tmem_ld32(lane_addr + kColY2 + half * 32, y2);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const uint32_t off = sw128_offset(t, half * 4 + k);
-                        const uint4 xv = *reinterpret_cast<const uint4*>(xs + off);
-                        const float2 x0 = unpack_bf16x2(xv.x), x1 = unpack_bf16x2(xv.y), x2 = unpack_bf16x2(xv.z), x3 = unpack_bf16x2(xv.w);
-                        const int j = k * 8;
-                        uint4 o;
-                        o.x = pack_bf16x2(fmaf(dskip, x0.x, fmaf(e, __uint_as_float(y2[j + 0]), __uint_as_float(y1[j + 0]))),
-                                          fmaf(dskip, x0.y, fmaf(e, __uint_as_float(y2[j + 1]), __uint_as_float(y1[j + 1]))));
-                        o.y = pack_bf16x2(fmaf(dskip, x1.x, fmaf(e, __uint_as_float(y2[j + 2]), __uint_as_float(y1[j + 2]))),
-                                          fmaf(dskip, x1.y, fmaf(e, __uint_as_float(y2[j + 3]), __uint_as_float(y1[j + 3]))));
-                        o.z = pack_bf16x2(fmaf(dskip, x2.x, fmaf(e, __uint_as_float(y2[j + 4]), __uint_as_float(y1[j + 4]))),
-                                          fmaf(dskip, x2.y, fmaf(e, __uint_as_float(y2[j + 5]), __uint_as_float(y1[j + 5]))));
-                        o.w = pack_bf16x2(fmaf(dskip, x3.x, fmaf(e, __uint_as_float(y2[j + 6]), __uint_as_float(y1[j + 6]))),
-                                          fmaf(dskip, x3.y, fmaf(e, __uint_as_float(y2[j + 7]), __uint_as_float(y1[j + 7]))));
-                        *reinterpret_cast<uint4*>(ys + off) = o;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                uint32_t y1[32], y2[32];
+                tmem_ld32(lane_addr + kColY1 + half * 32, y1);
+                tmem_ld32(lane_addr + kColY2 + st * 64 + half * 32, y2);
+                tmem_wait_ld();
+                if (half == 1) {
+                    // both accumulators are in registers: release them to the MMA issuers
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(&bars->y1_empty);
+                        mbar_arrive(&bars->y2_empty[st]);
                     }
                 }
-                tc_fence_before();
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&bars->y_empty);
-                    mbar_arrive(&bars->ld_empty[st]);
-                    mbar_arrive(&bars->cum_empty[cst]);
-                }
-                if (lane == 0) {
-                    // each warp stores its own 32 rows: no cross-warp barrier on this path
-                    tma_store_4d(&prm.tm_y, ys + q * 4096, 0, h, i * T + q * 32, b);
-                    tma_store_commit();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int j = k * 8;
+                    uint4 o;
+                    o.x = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 0]), e1 * __uint_as_float(y1[j + 0])),
+                                      fmaf(e, __uint_as_float(y2[j + 1]), e1 * __uint_as_float(y1[j + 1])));
+                    o.y = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 2]), e1 * __uint_as_float(y1[j + 2])),
+                                      fmaf(e, __uint_as_float(y2[j + 3]), e1 * __uint_as_float(y1[j + 3])));
+                    o.z = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 4]), e1 * __uint_as_float(y1[j + 4])),
+                                      fmaf(e, __uint_as_float(y2[j + 5]), e1 * __uint_as_float(y1[j + 5])));
+                    o.w = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 6]), e1 * __uint_as_float(y1[j + 6])),
+                                      fmaf(e, __uint_as_float(y2[j + 7]), e1 * __uint_as_float(y1[j + 7])));
+                    *reinterpret_cast<uint4*>(ys + sw128_offset(t, half * 4 + k)) = o;
                 }
             }
+            fence_proxy_async_smem();
+            __syncwarp();
+            BM_TRACE(6, it, 1);
+            if (lane == 0) {
+                tma_store_4d(&prm.tm_y, ys + q * 4096, 0, h, i * T + q * 32, b);
+                tma_store_commit();
+                mbar_arrive(&bars->cum_empty[cst]);
+                BM_TRACE(3, it, 2);
+                tma_store_wait_read<0>();
+                mbar_arrive(&bars->ystage_free[st]);
+            }
+            __syncwarp();
+            BM_TRACE(6, it, 2);
         }
     }
 done:
-    if (warp >= 8 && lane == 0) tma_store_wait_all<0>();
+    if (warp >= 12 && lane == 0) tma_store_wait_all<0>();
     tc_fence_before();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tmem, 512);
@@ -513,11 +723,12 @@ const char* ssd2_why_not(const bm_ssd2_fwd_args* a) {
 
 bool ssd2_supported(const bm_ssd2_fwd_args* a) { return ssd2_why_not(a) == nullptr; }
 
-size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args*) { return 256; }  // status word only
+size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args*) { return 256 + 7 * 64 * 4 * 8; }  // status word (+ trace area of development builds)
 
 int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
-    if (workspace == nullptr || workspace_bytes < 256)
-        return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, 256 needed", workspace_bytes);
+    if (workspace == nullptr || workspace_bytes < ssd2_workspace_bytes(a))
+        return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes,
+                    ssd2_workspace_bytes(a));
     Params prm{};
     const char* err = nullptr;
     const uint64_t S = a->seqlen, H = a->nheads, G = a->ngroups, B = a->batch;
@@ -525,7 +736,7 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     {
         const uint64_t dims[4] = {(uint64_t)P, H, S, B};
         const uint64_t strides[3] = {(uint64_t)P * 2, H * P * 2, S * H * P * 2};
-        const uint32_t box_y[4] = {64, 1, 32, 1};  // one warp's rows per store
+        const uint32_t box_y[4] = {64, 1, 32, 1};  // one epilogue warp's rows per store
         if (!make_tensor_map_bf16(&prm.tm_x, a->x, 4, dims, strides, box, true, &err) ||
             !make_tensor_map_bf16(&prm.tm_y, a->y, 4, dims, strides, box_y, true, &err))
             return fail(BM_ERR_CUDA, "tensor map (x/y): %s", err);
@@ -541,6 +752,7 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     prm.dt_min = a->dt_min, prm.dt_max = a->dt_max;
     prm.h_final = a->h_final, prm.chunk_states = a->chunk_states;
     prm.status = static_cast<int*>(workspace);
+    prm.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256);
     prm.B = a->batch, prm.S = a->seqlen, prm.H = a->nheads, prm.G = a->ngroups, prm.Q = a->chunk_len;
     prm.NC = (int)cdiv(a->seqlen, a->chunk_len);
     prm.tiles_per_unit = (int)cdiv(a->seqlen, T);

@@ -48,6 +48,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking test of a phase (try_wait may suspend the thread for a hardware-defined time; pollers
+// that watch several barriers must use this one).
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: ~kWaitBudget polls (each try_wait itself blocks for a short hardware-defined time).
 // Returns false when the budget ran out; the caller must then bail out through its error path.
 constexpr uint32_t kWaitBudget = 1u << 22;
