@@ -16,8 +16,7 @@
 //     state chain  Xw(i+1) | S(i) -> h(i+1) -> Y2(i+1)
 // Warp roles (512 threads): warp 0 TMA loads, warp 1 MMA issue for the scan chain, warp 2 TMEM
 // allocation + MMA issue for the state chain, warp 3 decay scan of dt, warps 4-7 mask pass (CB -> P),
-// warps 8-11 X scaling and state update, warps 12-15 epilogue.  The MMA issuers poll their input
-// barriers and issue whichever GEMM is ready, so neither chain blocks the other.
+// warps 8-11 X scaling and state update, warps 12-15 epilogue.
 // Every wait is bounded; a wait that gives up stores BM_ERR_TIMEOUT in the status word of the
 // workspace and all roles leave their loops.
 #include "ssd2_tc.cuh"
@@ -263,163 +262,102 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             tma_prefetch_desc(&prm.tm_b);
             tma_prefetch_desc(&prm.tm_c);
             tma_prefetch_desc(&prm.tm_y);
-            // two independent load streams (C + B tiles, X tiles), each as far ahead as its ring allows
-            int cb_next = 0, x_next = 0;
-            uint32_t idle = 0;
-            while (cb_next < total || x_next < total) {
-                bool progressed = false;
-                if (cb_next < total && mbar_test(&bars->cbld_empty[cb_next & 1], ((cb_next >> 1) & 1) ^ 1)) {
-                    const int unit = blockIdx.x + (cb_next / tpu) * gridDim.x, i = cb_next % tpu;
-                    const int b = unit / prm.H, g = (unit % prm.H) / hpg;
-                    const int st = cb_next & 1, s0 = i * T;
-                    BM_TRACE(0, cb_next, 0);
-                    mbar_expect_tx(&bars->cbld_full[st], kLoadBytesCB);
-                    unsigned char* cs = smem + kOffC + st * 2 * kPanel;
-                    unsigned char* bs = smem + kOffB + st * 2 * kPanel;
-                    tma_load_4d(cs, &prm.tm_c, &bars->cbld_full[st], 0, g, s0, b);
-                    tma_load_4d(cs + kPanel, &prm.tm_c, &bars->cbld_full[st], 64, g, s0, b);
-                    tma_load_4d(bs, &prm.tm_b, &bars->cbld_full[st], 0, g, s0, b);
-                    tma_load_4d(bs + kPanel, &prm.tm_b, &bars->cbld_full[st], 64, g, s0, b);
-                    ++cb_next;
-                    progressed = true;
-                }
-                if (x_next < total && mbar_test(&bars->xld_empty[x_next & 1], ((x_next >> 1) & 1) ^ 1)) {
-                    const int unit = blockIdx.x + (x_next / tpu) * gridDim.x, i = x_next % tpu;
-                    const int b = unit / prm.H, h = unit % prm.H;
-                    const int st = x_next & 1;
-                    BM_TRACE(0, x_next, 1);
-                    mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
-                    tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, i * T, b);
-                    ++x_next;
-                    progressed = true;
-                }
-                if (progressed) idle = 0;
-                else {
-                    if (++idle > kPollBudget) BM_ABORT();
-                    __nanosleep(64);  // keep the idle poller off the issue ports and the shared-memory pipe
-                }
-                if (*abort_flag) goto done;
+            for (int it = 0; it < total; ++it) {
+                const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
+                const int b = unit / prm.H, h = unit % prm.H, g = h / hpg;
+                const int st = it & 1, s0 = i * T;
+                // C + B stage: released once CB, Y2 and S of the tile two back have completed
+                BM_WAIT(&bars->cbld_empty[st], ((it >> 1) & 1) ^ 1);
+                BM_TRACE(0, it, 0);
+                mbar_expect_tx(&bars->cbld_full[st], kLoadBytesCB);
+                unsigned char* cs = smem + kOffC + st * 2 * kPanel;
+                unsigned char* bs = smem + kOffB + st * 2 * kPanel;
+                tma_load_4d(cs, &prm.tm_c, &bars->cbld_full[st], 0, g, s0, b);
+                tma_load_4d(cs + kPanel, &prm.tm_c, &bars->cbld_full[st], 64, g, s0, b);
+                tma_load_4d(bs, &prm.tm_b, &bars->cbld_full[st], 0, g, s0, b);
+                tma_load_4d(bs + kPanel, &prm.tm_b, &bars->cbld_full[st], 64, g, s0, b);
+                // X stage: released by the scaling pass and Y1 of the tile two back
+                BM_WAIT(&bars->xld_empty[st], ((it >> 1) & 1) ^ 1);
+                BM_TRACE(0, it, 1);
+                mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
+                tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, s0, b);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer, scan chain
-        // Two job streams, CB(i) = C B^T and Y1(i) = P X; each is issued as soon as its inputs are
-        // ready.  CB(i) reuses the TMEM buffer of P(i-2), so it may run at most one tile ahead of Y1.
-        if (lane == 0) {
+        // Per tile: CB(it+1) = C B^T first (its inputs arrive early and the mask pass of tile it+1
+        // needs it soonest), then Y1(it) = P X once the mask pass of tile it has published P.
+        if (lane == 0 && total > 0) {
             const uint32_t id_cb = umma_idesc_bf16(128, 128, false, false);
             const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
-            int cb_next = 0, y_next = 0;
-#ifdef BM_SSD2_TRACE
-            int cb_seen = 0;
-#endif
-            uint32_t idle = 0;
-            while (y_next < total) {
-                bool progressed = false;
-                if (cb_next < total && cb_next <= y_next + 1) {
-                    const int st = cb_next & 1;
-                    if (mbar_test(&bars->cbld_full[st], (cb_next >> 1) & 1)) {
-                        BM_TRACE(1, cb_next, 0);
-                        const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
+            for (int it = -1; it < total; ++it) {
+                if (it + 1 < total) {
+                    const int nx = it + 1, st = nx & 1;
+                    BM_WAIT(&bars->cbld_full[st], (nx >> 1) & 1);
+                    BM_TRACE(1, nx, 0);
+                    const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
 #pragma unroll 1
-                        for (int k = 0; k < 8; ++k) {
-                            const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                            umma_ss(tmem + kColCB + st * 128, umma_desc_kmajor(cs + off), umma_desc_kmajor(bs + off), id_cb, k > 0);
-                        }
-                        umma_commit(&bars->cb_full[st]);
-                        umma_commit(&bars->cbld_empty[st]);
-                        ++cb_next;
-                        progressed = true;
+                    for (int k = 0; k < 8; ++k) {
+                        const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                        umma_ss(tmem + kColCB + st * 128, umma_desc_kmajor(cs + off), umma_desc_kmajor(bs + off), id_cb, k > 0);
                     }
+                    umma_commit(&bars->cb_full[st]);
+                    umma_commit(&bars->cbld_empty[st]);
                 }
-                if (y_next < cb_next) {
-                    const int st = y_next & 1, cst = y_next % kCumStages;
-                    if (mbar_test(&bars->p_ready[st], (y_next >> 1) & 1) && mbar_test(&bars->y1_empty, (y_next & 1) ^ 1) &&
-                        mbar_test(&bars->xld_full[st], (y_next >> 1) & 1) && mbar_test(&bars->xw_ready[st], (y_next >> 1) & 1) &&
-                        mbar_test(&bars->cum_full[cst], (y_next / kCumStages) & 1)) {
-                        BM_TRACE(1, y_next, 1);
-                        tc_fence_after();
-                        // factored tiles multiply by the scaled tile Xw, exact tiles by X itself
-                        const float* flag = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 5 * T;
-                        const bool factored = *reinterpret_cast<const volatile float*>(flag) != 0.f;
-                        mbar_arrive(&bars->cum_empty[cst]);
-                        const uint32_t xs = factored ? xw_base + st * kPanel : x_base + st * kPanel;
+                if (it >= 0) {
+                    const int st = it & 1, cst = it % kCumStages;
+                    BM_WAIT(&bars->xld_full[st], (it >> 1) & 1);
+                    BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
+                    BM_WAIT(&bars->cum_full[cst], (it / kCumStages) & 1);
+                    BM_WAIT(&bars->y1_empty, (it & 1) ^ 1);
+                    BM_WAIT(&bars->p_ready[st], (it >> 1) & 1);
+                    BM_TRACE(1, it, 1);
+                    tc_fence_after();
+                    // factored tiles multiply by the scaled tile Xw, exact tiles by X itself
+                    const float* flag = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 5 * T;
+                    const bool factored = *reinterpret_cast<const volatile float*>(flag) != 0.f;
+                    mbar_arrive(&bars->cum_empty[cst]);
+                    const uint32_t xs = factored ? xw_base + st * kPanel : x_base + st * kPanel;
 #pragma unroll 1
-                        for (int k = 0; k < 8; ++k)
-                            umma_ts(tmem + kColY1, tmem + kColCB + st * 128 + k * 8, umma_desc_mnmajor(xs + k * 2048, kPanel), id_kmn, k > 0);
-                        umma_commit(&bars->y1_full);
-                        umma_commit(&bars->xld_empty[st]);
-                        ++y_next;
-                        progressed = true;
-                    }
+                    for (int k = 0; k < 8; ++k)
+                        umma_ts(tmem + kColY1, tmem + kColCB + st * 128 + k * 8, umma_desc_mnmajor(xs + k * 2048, kPanel), id_kmn, k > 0);
+                    umma_commit(&bars->y1_full);
+                    umma_commit(&bars->xld_empty[st]);
                 }
-#ifdef BM_SSD2_TRACE
-                if (cb_seen < cb_next && mbar_test(&bars->cb_full[cb_seen & 1], (cb_seen >> 1) & 1)) {
-                    BM_TRACE(1, cb_seen, 2);
-                    ++cb_seen;
-                }
-#endif
-                if (progressed) idle = 0;
-                else {
-                    if (++idle > kPollBudget) BM_ABORT();
-                    __nanosleep(64);  // keep the idle poller off the issue ports and the shared-memory pipe
-                }
-                if (*abort_flag) goto done;
             }
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ MMA issuer, state chain
-        // Two job streams, Y2(i) = C h^T and S(i) = B^T Xw; issued as their inputs become ready.
+        // Per tile: S(it) = B^T Xw first (its inputs are ready earliest and it feeds the state update),
+        // then Y2(it) = C h^T once the state entering the tile has been published.
         if (lane == 0) {
             const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
             const uint32_t id_mnmn = umma_idesc_bf16(128, 64, true, true);
-            int y2_next = 0, s_next = 0;
-            uint32_t idle = 0;
-            while (y2_next < total || s_next < total) {
-                bool progressed = false;
-                if (s_next < total) {
-                    const int st = s_next & 1;
-                    if (mbar_test(&bars->cbld_full[st], (s_next >> 1) & 1) && mbar_test(&bars->xw_ready[st], (s_next >> 1) & 1) &&
-                        mbar_test(&bars->s_empty, (s_next & 1) ^ 1)) {
-                        BM_TRACE(2, s_next, 1);
-                        tc_fence_after();
-                        const uint32_t bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
+            for (int it = 0; it < total; ++it) {
+                const int st = it & 1;
+                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
+                BM_WAIT(&bars->cbld_full[st], (it >> 1) & 1);
+                BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
+                BM_WAIT(&bars->s_empty, (it & 1) ^ 1);
+                BM_TRACE(2, it, 1);
+                tc_fence_after();
 #pragma unroll 1
-                        for (int k = 0; k < 8; ++k)
-                            umma_ss(tmem + kColS, umma_desc_mnmajor(bs + k * 2048, kPanel), umma_desc_mnmajor(xw + k * 2048, kPanel),
-                                    id_mnmn, k > 0);
-                        umma_commit(&bars->s_full);
-                        umma_commit(&bars->xw_free[st]);
-                        // the later of the tile's two GEMMs releases the C / B stage
-                        if (y2_next > s_next) umma_commit(&bars->cbld_empty[st]);
-                        ++s_next;
-                        progressed = true;
-                    }
-                }
-                if (y2_next < total) {
-                    const int st = y2_next & 1;
-                    if (mbar_test(&bars->cbld_full[st], (y2_next >> 1) & 1) && mbar_test(&bars->h_ready, y2_next & 1) &&
-                        mbar_test(&bars->y2_empty[st], ((y2_next >> 1) & 1) ^ 1)) {
-                        BM_TRACE(2, y2_next, 0);
-                        tc_fence_after();
-                        const uint32_t cs = c_base + st * 2 * kPanel;
+                for (int k = 0; k < 8; ++k)
+                    umma_ss(tmem + kColS, umma_desc_mnmajor(bs + k * 2048, kPanel), umma_desc_mnmajor(xw + k * 2048, kPanel), id_mnmn, k > 0);
+                umma_commit(&bars->s_full);
+                umma_commit(&bars->xw_free[st]);
+                BM_WAIT(&bars->h_ready, it & 1);
+                BM_WAIT(&bars->y2_empty[st], ((it >> 1) & 1) ^ 1);
+                BM_TRACE(2, it, 0);
+                tc_fence_after();
 #pragma unroll 1
-                        for (int k = 0; k < 8; ++k) {
-                            const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                            umma_ss(tmem + kColY2 + st * 64, umma_desc_kmajor(cs + off), umma_desc_mnmajor(h_base + k * 2048, kPanel), id_kmn, k > 0);
-                        }
-                        umma_commit(&bars->y2_full[st]);
-                        umma_commit(&bars->h_free);
-                        if (s_next > y2_next) umma_commit(&bars->cbld_empty[st]);
-                        ++y2_next;
-                        progressed = true;
-                    }
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                    umma_ss(tmem + kColY2 + st * 64, umma_desc_kmajor(cs + off), umma_desc_mnmajor(h_base + k * 2048, kPanel), id_kmn, k > 0);
                 }
-                if (progressed) idle = 0;
-                else {
-                    if (++idle > kPollBudget) BM_ABORT();
-                    __nanosleep(64);  // keep the idle poller off the issue ports and the shared-memory pipe
-                }
-                if (*abort_flag) goto done;
+                umma_commit(&bars->y2_full[st]);
+                umma_commit(&bars->h_free);
+                umma_commit(&bars->cbld_empty[st]);
             }
         }
     } else if (warp == 3) {
