@@ -15,6 +15,7 @@ BM_ERR_NULL_POINTER, BM_ERR_BAD_SHAPE, BM_ERR_BAD_ALIGNMENT, BM_ERR_UNSUPPORTED 
 BM_ERR_WORKSPACE_TOO_SMALL, BM_ERR_CUDA, BM_ERR_TIMEOUT = -5, -6, -7
 BM_DTYPE_F32, BM_DTYPE_BF16 = 0, 1
 BM_PATH_AUTO, BM_PATH_EXACT, BM_PATH_TENSOR = 0, 1, 2
+BM_SSD2_NOALLOC_SCRATCH_BYTES = 32 << 20
 
 _i32, _f32, _vp = C.c_int32, C.c_float, C.c_void_p
 
@@ -76,6 +77,7 @@ SYMBOLS = {
     "bm_ssd2_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd2FwdArgs)]),
     "bm_ssd2_fwd": (_i32, [C.POINTER(Ssd2FwdArgs), _vp, C.c_size_t, _vp]),
     "bm_workspace_status": (_i32, [_vp, _vp]),
+    "bm_ssd2_fwd_noalloc": (_i32, [C.POINTER(Ssd2FwdArgs), _vp]),
     "bm_step2": (_i32, [C.POINTER(Step2Args), _vp]),
     "bm_conv_step": (_i32, [C.POINTER(ConvStepArgs), _vp]),
     "bm_selscan1_fwd": (_i32, [C.POINTER(Selscan1Args), _vp]),

@@ -66,6 +66,14 @@ extern "C" int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* a, void* workspace, size_
     return exact::run(ssd2_exact_params(a), workspace, workspace_bytes, st);
 }
 
+extern "C" int32_t bm_ssd2_fwd_noalloc(const bm_ssd2_fwd_args* a, void* stream) {
+    clear_error();
+    if (int32_t e = validate_ssd2(a)) return e;
+    if (a->path == BM_PATH_TENSOR)
+        return fail(BM_ERR_UNSUPPORTED, "bm_ssd2_fwd_noalloc runs the exact path only");
+    return exact::run_noalloc(ssd2_exact_params(a), static_cast<cudaStream_t>(stream));
+}
+
 // ---------------------------------------------------------------------------------------------
 static int32_t validate_ssd3(const bm_ssd3_fwd_args* a, bool single) {
     if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");

@@ -6,6 +6,8 @@
 // src/mamba3/double_ssd/ssd/serial.rs:118-409 and src/mamba3/single_ssd/ssd/serial.rs:56-268 (Mamba-3).
 #include "ssd_exact.cuh"
 
+#include <mutex>
+
 namespace bm {
 namespace exact {
 
@@ -342,6 +344,60 @@ int32_t run(Params p, void* workspace, size_t ws_bytes, cudaStream_t stream) {
     if ((size_t)16 * (p.P + p.R) * sizeof(float) > 48 * 1024)
         return fail(BM_ERR_UNSUPPORTED, "headdim + state_rank too large for the exact path");
     return p.dtype == BM_DTYPE_F32 ? launch<float>(p, stream) : launch<__nv_bfloat16>(p, stream);
+}
+
+}  // namespace exact
+}  // namespace bm
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the exact Mamba-2 SSD forward.
+//
+// Some hosts of this library may never allocate device memory once they are running: a serving
+// process whose memory budget is fixed and handed out at start-up, a plugin that is given raw tensor
+// pointers by its framework but has no handle on that framework's allocator (so it cannot size and
+// obtain the workspace bm_ssd2_fwd asks for), or code that runs where cudaMalloc would serialise
+// the whole device.  For them the scratch of the exact path lives inside the library image: a
+// file-scope device array that every GPU loading the library holds until the process exits.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BM_SSD2_NOALLOC_SCRATCH_BYTES];
+
+namespace bm {
+namespace exact {
+
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol; the address the kernels can
+// use comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int32_t noalloc_scratch_ptr(void** out) {
+    constexpr int kMaxDevices = 64;
+    static void* ptrs[kMaxDevices] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    if (int32_t e = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return e;
+    if (dev < 0 || dev >= kMaxDevices) return fail(BM_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (ptrs[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess) return check_cuda(e, "cudaGetSymbolAddress(scratch)");
+        if (p == nullptr) return fail(BM_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return BM_OK;
+}
+
+int32_t run_noalloc(Params p, cudaStream_t stream) {
+    p.NC = (int)cdiv(p.S, p.Q);
+    const size_t need = workspace_bytes(p.B, p.S, p.H, p.P, p.R, p.Q, p.states == nullptr);
+    if (need > (size_t)BM_SSD2_NOALLOC_SCRATCH_BYTES)
+        return fail(BM_ERR_WORKSPACE_TOO_SMALL,
+                    "this problem needs %zu bytes of scratch, the built-in scratch holds %zu: use bm_ssd2_fwd with a "
+                    "caller-provided workspace",
+                    need, (size_t)BM_SSD2_NOALLOC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    if (int32_t e = noalloc_scratch_ptr(&scratch)) return e;
+    // Nothing in the scratch has to start at zero: K1 writes every cumsum / column-scale entry and K3
+    // writes every chunk state before anything reads them, so the previous call's contents are dead.
+    return run(p, scratch, (size_t)BM_SSD2_NOALLOC_SCRATCH_BYTES, stream);
 }
 
 }  // namespace exact

@@ -39,6 +39,8 @@ size_t workspace_bytes(int B, int S, int H, int P, int R, int Q, bool need_state
 // Carves cum / cs / states out of `workspace` (states only if p.states == NULL on entry) and runs
 // K1 -> K3 -> K4 -> K5 on `stream`.
 int32_t run(Params p, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+// Same chain with the library's built-in scratch array instead of a caller workspace (no allocation).
+int32_t run_noalloc(Params p, cudaStream_t stream);
 
 }  // namespace exact
 }  // namespace bm

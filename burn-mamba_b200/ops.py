@@ -213,3 +213,28 @@ def step3(state, k_state, v_state, angle, x, b, c, rot, dt, alpha, beta, gamma, 
                           beta=_ptr(beta), gamma=_ptr(gamma), mimo_x=_ptr(mimo_x), y=_ptr(y))
     check(lib.bm_step3(C.byref(args), _stream()), "bm_step3")
     return y
+
+
+def ssd2_fwd_noalloc(x, dt, a, b, c, d=None, h0=None, chunk_len=256, dt_bias=None, dt_limit=(0.0, 65504.0), z=None):
+    """bm_ssd2_fwd_noalloc: the exact Mamba-2 SSD forward with the library's built-in scratch instead of
+    a workspace -- this wrapper still allocates the outputs, the library call itself allocates nothing.
+    Raises BmError(BM_ERR_WORKSPACE_TOO_SMALL) when the problem needs more scratch than the built-in
+    array holds.  Calls share that array: do not overlap them on different streams."""
+    bsz, s, h, p = x.shape
+    g, r = b.shape[2], b.shape[3]
+    act = x.dtype
+    if act not in _DT:
+        raise ValueError(f"unsupported activation dtype {act}")
+    _chk(x, "x"); _chk(dt, "dt", torch.float32, (bsz, s, h)); _chk(a, "a", torch.float32, (h,))
+    _chk(b, "b", act, (bsz, s, g, r)); _chk(c, "c", act, (bsz, s, g, r))
+    _chk(d, "d", torch.float32, (h,), optional=True); _chk(h0, "h0", torch.float32, (bsz, h, p, r), optional=True)
+    _chk(dt_bias, "dt_bias", torch.float32, (h,), optional=True); _chk(z, "z", act, x.shape, optional=True)
+    y = torch.empty_like(x)
+    h_final = torch.empty((bsz, h, p, r), dtype=torch.float32, device=x.device)
+    args = _ffi.Ssd2FwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, chunk_len=chunk_len,
+                            dtype=_DT[act], path=_ffi.BM_PATH_EXACT, reserved=0, x=_ptr(x), dt=_ptr(dt), a=_ptr(a),
+                            b=_ptr(b), c=_ptr(c), d=_ptr(d), h0=_ptr(h0), dt_bias=_ptr(dt_bias),
+                            dt_min=dt_limit[0], dt_max=dt_limit[1], z=_ptr(z), y=_ptr(y), h_final=_ptr(h_final),
+                            chunk_states=None)
+    check(lib.bm_ssd2_fwd_noalloc(C.byref(args), _stream()), "bm_ssd2_fwd_noalloc")
+    return y, h_final

@@ -98,6 +98,24 @@ int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* args, void* workspace, size_t worksp
  * the kernel ran to completion, or for paths that cannot time out). */
 int32_t bm_workspace_status(const void* workspace, void* stream);
 
+/* Allocation-free variant of bm_ssd2_fwd (exact path).  It has no counterpart in the reference.
+ * It exists for callers that must not, or cannot, allocate device memory while running -- a server
+ * with a memory budget fixed at start-up, or a plugin that receives raw tensor pointers from its
+ * framework without access to the framework's allocator and so has nowhere to get a workspace from.
+ * The scratch is a device array of BM_SSD2_NOALLOC_SCRATCH_BYTES built into the library (each GPU
+ * that loads the library holds it until the process exits); the call allocates and frees nothing.
+ *   - Same arguments, layouts and results as bm_ssd2_fwd with path BM_PATH_AUTO / BM_PATH_EXACT (float32
+ *     arithmetic on CUDA cores; BM_PATH_TENSOR is refused with BM_ERR_UNSUPPORTED).
+ *   - Problems whose scratch need (what bm_ssd2_fwd_workspace_bytes reports for BM_PATH_EXACT) exceeds the
+ *     array are refused with BM_ERR_WORKSPACE_TOO_SMALL; nothing is launched.
+ *   - The first call on each device looks the array's device address up (with that device current);
+ *     make that first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents; nothing in
+ *     it needs clearing between calls, but two calls that overlap on the GPU (different streams) race
+ *     on it: serialise them. */
+#define BM_SSD2_NOALLOC_SCRATCH_BYTES (32u << 20)
+int32_t bm_ssd2_fwd_noalloc(const bm_ssd2_fwd_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Mamba-2 recurrent step: state update + readout for one token, state updated in place.
  * Replaces the body of Mamba2::step between the conv and the gated norm
