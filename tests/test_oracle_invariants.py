@@ -197,3 +197,50 @@ def test_c_port_matches_numpy_oracle():
     y, hf = cport.selscan1(sc["u"], sc["delta"], sc["a"], sc["b"], sc["c"], sc["d"], sc["h0"])
     wy, wh = mamba1.selective_scan(sc["delta"], sc["a"], sc["b"], sc["c"], sc["d"], sc["u"], sc["h0"], dtype=np.float64)
     assert rel_l2(y, wy) < 1e-5 and rel_l2(hf, wh) < 1e-5
+
+
+def test_backward_oracle_forward_matches_numpy_and_finite_differences():
+    """The torch restatement used for autodiff equals the numpy oracle, and its gradients equal central
+    finite differences of the numpy oracle (an autodiff-free check)."""
+    import torch
+    from oracle import backward, inputs
+    cfg = inputs.ssd2_prefill(seed=9, batch=1, seqlen=10, nheads=2, headdim=3, state_rank=4, ngroups=1, h0_std=0.3)
+    arr = {k: cfg[k].astype(np.float64) for k in ("x", "dt", "a", "b", "c", "d", "h0")}
+    rng = np.random.default_rng(0)
+    dy = rng.standard_normal(arr["x"].shape)
+    dhf = rng.standard_normal(arr["h0"].shape)
+    y_t, h_t = backward.ssd2_forward_torch(*(torch.tensor(arr[k]) for k in ("x", "dt", "a", "b", "c", "d", "h0")), 4)
+    y_n, h_n = mamba2.ssd_serial(arr["x"], arr["dt"], arr["a"], arr["b"], arr["c"], arr["d"], arr["h0"], 4)
+    assert np.max(np.abs(y_t.numpy() - y_n)) < 1e-12 and np.max(np.abs(h_t.numpy() - h_n)) < 1e-12
+    g = backward.ssd2_grads(arr["x"], arr["dt"], arr["a"], arr["b"], arr["c"], arr["d"], arr["h0"], dy, dhf, 4)
+
+    def loss(**a):
+        y, h = mamba2.ssd_serial(a["x"], a["dt"], a["a"], a["b"], a["c"], a["d"], a["h0"], 4)
+        return float((y * dy).sum() + (h * dhf).sum())
+
+    for name, key, idx in (("x", "dx", (0, 3, 1, 2)), ("dt", "ddt", (0, 5, 1)), ("a", "da", (1,)), ("b", "db", (0, 2, 0, 3)),
+                           ("c", "dc", (0, 7, 0, 1)), ("d", "dd", (0,)), ("h0", "dh0", (0, 1, 2, 3))):
+        fd = backward.finite_difference(loss, arr, name, idx)
+        assert abs(fd - g[key][idx]) < 1e-6 * max(1.0, abs(fd)), (name, fd, g[key][idx])
+
+
+def test_backward_oracle_m3_single_equals_double_gradients():
+    """single-SSD == double-SSD on gradients (src/mamba3/single_ssd/single_ssd/tests.rs:374-428), at the core
+    level: with scale = gamma (no look-ahead term) and a strict mask + gamma diagonal, the single core on v
+    equals the generic core on gamma*v, so their gradients with respect to B, C, da, h0 agree."""
+    from oracle import backward
+    rng = np.random.default_rng(3)
+    b, s, m, h, p, r = 1, 9, 2, 2, 3, 4
+    v = rng.standard_normal((b, s, m, h, p))
+    bm = rng.standard_normal((b, s, m, h, r))
+    cm = rng.standard_normal((b, s, m, h, r))
+    da = -rng.uniform(0.05, 0.3, (b, s, h))
+    gamma = rng.uniform(0.1, 0.5, (b, s, h))
+    h0 = 0.1 * rng.standard_normal((b, h, p, r))
+    dy = rng.standard_normal(v.shape)
+    dhf = rng.standard_normal(h0.shape)
+    g1 = backward.ssd3_grads(v, da, bm, cm, gamma, gamma, h0, dy, dhf, 4, single=True)
+    g2 = backward.ssd3_grads(v * gamma[:, :, None, :, None], da, bm, cm, None, None, h0, dy, dhf, 4, single=False)
+    for k in ("dda", "db", "dc", "dh0"):
+        assert np.max(np.abs(g1[k] - g2[k])) < 1e-9, k
+    assert np.max(np.abs(g1["dv"] - g2["dv"] * gamma[:, :, None, :, None])) < 1e-9
