@@ -13,7 +13,8 @@ namespace {
 
 constexpr int CH = 32;    // channels per CTA
 constexpr int TCH = 64;   // tokens per staged chunk
-constexpr int RPT = 4;    // states per thread
+constexpr int RPT = 2;    // states per thread
+constexpr int TU = 4;     // tokens processed together (independent loads / exps issued ahead of the recurrence)
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -37,7 +38,7 @@ template <typename T>
 __global__ void selscan1_kernel(bm_selscan1_args a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     Stage<T>* stages = reinterpret_cast<Stage<T>*>(smem_raw);
-    T* ytile = reinterpret_cast<T*>(smem_raw + 2 * sizeof(Stage<T>));  // [TCH][CH]
+    float* ytile = reinterpret_cast<float*>(smem_raw + 2 * sizeof(Stage<T>));  // [TCH][CH] pre-gate outputs
     const int R = a.state_rank, I = a.d_inner, S = a.seqlen;
     const int tpc = R / RPT;  // threads per channel
     const int tid = threadIdx.x, nthreads = blockDim.x;
@@ -91,7 +92,43 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
         __syncthreads();
         Stage<T>& st = stages[stg];
         const int t0 = chunk * TCH, nt = min(TCH, S - t0);
-        for (int t = 0; t < nt; ++t) {
+        // The recurrence only chains through h; everything else of TU tokens (loads, softplus, exp,
+        // input term) is issued first so the dependent FMAs of the TU steps run back to back.
+        int t = 0;
+        for (; t + TU <= nt; t += TU) {
+            float dl[TU], uu[TU], ea[TU][RPT], bu[TU][RPT], ck[TU][RPT], part[TU];
+#pragma unroll
+            for (int j = 0; j < TU; ++j) {
+                dl[j] = to_f32(st.delta[t + j][cl]);
+                if (a.delta_softplus) dl[j] = softplus_stock(dl[j] + dbias);
+                uu[j] = to_f32(st.u[t + j][cl]);
+                const float du = dl[j] * uu[j];
+#pragma unroll
+                for (int k = 0; k < RPT; ++k) {
+                    ea[j][k] = __expf(dl[j] * av[k]);
+                    bu[j][k] = du * to_f32(st.bmat[(t + j) * R + q * RPT + k]);
+                    ck[j][k] = to_f32(st.cmat[(t + j) * R + q * RPT + k]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < TU; ++j) {
+                part[j] = 0.f;
+#pragma unroll
+                for (int k = 0; k < RPT; ++k) {
+                    h[k] = fmaf(h[k], ea[j][k], bu[j][k]);
+                    part[j] = fmaf(h[k], ck[j][k], part[j]);
+                }
+            }
+            for (int o = tpc >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int j = 0; j < TU; ++j) part[j] += __shfl_xor_sync(0xffffffffu, part[j], o);
+            }
+            if (q == 0) {
+#pragma unroll
+                for (int j = 0; j < TU; ++j) ytile[(t + j) * CH + cl] = fmaf(dskip, uu[j], part[j]);
+            }
+        }
+        for (; t < nt; ++t) {
             float delta = to_f32(st.delta[t][cl]);
             if (a.delta_softplus) delta = softplus_stock(delta + dbias);
             const float u = to_f32(st.u[t][cl]);
@@ -100,27 +137,28 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
 #pragma unroll
             for (int k = 0; k < RPT; ++k) {
                 const float bk = to_f32(st.bmat[t * R + q * RPT + k]);
-                const float ck = to_f32(st.cmat[t * R + q * RPT + k]);
+                const float ckk = to_f32(st.cmat[t * R + q * RPT + k]);
                 h[k] = fmaf(h[k], __expf(delta * av[k]), du * bk);
-                part = fmaf(h[k], ck, part);
+                part = fmaf(h[k], ckk, part);
             }
             for (int o = tpc >> 1; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (q == 0) {
-                float y = fmaf(dskip, u, part);
-                if (zg) y *= silu_f32(to_f32(st.z[t][cl]));
-                ytile[t * CH + cl] = from_f32<T>(y);
-            }
+            if (q == 0) ytile[t * CH + cl] = fmaf(dskip, u, part);
         }
         __syncthreads();
+        // gate and store: every thread handles one 16-byte vector of outputs (coalesced along channels)
         constexpr int VPR = CH / EPV;
         for (int e = tid; e < nt * VPR; e += nthreads) {
-            int t = e / VPR, vv = (e % VPR) * EPV;
-            *reinterpret_cast<uint4*>(yg + (int64_t)(t0 + t) * I + vv) = *reinterpret_cast<const uint4*>(&ytile[t * CH + vv]);
+            const int tt = e / VPR, vv = (e % VPR) * EPV;
+            alignas(16) T outv[EPV];
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) {
+                float y = ytile[tt * CH + vv + j];
+                if (zg) y *= silu_f32(to_f32(st.z[tt][vv + j]));
+                outv[j] = from_f32<T>(y);
+            }
+            *reinterpret_cast<uint4*>(yg + (int64_t)(t0 + tt) * I + vv) = *reinterpret_cast<const uint4*>(outv);
         }
-        // the next iteration's barrier (after its cp.async wait) orders these reads of ytile and of
-        // stage `stg` before they are overwritten: ytile is rewritten only after that barrier, and
-        // stage `stg` is refilled by issue() of iteration chunk + 1, i.e. after this point for every
-        // thread, but other threads may still be reading it -> explicit barrier.
+        // stage `stg` and ytile are refilled in the next iteration: every thread must be done reading them
         __syncthreads();
     }
 #pragma unroll
@@ -168,7 +206,7 @@ int32_t launch(const bm_selscan1_args& a, cudaStream_t st) {
     constexpr int EPV = 16 / sizeof(T);
     const bool fast = I % CH == 0 && R % RPT == 0 && R <= 64 && pow2 && tpc <= 32 && (R % EPV == 0);
     if (fast) {
-        size_t smem = 2 * sizeof(Stage<T>) + sizeof(T) * TCH * CH;
+        size_t smem = 2 * sizeof(Stage<T>) + sizeof(float) * TCH * CH;
         cudaError_t e = cudaFuncSetAttribute(selscan1_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(selscan1)");
         unsigned grid = (unsigned)((int64_t)a.batch * (I / CH));

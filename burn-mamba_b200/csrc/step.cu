@@ -199,17 +199,19 @@ __global__ void step1_kernel(bm_step1_args a) {
 // ------------------------------------------------------------------------------------------
 constexpr int kStep3MaxM = 8;
 
-__device__ __forceinline__ float rot_elem(const float* row, const float* ang_sm, int r, int R, int rope_dim, bool pairwise) {
+// One rotated B/C element from the cos/sin tables of the new angle (src/modules/misc/rope.rs:50-170).
+__device__ __forceinline__ float rot_elem(const float* row, const float* cs_sm, const float* sn_sm, int r, int R, int rope_dim,
+                                          bool pairwise) {
     float self = row[r];
     if (rope_dim == 0) return self;
     if (pairwise) {
         if (r >= rope_dim) return self;
-        float th = ang_sm[r >> 1], c = cosf(th), s = sinf(th), other = row[r ^ 1];
+        const float c = cs_sm[r >> 1], s = sn_sm[r >> 1], other = row[r ^ 1];
         return (r & 1) ? (s * other + c * self) : (c * self - s * other);
     }
     int half = R >> 1, na = rope_dim >> 1;
-    if (r < na) return cosf(ang_sm[r]) * self - sinf(ang_sm[r]) * row[r + half];
-    if (r >= half && r < half + na) return sinf(ang_sm[r - half]) * row[r - half] + cosf(ang_sm[r - half]) * self;
+    if (r < na) return cs_sm[r] * self - sn_sm[r] * row[r + half];
+    if (r >= half && r < half + na) return sn_sm[r - half] * row[r - half] + cs_sm[r - half] * self;
     return self;
 }
 
@@ -217,8 +219,10 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
     extern __shared__ float sm[];
     const int R = a.state_rank, P = a.headdim, M = a.mimo_rank, H = a.nheads;
     const int na_alloc = max(a.rope_dim / 2, 1), na = a.rope_dim / 2;
-    float* ang = sm;                 // [na_alloc]
-    float* bs = ang + na_alloc;      // [M][R] rotated B
+    float* ang = sm;                 // [na_alloc] new wrapped angle
+    float* cosv = ang + na_alloc;    // [na_alloc]
+    float* sinv = cosv + na_alloc;   // [na_alloc]
+    float* bs = sm + ((3 * na_alloc + 3) & ~3);  // [M][R] rotated B (16-byte aligned for 128-bit reads)
     float* cs = bs + M * R;          // [M][R] rotated C
     float* bp = cs + M * R;          // [M][R] previous rotated B
     const int bh = blockIdx.x, b = bh / H, h = bh % H, tid = threadIdx.x;
@@ -229,14 +233,15 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
         float inc = dt * (tanhf(a.rot[(int64_t)b * na_alloc + j]) * (a.range * 3.14159265358979323846f));
         float th = wrap_angle(a.angle[(int64_t)bh * na_alloc + j] + inc);
         ang[j] = th;
+        sincosf(th, &sinv[j], &cosv[j]);
     }
     __syncthreads();
     // (1b) rotate B and C, stage the previous B
     for (int e = tid; e < M * R; e += blockDim.x) {
         int m = e / R, r = e % R;
         int64_t row = (((int64_t)b * M + m) * H + h) * R;
-        bs[e] = rot_elem(a.b + row, ang, r, R, na * 2, pairwise);
-        cs[e] = rot_elem(a.c + row, ang, r, R, na * 2, pairwise);
+        bs[e] = rot_elem(a.b + row, cosv, sinv, r, R, na * 2, pairwise);
+        cs[e] = rot_elem(a.c + row, cosv, sinv, r, R, na * 2, pairwise);
         bp[e] = a.k_state[row + r];
     }
     __syncthreads();
@@ -244,6 +249,72 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
     const float alpha = a.alpha[bh], beta = a.beta[bh], gamma = a.gamma[bh];
     const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     float* st = a.state + (int64_t)bh * P * R;
+    if (R % 4 == 0 && R <= 128 && M <= 4) {
+        // Fast path: a lane owns 4 consecutive state columns of every row (one 128-bit load / store per
+        // row), keeps its slice of the rotated B / C and of the previous B in registers, and the warp
+        // works on two rows at a time so that two independent row loads are in flight.
+        const int r4 = lane * 4;
+        const bool act = r4 < R;
+        float4 bq[4], cq[4], pq[4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const bool on = act && m < M;
+            bq[m] = on ? ld4(bs + m * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            cq[m] = on ? ld4(cs + m * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            pq[m] = on ? ld4(bp + m * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        for (int p0 = warp; p0 < P; p0 += 2 * nwarps) {
+            const int rows[2] = {p0, p0 + nwarps};
+            float4 hv[2];
+            float xr[2], xp[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const bool live = rows[j] < P;
+                hv[j] = (live && act) ? ld4(st + (int64_t)rows[j] * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                xr[j] = live ? a.x[(int64_t)bh * P + rows[j]] : 0.f;
+                xp[j] = live ? a.v_state[(int64_t)bh * P + rows[j]] : 0.f;
+            }
+            float part[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                float4 h4 = make_float4(alpha * hv[j].x, alpha * hv[j].y, alpha * hv[j].z, alpha * hv[j].w);
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    if (m < M) {
+                        const float mx = (a.mimo_x && rows[j] < P) ? a.mimo_x[((int64_t)h * M + m) * P + rows[j]] : 1.f;
+                        const float g = gamma * xr[j] * mx, bt = beta * xp[j] * mx;
+                        h4.x = fmaf(g, bq[m].x, fmaf(bt, pq[m].x, h4.x));
+                        h4.y = fmaf(g, bq[m].y, fmaf(bt, pq[m].y, h4.y));
+                        h4.z = fmaf(g, bq[m].z, fmaf(bt, pq[m].z, h4.z));
+                        h4.w = fmaf(g, bq[m].w, fmaf(bt, pq[m].w, h4.w));
+                    }
+                }
+                if (rows[j] < P && act) st4(st + (int64_t)rows[j] * R + r4, h4);
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    part[j][m] = h4.x * cq[m].x + h4.y * cq[m].y + h4.z * cq[m].z + h4.w * cq[m].w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int m = 0; m < 4; ++m)
+                        if (m < M) part[j][m] += __shfl_xor_sync(0xffffffffu, part[j][m], o);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    if (rows[j] < P) {
+#pragma unroll
+                        for (int m = 0; m < 4; ++m)
+                            if (m < M) a.y[(((int64_t)b * M + m) * H + h) * P + rows[j]] = part[j][m];
+                        a.v_state[(int64_t)bh * P + rows[j]] = xr[j];
+                    }
+                }
+            }
+        }
+    } else {
     for (int p = warp; p < P; p += nwarps) {
         const float x = a.x[(int64_t)bh * P + p], xprev = a.v_state[(int64_t)bh * P + p];
         float cg[kStep3MaxM], cb[kStep3MaxM], part[kStep3MaxM];
@@ -274,6 +345,7 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
             }
         }
         if (lane == 0) a.v_state[(int64_t)bh * P + p] = x;
+    }
     }
     // (3) cache roll: k_state := rotated B, angle := new angle (all reads of the old values are done:
     // bp / ang were staged before the barrier above)
@@ -370,7 +442,7 @@ extern "C" int32_t bm_step3(const bm_step3_args* a, void* stream) {
     BM_REQUIRE_PTR(a->gamma);
     BM_REQUIRE_PTR(a->y);
     BM_OPTIONAL_PTR(a->mimo_x);
-    size_t smem = ((size_t)(a->rope_dim / 2 > 1 ? a->rope_dim / 2 : 1) + 3 * (size_t)a->mimo_rank * a->state_rank) * sizeof(float);
+    size_t smem = (((3 * (size_t)(a->rope_dim / 2 > 1 ? a->rope_dim / 2 : 1) + 3) & ~(size_t)3) + 3 * (size_t)a->mimo_rank * a->state_rank) * sizeof(float);
     BM_REQUIRE(smem <= 48 * 1024, BM_ERR_UNSUPPORTED, "mimo_rank * state_rank too large for the step kernel");
     int64_t bh = (int64_t)a->batch * a->nheads;
     step3_kernel<<<(unsigned)bh, 256, smem, static_cast<cudaStream_t>(stream)>>>(*a);
