@@ -57,6 +57,20 @@ class Ssd3FwdArgs(C.Structure):
         ("y", _vp), ("h_final", _vp)]
 
 
+class Ssd2BwdArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "headdim", "state_rank", "ngroups", "chunk_len",
+                                    "dtype")] + [
+        (n, _vp) for n in ("x", "dt", "a", "b", "c", "d", "h0", "dy", "dh_final", "dx", "ddt", "da", "db", "dc", "dd",
+                           "dh0")]
+
+
+class Ssd3BwdArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "headdim", "state_rank", "mimo_rank", "chunk_len",
+                                    "dtype")] + [
+        (n, _vp) for n in ("v", "da", "b", "c", "gamma", "scale", "h0", "dy", "dh_final", "dv", "dda", "db", "dc",
+                           "dgamma", "dscale", "dh0")]
+
+
 class AngleCumsumArgs(C.Structure):
     _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "nangles")] + [
         ("range", _f32), ("rot", _vp), ("dt", _vp), ("prev", _vp), ("theta", _vp), ("last", _vp)]
@@ -78,6 +92,11 @@ SYMBOLS = {
     "bm_ssd2_fwd": (_i32, [C.POINTER(Ssd2FwdArgs), _vp, C.c_size_t, _vp]),
     "bm_workspace_status": (_i32, [_vp, _vp]),
     "bm_ssd2_fwd_noalloc": (_i32, [C.POINTER(Ssd2FwdArgs), _vp]),
+    "bm_ssd2_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd2BwdArgs)]),
+    "bm_ssd2_bwd": (_i32, [C.POINTER(Ssd2BwdArgs), _vp, C.c_size_t, _vp]),
+    "bm_ssd3_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd3BwdArgs)]),
+    "bm_ssd3_single_bwd": (_i32, [C.POINTER(Ssd3BwdArgs), _vp, C.c_size_t, _vp]),
+    "bm_ssd3_double_bwd": (_i32, [C.POINTER(Ssd3BwdArgs), _vp, C.c_size_t, _vp]),
     "bm_step2": (_i32, [C.POINTER(Step2Args), _vp]),
     "bm_conv_step": (_i32, [C.POINTER(ConvStepArgs), _vp]),
     "bm_selscan1_fwd": (_i32, [C.POINTER(Selscan1Args), _vp]),

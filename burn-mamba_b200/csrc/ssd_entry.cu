@@ -146,3 +146,71 @@ extern "C" int32_t bm_workspace_status(const void* workspace, void* stream) {
     if (word == BM_ERR_TIMEOUT) return fail(BM_ERR_TIMEOUT, "a bounded barrier wait inside the SSD kernel ran out");
     return BM_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Backward entry points
+// ---------------------------------------------------------------------------------------------
+extern "C" size_t bm_ssd2_bwd_workspace_bytes(const bm_ssd2_bwd_args* a) {
+    if (a == nullptr || a->batch <= 0 || a->seqlen <= 0 || a->nheads <= 0 || a->chunk_len <= 0) return 0;
+    return exact::bwd_workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, true);
+}
+
+extern "C" int32_t bm_ssd2_bwd(const bm_ssd2_bwd_args* a, void* ws, size_t ws_bytes, void* stream) {
+    clear_error();
+    if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
+    BM_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->nheads > 0 && a->headdim > 0 && a->state_rank > 0, BM_ERR_BAD_SHAPE,
+               "batch, seqlen, nheads, headdim, state_rank must be positive");
+    BM_REQUIRE(a->chunk_len > 0, BM_ERR_BAD_SHAPE, "chunk_len must be positive");
+    BM_REQUIRE(a->ngroups > 0 && a->nheads % a->ngroups == 0, BM_ERR_BAD_SHAPE, "nheads must be divisible by ngroups");
+    BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
+    BM_REQUIRE_PTR(a->x); BM_REQUIRE_PTR(a->dt); BM_REQUIRE_PTR(a->a); BM_REQUIRE_PTR(a->b); BM_REQUIRE_PTR(a->c);
+    BM_REQUIRE_PTR(a->dy); BM_REQUIRE_PTR(a->dx); BM_REQUIRE_PTR(a->ddt); BM_REQUIRE_PTR(a->da); BM_REQUIRE_PTR(a->db);
+    BM_REQUIRE_PTR(a->dc); BM_REQUIRE_PTR(a->dh0);
+    BM_OPTIONAL_PTR(a->d); BM_OPTIONAL_PTR(a->h0); BM_OPTIONAL_PTR(a->dh_final); BM_OPTIONAL_PTR(a->dd);
+    BM_REQUIRE((a->d == nullptr) == (a->dd == nullptr), BM_ERR_NULL_POINTER, "d and dd must be given together");
+    exact::BwdParams bp{};
+    exact::Params& p = bp.fwd;
+    p.B = a->batch, p.S = a->seqlen, p.H = a->nheads, p.P = a->headdim, p.R = a->state_rank;
+    p.G = a->ngroups, p.M = 1, p.Q = a->chunk_len, p.dtype = a->dtype, p.strict = 0, p.cs_mode = 1, p.pairwise = 1;
+    p.v = a->x, p.bmat = a->b, p.cmat = a->c, p.dsrc = a->dt, p.a = a->a, p.d = a->d, p.h0 = a->h0;
+    bp.dy = a->dy, bp.dh_final = a->dh_final, bp.dv = a->dx, bp.db = a->db, bp.dc = a->dc;
+    bp.d_dt = a->ddt, bp.d_a = a->da, bp.dd = a->dd, bp.dh0 = a->dh0;
+    return exact::run_bwd(bp, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t bm_ssd3_bwd_workspace_bytes(const bm_ssd3_bwd_args* a) {
+    if (a == nullptr || a->batch <= 0 || a->seqlen <= 0 || a->nheads <= 0 || a->chunk_len <= 0) return 0;
+    return exact::bwd_workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, false);
+}
+
+static int32_t ssd3_bwd(const bm_ssd3_bwd_args* a, void* ws, size_t ws_bytes, void* stream, bool single) {
+    clear_error();
+    if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
+    BM_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->nheads > 0 && a->headdim > 0 && a->state_rank > 0 && a->mimo_rank > 0,
+               BM_ERR_BAD_SHAPE, "batch, seqlen, nheads, headdim, state_rank, mimo_rank must be positive");
+    BM_REQUIRE(a->chunk_len > 0, BM_ERR_BAD_SHAPE, "chunk_len must be positive");
+    BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
+    BM_REQUIRE_PTR(a->v); BM_REQUIRE_PTR(a->da); BM_REQUIRE_PTR(a->b); BM_REQUIRE_PTR(a->c); BM_REQUIRE_PTR(a->dy);
+    BM_REQUIRE_PTR(a->dv); BM_REQUIRE_PTR(a->dda); BM_REQUIRE_PTR(a->db); BM_REQUIRE_PTR(a->dc); BM_REQUIRE_PTR(a->dh0);
+    BM_OPTIONAL_PTR(a->h0); BM_OPTIONAL_PTR(a->dh_final);
+    if (single) {
+        BM_REQUIRE_PTR(a->gamma); BM_REQUIRE_PTR(a->scale); BM_REQUIRE_PTR(a->dgamma); BM_REQUIRE_PTR(a->dscale);
+    }
+    exact::BwdParams bp{};
+    exact::Params& p = bp.fwd;
+    p.B = a->batch, p.S = a->seqlen, p.H = a->nheads, p.P = a->headdim, p.R = a->state_rank;
+    p.G = a->nheads, p.M = a->mimo_rank, p.Q = a->chunk_len, p.dtype = a->dtype;
+    p.strict = single ? 1 : 0, p.cs_mode = single ? 2 : 0, p.pairwise = a->mimo_rank == 1;
+    p.v = a->v, p.bmat = a->b, p.cmat = a->c, p.dsrc = a->da, p.colscale = single ? a->scale : nullptr;
+    p.gamma = single ? a->gamma : nullptr, p.h0 = a->h0;
+    bp.dy = a->dy, bp.dh_final = a->dh_final, bp.dv = a->dv, bp.db = a->db, bp.dc = a->dc, bp.d_da = a->dda;
+    bp.d_cs = single ? a->dscale : nullptr, bp.d_gs = single ? a->dgamma : nullptr, bp.dh0 = a->dh0;
+    return exact::run_bwd(bp, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t bm_ssd3_single_bwd(const bm_ssd3_bwd_args* a, void* ws, size_t ws_bytes, void* stream) {
+    return ssd3_bwd(a, ws, ws_bytes, stream, true);
+}
+extern "C" int32_t bm_ssd3_double_bwd(const bm_ssd3_bwd_args* a, void* ws, size_t ws_bytes, void* stream) {
+    return ssd3_bwd(a, ws, ws_bytes, stream, false);
+}

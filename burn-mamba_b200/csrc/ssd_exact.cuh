@@ -33,7 +33,29 @@ struct Params {
     float* states;          // workspace or caller buffer [b, nc, h, p, r]
     void* y;
     float* h_final;
+    float* gs;              // optional workspace [b, h, nc, Q]: same-time weight (written by K1 when set)
+    int state_weight_mode;  // K3 row weight: 0 = cs * exp(Aend - cum) (forward), 1 = exp(cum) (readout gradient)
 };
+
+// Backward of the same general chunked SSD (Mamba-2 and both Mamba-3 cores).  All gradients float32.
+struct BwdParams {
+    Params fwd;             // forward inputs (y, h_final, z, angles, dt_bias unused / must be NULL)
+    const void* dy;         // [b, s, m, h, p] act dtype
+    const float* dh_final;  // [b, h, p, r] or NULL
+    float* dv;              // [b, s, m, h, p]
+    float* db;              // [b, s, m, G, r] (summed over the heads of a group when G < H)
+    float* dc;              // [b, s, m, G, r]
+    float* d_da;            // [b, s, h]   gradient of the per-step log-decay (Mamba-3: output; Mamba-2: internal)
+    float* d_cs;            // [b, s, h]   gradient of the source-column scale (Mamba-3 single: d_scale)
+    float* d_gs;            // [b, s, h]   gradient of the same-time weight   (Mamba-3 single: d_gamma)
+    float* d_dt;            // [b, s, h]   Mamba-2 only: d_da * A + d_cs + d_gs
+    float* d_a;             // [h]         Mamba-2 only: sum d_da * dt
+    float* dd;              // [h] or NULL
+    float* dh0;             // [b, h, p, r]
+};
+
+size_t bwd_workspace_bytes(int B, int S, int H, int P, int R, int Q, bool mamba2);
+int32_t run_bwd(BwdParams p, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 size_t workspace_bytes(int B, int S, int H, int P, int R, int Q, bool need_states);
 // Carves cum / cs / states out of `workspace` (states only if p.states == NULL on entry) and runs

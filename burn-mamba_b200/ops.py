@@ -238,3 +238,55 @@ def ssd2_fwd_noalloc(x, dt, a, b, c, d=None, h0=None, chunk_len=256, dt_bias=Non
                             chunk_states=None)
     check(lib.bm_ssd2_fwd_noalloc(C.byref(args), _stream()), "bm_ssd2_fwd_noalloc")
     return y, h_final
+
+
+def ssd2_bwd(x, dt, a, b, c, d, h0, dy, dh_final=None, chunk_len=256):
+    """Mamba-2 SSD backward (recompute).  Returns dict(dx, ddt, da, db, dc, dd, dh0), all float32;
+    db / dc are per group."""
+    bsz, s, h, p = x.shape
+    g, r = b.shape[2], b.shape[3]
+    act = x.dtype
+    _chk(x, "x"); _chk(dt, "dt", torch.float32, (bsz, s, h)); _chk(a, "a", torch.float32, (h,))
+    _chk(b, "b", act, (bsz, s, g, r)); _chk(c, "c", act, (bsz, s, g, r)); _chk(dy, "dy", act, x.shape)
+    _chk(d, "d", torch.float32, (h,), optional=True); _chk(h0, "h0", torch.float32, (bsz, h, p, r), optional=True)
+    _chk(dh_final, "dh_final", torch.float32, (bsz, h, p, r), optional=True)
+    f = dict(dtype=torch.float32, device=x.device)
+    out = dict(dx=torch.empty((bsz, s, h, p), **f), ddt=torch.empty((bsz, s, h), **f), da=torch.empty((h,), **f),
+               db=torch.empty((bsz, s, g, r), **f), dc=torch.empty((bsz, s, g, r), **f),
+               dd=None if d is None else torch.empty((h,), **f), dh0=torch.empty((bsz, h, p, r), **f))
+    args = _ffi.Ssd2BwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, chunk_len=chunk_len,
+                            dtype=_DT[act], x=_ptr(x), dt=_ptr(dt), a=_ptr(a), b=_ptr(b), c=_ptr(c), d=_ptr(d),
+                            h0=_ptr(h0), dy=_ptr(dy), dh_final=_ptr(dh_final), dx=_ptr(out["dx"]), ddt=_ptr(out["ddt"]),
+                            da=_ptr(out["da"]), db=_ptr(out["db"]), dc=_ptr(out["dc"]), dd=_ptr(out["dd"]),
+                            dh0=_ptr(out["dh0"]))
+    ws = _workspace(lib.bm_ssd2_bwd_workspace_bytes(C.byref(args)), x.device)
+    check(lib.bm_ssd2_bwd(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_ssd2_bwd")
+    return out
+
+
+def ssd3_bwd(v, da, b, c, gamma, scale, h0, dy, dh_final=None, chunk_len=64, single=True):
+    """Mamba-3 SSD backward.  single: returns also dgamma / dscale.  All gradients float32."""
+    bsz, s, m, h, p = v.shape
+    r = b.shape[-1]
+    act = v.dtype
+    _chk(v, "v"); _chk(da, "da", torch.float32, (bsz, s, h)); _chk(b, "b", act, (bsz, s, m, h, r))
+    _chk(c, "c", act, (bsz, s, m, h, r)); _chk(dy, "dy", act, v.shape)
+    _chk(h0, "h0", torch.float32, (bsz, h, p, r), optional=True)
+    _chk(dh_final, "dh_final", torch.float32, (bsz, h, p, r), optional=True)
+    f = dict(dtype=torch.float32, device=v.device)
+    out = dict(dv=torch.empty((bsz, s, m, h, p), **f), dda=torch.empty((bsz, s, h), **f),
+               db=torch.empty((bsz, s, m, h, r), **f), dc=torch.empty((bsz, s, m, h, r), **f),
+               dh0=torch.empty((bsz, h, p, r), **f))
+    if single:
+        _chk(gamma, "gamma", torch.float32, (bsz, s, h)); _chk(scale, "scale", torch.float32, (bsz, s, h))
+        out.update(dgamma=torch.empty((bsz, s, h), **f), dscale=torch.empty((bsz, s, h), **f))
+    args = _ffi.Ssd3BwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, mimo_rank=m, chunk_len=chunk_len,
+                            dtype=_DT[act], v=_ptr(v), da=_ptr(da), b=_ptr(b), c=_ptr(c),
+                            gamma=_ptr(gamma) if single else None, scale=_ptr(scale) if single else None, h0=_ptr(h0),
+                            dy=_ptr(dy), dh_final=_ptr(dh_final), dv=_ptr(out["dv"]), dda=_ptr(out["dda"]),
+                            db=_ptr(out["db"]), dc=_ptr(out["dc"]), dgamma=_ptr(out.get("dgamma")),
+                            dscale=_ptr(out.get("dscale")), dh0=_ptr(out["dh0"]))
+    ws = _workspace(lib.bm_ssd3_bwd_workspace_bytes(C.byref(args)), v.device)
+    fn = lib.bm_ssd3_single_bwd if single else lib.bm_ssd3_double_bwd
+    check(fn(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_ssd3_bwd")
+    return out

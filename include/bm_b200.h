@@ -117,6 +117,40 @@ int32_t bm_workspace_status(const void* workspace, void* stream);
 int32_t bm_ssd2_fwd_noalloc(const bm_ssd2_fwd_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Mamba-2 chunked SSD backward (recompute: only the forward inputs are needed, no saved activations).
+ * Replaces combined_backward (src/mamba2/ssd/serial_recalculated/combined_backward.rs:126-590) behind the
+ * Autodiff impl of the slot (src/mamba2/ssd/serial_recalculated/backward.rs:29-321).
+ * Forward inputs as in bm_ssd2_fwd (dt already discretised: dt_bias fusion is not differentiated here);
+ * dy / dh_final are the upstream gradients of y and of the final state.  All gradients are float32.
+ * db / dc are per group: already summed over the heads of each group (the reference returns them per
+ * head and leaves that sum to the autodiff of its group->head expand, src/modules/misc/gqa.rs:30-56;
+ * pass ngroups = nheads with per-head B/C to get exactly the per-head tensors).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+    int32_t batch, seqlen, nheads, headdim, state_rank, ngroups, chunk_len;
+    int32_t dtype;            /* bm_dtype of x, b, c, dy */
+    const void* x;            /* [b, s, h, p] */
+    const float* dt;          /* [b, s, h] */
+    const float* a;           /* [h] */
+    const void* b;            /* [b, s, g, r] */
+    const void* c;            /* [b, s, g, r] */
+    const float* d;           /* [h] or NULL */
+    const float* h0;          /* [b, h, p, r] or NULL */
+    const void* dy;           /* [b, s, h, p] act dtype */
+    const float* dh_final;    /* [b, h, p, r] or NULL (zero) */
+    float* dx;                /* [b, s, h, p] */
+    float* ddt;               /* [b, s, h] */
+    float* da;                /* [h] */
+    float* db;                /* [b, s, g, r] */
+    float* dc;                /* [b, s, g, r] */
+    float* dd;                /* [h] or NULL */
+    float* dh0;               /* [b, h, p, r] */
+} bm_ssd2_bwd_args;
+
+size_t bm_ssd2_bwd_workspace_bytes(const bm_ssd2_bwd_args* args);
+int32_t bm_ssd2_bwd(const bm_ssd2_bwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Mamba-2 recurrent step: state update + readout for one token, state updated in place.
  * Replaces the body of Mamba2::step between the conv and the gated norm
  *   (src/mamba2/mamba2.rs:907-991): h = exp(dt A) h + dt B (x) x ; y = sum_r C h + D x.
@@ -230,6 +264,37 @@ typedef struct {
 size_t bm_ssd3_fwd_workspace_bytes(const bm_ssd3_fwd_args* args);
 int32_t bm_ssd3_single_fwd(const bm_ssd3_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
 int32_t bm_ssd3_double_fwd(const bm_ssd3_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Mamba-3 SSD backward (recompute).  bm_ssd3_single_bwd replaces combined_backward of the single-pass core
+ * (src/mamba3/single_ssd/ssd/serial_recalculated/combined_backward.rs:74-536: gradients for v, da, b, c,
+ * gamma, scale, h0), bm_ssd3_double_bwd the generic core's
+ * (src/mamba3/double_ssd/ssd/serial_recalculated/combined_backward.rs:98; dgamma / dscale unused).
+ * B and C are the rotated per-head tensors (the rotation is differentiated outside the slot, as in the
+ * reference).  All gradients float32. */
+typedef struct {
+    int32_t batch, seqlen, nheads, headdim, state_rank, mimo_rank, chunk_len;
+    int32_t dtype;            /* bm_dtype of v, b, c, dy */
+    const void* v;            /* [b, s, m, h, p] */
+    const float* da;          /* [b, s, h] */
+    const void* b;            /* [b, s, m, h, r] */
+    const void* c;            /* [b, s, m, h, r] */
+    const float* gamma;       /* [b, s, h] (single) */
+    const float* scale;       /* [b, s, h] (single) */
+    const float* h0;          /* [b, h, p, r] or NULL */
+    const void* dy;           /* [b, s, m, h, p] */
+    const float* dh_final;    /* [b, h, p, r] or NULL */
+    float* dv;                /* [b, s, m, h, p] */
+    float* dda;               /* [b, s, h] */
+    float* db;                /* [b, s, m, h, r] */
+    float* dc;                /* [b, s, m, h, r] */
+    float* dgamma;            /* [b, s, h] (single) */
+    float* dscale;            /* [b, s, h] (single) */
+    float* dh0;               /* [b, h, p, r] */
+} bm_ssd3_bwd_args;
+
+size_t bm_ssd3_bwd_workspace_bytes(const bm_ssd3_bwd_args* args);
+int32_t bm_ssd3_single_bwd(const bm_ssd3_bwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
+int32_t bm_ssd3_double_bwd(const bm_ssd3_bwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Cumulative rotation angles (Complex2D), replacing the angle part of rotate_bc_forward
  * (src/mamba3/rotation/mod.rs:653-679, increment :559-567):

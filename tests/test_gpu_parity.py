@@ -316,3 +316,47 @@ def test_ssd2_tensor_path_strong_decay_is_finite(bm):
     cfg["a"] = np.float32([-16.0, -0.001])
     y, hf = _ssd2_case(bm, cfg, 256, torch.bfloat16, path="tensor", check_status=True)
     assert torch.isfinite(y.float()).all() and torch.isfinite(hf).all()
+
+
+# ------------------------------------------------------------------ backward (recompute) vs autodiff oracle
+def _grad_close(got, want, tol=1e-3):
+    """The reference's gradient tolerance is max-abs 1e-3 at its tiny shapes; relative-L2 here."""
+    return rel_l2(host(got), want) <= tol
+
+
+@pytest.mark.parametrize("b,s,h,p,r,g,Q", [(2, 12, 4, 8, 8, 1, 4), (2, 10, 4, 8, 8, 2, 4), (1, 70, 2, 16, 32, 1, 32),
+                                           (1, 96, 2, 64, 128, 1, 64), (1, 33, 3, 8, 16, 3, 16)])
+def test_ssd2_backward_matches_autodiff_oracle(bm, b, s, h, p, r, g, Q):
+    """Recompute backward == autodiff of the serial forward
+    (src/mamba2/ssd/ssd_path/tests.rs:184-336 asserts the same on all seven inputs)."""
+    from oracle import backward
+    cfg = inputs.ssd2_prefill(seed=300 + s, batch=b, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, h0_std=0.2)
+    rng = np.random.default_rng(1)
+    dy = rng.standard_normal(cfg["x"].shape).astype(np.float32)
+    dhf = rng.standard_normal(cfg["h0"].shape).astype(np.float32)
+    want = backward.ssd2_grads(cfg["x"], cfg["dt"], cfg["a"], cfg["b"], cfg["c"], cfg["d"], cfg["h0"], dy, dhf, Q)
+    got = bm.ops.ssd2_bwd(dev(cfg["x"]), dev(cfg["dt"]), dev(cfg["a"]), dev(cfg["b"]), dev(cfg["c"]), dev(cfg["d"]),
+                          dev(cfg["h0"]), dev(dy), dev(dhf), chunk_len=Q)
+    torch.cuda.synchronize()
+    for k in ("dx", "ddt", "da", "db", "dc", "dd", "dh0"):
+        assert _grad_close(got[k], want[k]), (k, rel_l2(host(got[k]), want[k]))
+
+
+@pytest.mark.parametrize("b,s,h,p,r,m,Q", [(2, 12, 2, 8, 8, 1, 4), (2, 10, 2, 8, 8, 2, 4), (1, 40, 2, 16, 32, 3, 16),
+                                           (1, 64, 2, 64, 128, 4, 32)])
+def test_ssd3_backward_matches_autodiff_oracle(bm, b, s, h, p, r, m, Q):
+    """src/mamba3/single_ssd/ssd/ssd_path/tests.rs:175-339 (incl. d_gamma, d_scale) and the generic core."""
+    from oracle import backward
+    cfg = inputs.ssd3_single(seed=60 + s, batch=b, seqlen=s, nheads=h, headdim=p, state_rank=r, mimo_rank=m, h0_std=0.2)
+    rng = np.random.default_rng(2)
+    dy = rng.standard_normal(cfg["v"].shape).astype(np.float32)
+    dhf = rng.standard_normal(cfg["h0"].shape).astype(np.float32)
+    args = (cfg["v"], cfg["da"], cfg["b"], cfg["c"], cfg["gamma"], cfg["scale"], cfg["h0"])
+    want = backward.ssd3_grads(*args, dy, dhf, Q, single=True)
+    got = bm.ops.ssd3_bwd(*(dev(t) for t in args), dev(dy), dev(dhf), chunk_len=Q, single=True)
+    for k in ("dv", "dda", "db", "dc", "dgamma", "dscale", "dh0"):
+        assert _grad_close(got[k], want[k]), ("single", k, rel_l2(host(got[k]), want[k]))
+    want = backward.ssd3_grads(*args, dy, dhf, Q, single=False)
+    got = bm.ops.ssd3_bwd(*(dev(t) for t in args), dev(dy), dev(dhf), chunk_len=Q, single=False)
+    for k in ("dv", "dda", "db", "dc", "dh0"):
+        assert _grad_close(got[k], want[k]), ("double", k, rel_l2(host(got[k]), want[k]))
