@@ -1,0 +1,90 @@
+"""Block-level GPU parity through the reference-shaped host interface (Mamba2.forward / step,
+Mamba2SsdInput.run): the CPU-runnable benchmark configuration and the forward == step property."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mamba2 as o2
+from oracle.numerics import rel_l2, bf16_round
+
+pytestmark = pytest.mark.gpu
+
+
+def _block(bm, w, dtype=torch.float32):
+    t = lambda a, dt=None: torch.from_numpy(np.ascontiguousarray(a)).cuda().to(dt or torch.float32)
+    return bm.Mamba2(t(w.w_in, dtype), t(w.conv_w), t(w.conv_b), t(w.dt_bias), t(w.a_log), t(w.d), t(w.norm_gamma, dtype),
+                     t(w.w_out, dtype), nheads=w.nheads, state_rank=w.state_rank, ngroups=w.ngroups)
+
+
+def test_cpu_runnable_configuration_block_forward_fp32(bm):
+    """'Mamba-2 single SSM block forward, fp32, seed 0': d_model 256, d_inner 512, P 64 (H 8), N 64, G 1, Q 64,
+    batch 2, L 512; compare output (2,512,256) and final SSM state (2,8,64,64) at rel-L2 <= 1e-4."""
+    rng = np.random.Generator(np.random.PCG64(0))
+    w = o2.Mamba2Weights(rng, d_model=256, d_inner=512, nheads=8, state_rank=64, ngroups=1, dtype=np.float32)
+    u = rng.standard_normal((2, 512, 256), dtype=np.float32)
+    conv0 = np.zeros((2, w.conv_dim, 4), np.float32)
+    ssm0 = np.zeros((2, 8, 64, 64), np.float32)
+    want_out, want_conv, want_state, pre = o2.block_forward(w, u.astype(np.float64), conv0.astype(np.float64),
+                                                            ssm0.astype(np.float64), chunk_len=64, dtype_name="f32")
+    blk = _block(bm, w)
+    out, cache = blk.forward(torch.from_numpy(u).cuda(), None, bm.Mamba2SsdPath.serial_recalculated(64), kernel_path="exact")
+    assert rel_l2(out.cpu().numpy(), want_out) <= 1e-4
+    assert rel_l2(cache.ssm_bhpr.cpu().numpy(), want_state) <= 1e-4
+    assert rel_l2(cache.conv_bvk.cpu().numpy(), want_conv) <= 1e-5
+    # the slot alone, fed the oracle's pre-SSD tensors through the reference-shaped input bundle
+    f = lambda a: torch.from_numpy(np.ascontiguousarray(a.astype(np.float32))).cuda()
+    inp = bm.Mamba2SsdInput(f(pre["x"]).reshape(2, 8, 64, 8, 64), f(pre["dt"]).reshape(2, 8, 64, 8), f(pre["a"]),
+                            f(pre["b"]).reshape(2, 8, 64, 1, 64), f(pre["c"]).reshape(2, 8, 64, 1, 64), f(w.d),
+                            f(ssm0))
+    y, hf = inp.run(bm.Mamba2SsdPath.serial_recalculated(64), kernel_path="exact")
+    assert rel_l2(y.reshape(2, 512, 8, 64).cpu().numpy(), pre["y"]) <= 1e-4
+    assert rel_l2(hf.cpu().numpy(), want_state) <= 1e-4
+    with pytest.raises(AssertionError):   # serial variants reject a learnable init state (serial.rs:48-51)
+        inp.init_state_hpr = f(np.zeros((8, 64, 64)))
+        inp.run(bm.Mamba2SsdPath.serial(64))
+
+
+@pytest.mark.parametrize("g", [1, 2])
+def test_block_forward_equals_unrolled_step_and_split(bm, g):
+    """forward == unrolled step on output, conv window and SSM state (src/mamba2/mamba2/tests.rs:202-252, tolerance
+    1e-4 max-abs), split == full (:343-392), with a random initial cache (:290-328), CUDA vs CUDA."""
+    rng = np.random.Generator(np.random.PCG64(5))
+    w = o2.Mamba2Weights(rng, d_model=32, d_inner=64, nheads=4, state_rank=16, ngroups=g, dtype=np.float32)
+    blk = _block(bm, w)
+    bsz, s = 2, 21
+    u = torch.from_numpy(rng.standard_normal((bsz, s, 32), dtype=np.float32)).cuda()
+    c0 = bm.Mamba2Cache(0.1 * torch.randn(bsz, w.conv_dim, 4, device="cuda"), 0.1 * torch.randn(bsz, 4, 16, 16, device="cuda"))
+    clone = lambda c: bm.Mamba2Cache(c.conv_bvk.clone(), c.ssm_bhpr.clone())
+    out, cache = blk.forward(u, clone(c0), bm.Mamba2SsdPath.serial_recalculated(8), kernel_path="exact")
+    c = clone(c0)
+    for t in range(s):
+        o, c = blk.step(u[:, t].contiguous(), c)
+        assert torch.max(torch.abs(o - out[:, t])).item() <= 1e-4
+    assert torch.max(torch.abs(c.ssm_bhpr - cache.ssm_bhpr)).item() <= 1e-4
+    assert torch.max(torch.abs(c.conv_bvk - cache.conv_bvk)).item() <= 1e-5
+    o1, c1 = blk.forward(u[:, :9].contiguous(), clone(c0), bm.Mamba2SsdPath.serial_recalculated(8), kernel_path="exact")
+    o2_, c2 = blk.forward(u[:, 9:].contiguous(), c1, bm.Mamba2SsdPath.serial_recalculated(8), kernel_path="exact")
+    assert torch.max(torch.abs(torch.cat([o1, o2_], 1) - out)).item() <= 1e-4
+    assert torch.max(torch.abs(c2.ssm_bhpr - cache.ssm_bhpr)).item() <= 1e-4
+
+
+def test_decode_prefix_equals_forward_at_the_2_7b_head_shape(bm):
+    """'Mamba-2 recurrent step() decode ... check the outputs equal the matching positions of forward() on the same
+    128-token prefix' -- one layer at the 2.7B head shape (P 64, N 128) with a reduced width (H 8, batch 4) so the
+    test stays small; bf16 activations, tensor-core prefill vs step kernels, initial cache ~ N(0, 0.1)."""
+    rng = np.random.Generator(np.random.PCG64(3))
+    w = o2.Mamba2Weights(rng, d_model=256, d_inner=512, nheads=8, state_rank=128, ngroups=1, dtype=np.float32)
+    blk = _block(bm, w, torch.bfloat16)
+    bsz, s = 4, 128
+    u = torch.from_numpy(rng.standard_normal((bsz, s, 256), dtype=np.float32)).cuda().to(torch.bfloat16)
+    c0 = bm.Mamba2Cache(0.1 * torch.randn(bsz, w.conv_dim, 4, device="cuda"), 0.1 * torch.randn(bsz, 8, 64, 128, device="cuda"))
+    clone = lambda c: bm.Mamba2Cache(c.conv_bvk.clone(), c.ssm_bhpr.clone())
+    out, cache = blk.forward(u, clone(c0), bm.Mamba2SsdPath.serial_recalculated(256), kernel_path="tensor")
+    c = clone(c0)
+    steps = []
+    for t in range(s):
+        o, c = blk.step(u[:, t].contiguous(), c)
+        steps.append(o)
+    got = torch.stack(steps, 1)
+    assert rel_l2(got.float().cpu().numpy(), out.float().cpu().numpy()) <= 2e-2
+    assert rel_l2(c.ssm_bhpr.cpu().numpy(), cache.ssm_bhpr.cpu().numpy()) <= 2e-2
