@@ -125,11 +125,18 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
         *abort_flag = 1;                                     \
         goto done;                                           \
     } while (0)
-// Bounded wait used by single-thread roles.
-#define BM_WAIT(bar, par)                                    \
-    do {                                                     \
-        if (!mbar_wait((bar), (par))) BM_ABORT();            \
-        if (*abort_flag) goto done;                          \
+// Bounded wait used by single-thread roles (out of line, like wait_warp below).
+__device__ __noinline__ bool wait_one(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, int* status) {
+    if (!mbar_wait(bar, parity)) {
+        atomicExch(status, (int)BM_ERR_TIMEOUT);
+        *abort_flag = 1;
+        return false;
+    }
+    return *abort_flag == 0;
+}
+#define BM_WAIT(bar, par)                                                 \
+    do {                                                                  \
+        if (!wait_one((bar), (par), abort_flag, prm.status)) goto done;   \
     } while (0)
 // Bounded wait executed by a whole warp; the leave/stay decision is made warp-uniform so that no lane
 // is left behind at a later __syncwarp or .aligned tcgen05 instruction.  Kept out of line: the kernel
@@ -204,9 +211,32 @@ __device__ __forceinline__ void mask_block(const uint32_t (&r)[32], uint32_t (&o
     }
 }
 
+// clamp(softplus(x)) of the fused dt path (src/mamba2/mamba2.rs:692-697); out of line: rarely used
+__device__ __noinline__ float dt_activation(float x, float lo, float hi) { return fminf(fmaxf(softplus_f32(x), lo), hi); }
+
+// Walks this CTA's tiles in order: units blockIdx.x, blockIdx.x + gridDim.x, ... and the tiles of each unit.
+// Divisions happen only at unit boundaries.
+struct TileWalk {
+    int i, unit, b, h, tpu, H, stride;
+    __device__ __forceinline__ TileWalk(int tpu_, int H_) : i(0), unit(blockIdx.x), tpu(tpu_), H(H_), stride(gridDim.x) {
+        b = unit / H;
+        h = unit % H;
+    }
+    __device__ __forceinline__ void next() {
+        if (++i == tpu) {
+            i = 0;
+            unit += stride;
+            b = unit / H;
+            h = unit % H;
+        }
+    }
+};
+
 __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_constant__ Params prm) {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    // 1024-byte aligned base, formed as an offset on the __shared__ array so that the compiler keeps the
+    // shared address space (32-bit LDS / STS) for everything derived from it
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kOffBar);
     volatile uint32_t* abort_flag = &bars->abort_flag;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -262,10 +292,10 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             tma_prefetch_desc(&prm.tm_b);
             tma_prefetch_desc(&prm.tm_c);
             tma_prefetch_desc(&prm.tm_y);
-            for (int it = 0; it < total; ++it) {
-                const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
-                const int b = unit / prm.H, h = unit % prm.H, g = h / hpg;
-                const int st = it & 1, s0 = i * T;
+            TileWalk tw(tpu, prm.H);
+            for (int it = 0; it < total; ++it, tw.next()) {
+                const int b = tw.b, h = tw.h, g = h / hpg;
+                const int st = it & 1, s0 = tw.i * T;
                 // C + B stage: released once CB, Y2 and S of the tile two back have completed
                 BM_WAIT(&bars->cbld_empty[st], ((it >> 1) & 1) ^ 1);
                 BM_TRACE(0, it, 0);
@@ -305,10 +335,10 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     umma_commit(&bars->cbld_empty[st]);
                 }
                 if (it >= 0) {
-                    const int st = it & 1, cst = it % kCumStages;
+                    const int st = it & 1, cst = (it & (kCumStages - 1));
                     BM_WAIT(&bars->xld_full[st], (it >> 1) & 1);
                     BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
-                    BM_WAIT(&bars->cum_full[cst], (it / kCumStages) & 1);
+                    BM_WAIT(&bars->cum_full[cst], (it >> 2) & 1);
                     BM_WAIT(&bars->y1_empty, (it & 1) ^ 1);
                     BM_WAIT(&bars->p_ready[st], (it >> 1) & 1);
                     BM_TRACE(1, it, 1);
@@ -364,11 +394,11 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // ------------------------------------------------------------------ decay scan of dt
         // log2-domain cumulative sum of dt*A over the tile, plus the derived per-token factors.
         const float log2e = 1.4426950408889634f;
-        for (int it = 0; it < total; ++it) {
-            const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
-            const int b = unit / prm.H, h = unit % prm.H;
-            const int cst = it % kCumStages;
-            BM_WAIT_WARP(&bars->cum_empty[cst], ((it / kCumStages) & 1) ^ 1);
+        TileWalk tw(tpu, prm.H);
+        for (int it = 0; it < total; ++it, tw.next()) {
+            const int b = tw.b, h = tw.h, i = tw.i;
+            const int cst = (it & (kCumStages - 1));
+            BM_WAIT_WARP(&bars->cum_empty[cst], ((it >> 2) & 1) ^ 1);
             float* cum2 = reinterpret_cast<float*>(smem + kOffCum + cst * kCumStageBytes);
             float *dtv = cum2 + T, *erow = cum2 + 2 * T, *wv = cum2 + 3 * T, *colf = cum2 + 4 * T;
             const float ah = prm.a[h] * log2e;
@@ -381,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 float v = 0.f;
                 if (s < prm.S) {
                     v = prm.dt[((int64_t)b * prm.S + s) * prm.H + h];
-                    if (prm.dt_bias) v = fminf(fmaxf(softplus_f32(v + bias), prm.dt_min), prm.dt_max);
+                    if (prm.dt_bias) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
                 }
                 d4[k] = v;
                 run += v * ah;
@@ -416,14 +446,14 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // ------------------------------------------------------------------ mask pass: CB -> P
         const int q = warp & 3, t = q * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
-        for (int it = 0; it < total; ++it) {
-            const int unit = blockIdx.x + (it / tpu) * gridDim.x;
-            const int st = it & 1, cst = it % kCumStages;
+        TileWalk tw(tpu, prm.H);
+        for (int it = 0; it < total; ++it, tw.next()) {
+            const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + T, *colf = cum2 + 4 * T;
-            const float dskip = prm.d ? prm.d[unit % prm.H] : 0.f;
+            const float dskip = prm.d ? prm.d[tw.h] : 0.f;
             BM_TRACE(4, it, 0);
-            BM_WAIT_WARP(&bars->cum_full[cst], (it / kCumStages) & 1);
+            BM_WAIT_WARP(&bars->cum_full[cst], (it >> 2) & 1);
             BM_WAIT_WARP(&bars->cb_full[st], (it >> 1) & 1);
             BM_TRACE(4, it, 1);
             tc_fence_after();
@@ -462,7 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         float hst[P];
         auto scale_x = [&](int it) {
             // Xw = X * dt * exp(cum_end - cum) for tile `it` (rows keep their swizzled positions)
-            const int st = it & 1, cst = it % kCumStages;
+            const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* wv = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 3 * T;
             const unsigned char* xs = smem + kOffX + st * kPanel;
             unsigned char* xw = smem + kOffXw + st * kPanel;
@@ -502,11 +532,12 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         };
         // Iteration `it` publishes the state entering tile it, scales the X tile of tile it+1 (one
         // tile ahead, so S(it+1) can be issued early) and then folds S(it) into the state.
+        TileWalk tw(tpu, prm.H);
         for (int it = -1; it < total; ++it) {
+            if (it > 0) tw.next();
             const int itc = it < 0 ? 0 : it;
-            const int unit = blockIdx.x + (itc / tpu) * gridDim.x, i = itc % tpu;
-            const int b = unit / prm.H, h = unit % prm.H;
-            const int cst = itc % kCumStages;
+            const int i = tw.i, b = tw.b, h = tw.h;
+            const int cst = (itc & (kCumStages - 1));
             const float* erow = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 2 * T;
             const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
             if (it >= 0) {
@@ -530,7 +561,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 // scaled X of the next tile: its buffer was last read by S(it-1) (observed through
                 // s_full in the previous iteration) and, as y staging tile, by the store of tile it-1
                 BM_WAIT_WARP(&bars->xld_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
-                BM_WAIT_WARP(&bars->cum_full[(it + 1) % kCumStages], ((it + 1) / kCumStages) & 1);
+                BM_WAIT_WARP(&bars->cum_full[((it + 1) & (kCumStages - 1))], ((it + 1) >> 2) & 1);
                 BM_WAIT_WARP(&bars->ystage_free[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
                 BM_TRACE(5, itc, 0);
                 scale_x(it + 1);
@@ -569,13 +600,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // completed) and written with one TMA store per warp (its own 32 rows).
         const int q = warp & 3, t = q * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
-        for (int it = 0; it < total; ++it) {
-            const int unit = blockIdx.x + (it / tpu) * gridDim.x, i = it % tpu;
-            const int b = unit / prm.H, h = unit % prm.H;
-            const int st = it & 1, cst = it % kCumStages;
+        TileWalk tw(tpu, prm.H);
+        for (int it = 0; it < total; ++it, tw.next()) {
+            const int i = tw.i, b = tw.b, h = tw.h;
+            const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* erow = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 2 * T;
             unsigned char* ys = smem + kOffXw + st * kPanel;
-            BM_WAIT_WARP(&bars->cum_full[cst], (it / kCumStages) & 1);
+            BM_WAIT_WARP(&bars->cum_full[cst], (it >> 2) & 1);
             const float e = erow[t];
             // row factor of the factored mask: exp2(cum_t - cend); 1 for exact tiles
             const float* cum2 = erow - 2 * T;
