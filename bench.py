@@ -50,33 +50,78 @@ def measured_peak_hbm():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+    """Samples SM clocks and clock-event reasons of one GPU while the timed region runs (read-only).
+    The samples come from NVML inside this process: a separate nvidia-smi polling loop was seen to hold
+    driver locks for tens of milliseconds at a time, which stalled the kernel launches it was meant to
+    observe.  nvidia-smi is only the fallback when the NVML binding is missing."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, uuid=None, period_s=0.02):
+        self.index, self.uuid, self.period = index, uuid, period_s
+        self.rows, self.proc, self.thread, self.stop_flag, self.source = [], None, None, False, None
 
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-            # nvidia-smi holds driver-wide locks while it starts up, which stalls kernel launches of this
-            # process: wait for its first sample so that only its steady-state polling overlaps the timing
-            t0 = time.time()
-            while not self.rows and time.time() - t0 < 10.0:
-                time.sleep(0.05)
-            self.warm = len(self.rows)
-        except Exception:
-            self.proc = None
+    # -- NVML in-process ---------------------------------------------------------------------
+    def _nvml_loop(self, nv, handle):
+        bits = [nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown,
+                nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap]
+        mx = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+        while not self.stop_flag:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                self.rows.append([sm, mx] + ["Active" if mask & b else "Not Active" for b in bits])
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def _start_nvml(self):
+        import pynvml as nv
+        nv.nvmlInit()
+        handle = None
+        if self.uuid:
+            try:
+                handle = nv.nvmlDeviceGetHandleByUUID(("GPU-" + self.uuid).encode())
+            except Exception:
+                handle = None
+        if handle is None:
+            handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+        nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)   # fail here, not in the thread
+        self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+        self.thread.start()
+        self.source = "nvml"
+
+    # -- nvidia-smi fallback -----------------------------------------------------------------
+    def _start_smi(self):
+        self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE,
+                                     stderr=subprocess.DEVNULL, text=True)
+        threading.Thread(target=self._read, daemon=True).start()
+        self.source = "nvidia-smi"
 
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([p.strip() for p in line.split(",")])
 
+    def start(self):
+        try:
+            try:
+                self._start_nvml()
+            except Exception:
+                self._start_smi()
+            # the first sample marks the end of the sampler's own start-up work
+            t0 = time.time()
+            while not self.rows and time.time() - t0 < 10.0:
+                time.sleep(0.02)
+            self.warm = len(self.rows)
+        except Exception:
+            self.proc = None
+
     def stop(self):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -84,19 +129,18 @@ class ClockSampler:
             except Exception:
                 pass
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows[getattr(self, "warm", 0):] or self.rows:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
-                for n, v in zip(names, r[2:6]):
-                    if v.lower().startswith("active"):
+                for n, v in zip(self.NAMES, r[2:6]):
+                    if str(v).lower().startswith("active"):
                         reasons.add(n)
             except Exception:
                 continue
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": self.source}
 
 
 def make_inputs(torch, seed, c):
@@ -172,11 +216,31 @@ def run_ours(args):
     # device status of the tensor-core kernel (bounded waits) -- checked once, outside the timed region
     y, hf = bm.ops.ssd2_fwd(devt["x"], devt["dt"], devt["a"], devt["b"], devt["c"], devt["d"], None,
                             chunk_len=c["chunk_len"], path="auto", check_status=True)
-    sampler = ClockSampler(local)
+    try:
+        gpu_uuid = str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local, gpu_uuid)
+    # reference point without any sampler running: a timed region several times slower than this is a
+    # disturbed measurement (launches stalled behind a driver lock), which is taken once more and reported
+    quick_ms = timed(step_resident, 10) / 10
     if rank == 0:
         sampler.start()
     ms = timed(step_resident, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    remeasured = None
+    if ms / args.steps > 2.5 * quick_ms:
+        remeasured = {"first_ms_per_step": ms / args.steps, "undisturbed_ms_per_step": quick_ms,
+                      "reason": "timed region >2.5x slower than the same launches without the clock sampler"}
+        sampler = ClockSampler(local, gpu_uuid, period_s=0.05)
+        if rank == 0:
+            sampler.start()
+        ms = timed(step_resident, args.steps)
+        clocks = sampler.stop() if rank == 0 else None
+    # a bounded wait that ran out during the timed launches would have left its code in the workspace
+    st = bm.ops.last_workspace_status()
+    if st != 0:
+        raise RuntimeError(f"tensor-core kernel reported status {st} during the timed region")
     e2e_steps = max(1, min(args.steps, 10))
     if args.profile:  # kernel-only run for ncu captures: no end-to-end leg, no CPU arm
         ms_e2e = float("nan")
@@ -204,6 +268,7 @@ def run_ours(args):
                 "steps": e2e_steps},
         "gpu_launches": args.steps,
         "clocks": clocks,
+        "remeasured": remeasured,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": f"{peak_src} (MEASURED_PEAKS.json hbm_gbs)", "algorithmic_bytes": abytes,
                      "traffic": TRAFFIC_BYTES_PER_LAUNCH},

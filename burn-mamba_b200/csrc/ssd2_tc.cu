@@ -32,7 +32,6 @@ constexpr int P = 64;         // head dim
 constexpr int R = 128;        // state rank
 constexpr int kThreads = 512;
 constexpr int kCumStages = 4;
-constexpr uint32_t kPollBudget = 1u << 24;
 // Tiles whose total log2 decay |cend| stays below this use the factored mask: every factor
 // exp2(+-cend) then stays far inside the float32 / bfloat16 exponent range.
 constexpr float kFactoredMaxLog2Decay = 100.f;  // non-blocking polls of an idle issuer before it gives up (~ seconds)
@@ -103,9 +102,44 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// Packed pairs of float32 (one instruction for two lanes of math; halves the code of the unrolled loops).
+__device__ __forceinline__ uint64_t pair_f32(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t pair_u32(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2_pair(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return pack_bf16x2(lo, hi);
+}
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
+
+// Descriptor of the same operand `bytes` further on (the start-address field counts 16-byte units and
+// never carries out of its field for addresses inside one CTA's shared memory).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
 
 // Optional timeline instrumentation (development builds only, -DBM_SSD2_TRACE): CTA 0 records
 // clock64() at role milestones of its first tiles into prm.trace[role][tile][event].
@@ -119,94 +153,71 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
 #define BM_TRACE(role, it, ev) do { } while (0)
 #endif
 
-#define BM_ABORT()                                           \
-    do {                                                     \
-        atomicExch(prm.status, (int)BM_ERR_TIMEOUT);         \
-        *abort_flag = 1;                                     \
-        goto done;                                           \
+// Bounded waits, inline: a short try_wait loop with an iteration budget.  A wait that runs out of budget
+// leaves through the `timed_out` label at the end of the kernel, which records BM_ERR_TIMEOUT and raises
+// the CTA's abort flag.  (Calls into an out-of-line wait cost the single-thread roles more than the wait
+// itself: their code is executed once per tile and every jump is a fresh instruction fetch.)
+#define BM_WAIT(bar, par)                                          \
+    do {                                                           \
+        uint32_t n_ = 0;                                           \
+        _Pragma("unroll 1")                                        \
+        while (!mbar_try_wait((bar), (par)))                       \
+            if (++n_ >= kWaitBudget) goto timed_out;               \
     } while (0)
-// Bounded wait used by single-thread roles (out of line, like wait_warp below).
-__device__ __noinline__ bool wait_one(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, int* status) {
-    if (!mbar_wait(bar, parity)) {
-        atomicExch(status, (int)BM_ERR_TIMEOUT);
-        *abort_flag = 1;
-        return false;
-    }
-    return *abort_flag == 0;
-}
-#define BM_WAIT(bar, par)                                                 \
-    do {                                                                  \
-        if (!wait_one((bar), (par), abort_flag, prm.status)) goto done;   \
-    } while (0)
-// Bounded wait executed by a whole warp; the leave/stay decision is made warp-uniform so that no lane
-// is left behind at a later __syncwarp or .aligned tcgen05 instruction.  Kept out of line: the kernel
-// has many wait sites and its hot loops should stay resident in the instruction cache.
-__device__ __noinline__ bool wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, int* status) {
-    const bool ok = mbar_wait(bar, parity);
-    const bool ab = *abort_flag != 0;
-    if (!__all_sync(0xffffffffu, ok && !ab)) {
-        if (!ok) {
-            atomicExch(status, (int)BM_ERR_TIMEOUT);
-            *abort_flag = 1;
-        }
-        return false;
-    }
-    return true;
-}
-#define BM_WAIT_WARP(bar, par)                                            \
-    do {                                                                  \
-        if (!wait_warp((bar), (par), abort_flag, prm.status)) goto done;  \
+// The same for a whole warp; the leave/stay decision is made warp-uniform so that no lane is left behind
+// at a later __syncwarp or .aligned tcgen05 instruction.
+#define BM_WAIT_WARP(bar, par)                                     \
+    do {                                                           \
+        uint32_t n_ = 0;                                           \
+        bool ok_ = true;                                           \
+        _Pragma("unroll 1")                                        \
+        while (!mbar_try_wait((bar), (par)))                       \
+            if (++n_ >= kWaitBudget) {                             \
+                ok_ = false;                                       \
+                break;                                             \
+            }                                                      \
+        if (!__all_sync(0xffffffffu, ok_)) goto timed_out;         \
     } while (0)
 
 // One 32-column block of the decay mask: out = bf16 pairs of P for columns [32c, 32c + 32).
 // Exact form (any decay): the kernel exp(cum_t - cum_s) dt_s is applied here.
 //   below the diagonal block:  rowfac * colf[s]   (both factors <= 1, reference = end of column block)
-//   diagonal block:            exp2(cum_t - cum_s) dt_s for s <= t, 0 above (the reference's -inf fill),
-//                              plus the skip weight D at s == t (y += D x rides along in P X)
+//   diagonal block:            exp2(cum_t - cum_s) dt_s, then the causal bit mask (the reference's -inf fill)
 // Factored form (tiles whose total decay stays far inside the float32 exponent range): the whole
 // kernel factors as exp2(cum_t - cend) * [dt_s exp2(cend - cum_s)]; the column factor is already in
-// the scaled tile Xw and the row factor is applied in the epilogue, so P is just the causally masked
-// CB (plus D / dt_t on the diagonal, which the two factors turn back into D).
+// the scaled tile Xw and the row factor is applied in the epilogue, so P is just the causally masked CB.
+// causal[j] keeps the halves of pair j at or below the diagonal (it depends on the lane only).
+// The skip term D x is added by the epilogue in both forms.
 __device__ __forceinline__ void mask_block(const uint32_t (&r)[32], uint32_t (&out)[16], bool factored, bool diagonal, int c,
-                                           int t, float ct, float dskip, const float* cum2, const float* dtv,
-                                           const float* colf) {
+                                           float ct, const float* cum2, const float* dtv, const float* colf,
+                                           const uint32_t (&causal)[16]) {
     if (factored) {
         if (!diagonal) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) out[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
         } else {
-            const float dt_t = dtv[t];
-            const float dd = dt_t > 0.f ? dskip / dt_t : 0.f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int s0 = c * 32 + 2 * j, s1 = s0 + 1;
-                float m0 = s0 <= t ? __uint_as_float(r[2 * j]) : 0.f;
-                float m1 = s1 <= t ? __uint_as_float(r[2 * j + 1]) : 0.f;
-                if (s0 == t) m0 += dd;
-                if (s1 == t) m1 += dd;
-                out[j] = pack_bf16x2(m0, m1);
-            }
+            for (int j = 0; j < 16; ++j)
+                out[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])) & causal[j];
         }
     } else if (!diagonal) {
         const float rf = ex2(ct - cum2[c * 32 + 31]);
+        const uint64_t rf2 = pair_f32(rf, rf);
+        const uint64_t* cf = reinterpret_cast<const uint64_t*>(colf + c * 32);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float2 cf = *reinterpret_cast<const float2*>(colf + c * 32 + 2 * j);
-            out[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * (rf * cf.x), __uint_as_float(r[2 * j + 1]) * (rf * cf.y));
-        }
+        for (int j = 0; j < 16; ++j) out[j] = pack_bf16x2_pair(mul2(pair_u32(r[2 * j], r[2 * j + 1]), mul2(rf2, cf[j])));
     } else {
+        const uint64_t ct2 = pair_f32(ct, ct), neg1 = pair_f32(-1.f, -1.f);
+        const uint64_t* cs = reinterpret_cast<const uint64_t*>(cum2 + c * 32);
+        const uint64_t* ds = reinterpret_cast<const uint64_t*>(dtv + c * 32);
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const int s0 = c * 32 + 2 * j, s1 = s0 + 1;
-            const float2 cs = *reinterpret_cast<const float2*>(cum2 + s0);
-            const float2 ds = *reinterpret_cast<const float2*>(dtv + s0);
-            const float a0 = s0 <= t ? ct - cs.x : -INFINITY;
-            const float a1 = s1 <= t ? ct - cs.y : -INFINITY;
-            float m0 = __uint_as_float(r[2 * j]) * (ex2(a0) * ds.x);
-            float m1 = __uint_as_float(r[2 * j + 1]) * (ex2(a1) * ds.y);
-            if (s0 == t) m0 += dskip;
-            if (s1 == t) m1 += dskip;
-            out[j] = pack_bf16x2(m0, m1);
+            // above the diagonal the exponent is positive and may overflow; the bit mask clears whatever
+            // comes out of it
+            float a0, a1;
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(fma2(cs[j], neg1, ct2)));
+            const uint64_t w = mul2(pair_f32(ex2(a0), ex2(a1)), ds[j]);
+            out[j] = pack_bf16x2_pair(mul2(pair_u32(r[2 * j], r[2 * j + 1]), w)) & causal[j];
         }
     }
 }
@@ -217,17 +228,22 @@ __device__ __noinline__ float dt_activation(float x, float lo, float hi) { retur
 // Walks this CTA's tiles in order: units blockIdx.x, blockIdx.x + gridDim.x, ... and the tiles of each unit.
 // Divisions happen only at unit boundaries.
 struct TileWalk {
-    int i, unit, b, h, tpu, H, stride;
-    __device__ __forceinline__ TileWalk(int tpu_, int H_) : i(0), unit(blockIdx.x), tpu(tpu_), H(H_), stride(gridDim.x) {
-        b = unit / H;
-        h = unit % H;
+    int i, b, h, tpu, H, db, dh;
+    __device__ __forceinline__ TileWalk(int tpu_, int H_) : i(0), tpu(tpu_), H(H_) {
+        b = (int)blockIdx.x / H;
+        h = (int)blockIdx.x % H;
+        db = (int)gridDim.x / H;     // a step of gridDim.x units moves (b, h) by (db, dh) with one carry
+        dh = (int)gridDim.x % H;
     }
     __device__ __forceinline__ void next() {
         if (++i == tpu) {
             i = 0;
-            unit += stride;
-            b = unit / H;
-            h = unit % H;
+            b += db;
+            h += dh;
+            if (h >= H) {
+                h -= H;
+                ++b;
+            }
         }
     }
 };
@@ -246,7 +262,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             mbar_init(&bars->cbld_full[i], 1);
             mbar_init(&bars->cbld_empty[i], 2);   // commits of both MMA issuers
             mbar_init(&bars->xld_full[i], 1);
-            mbar_init(&bars->xld_empty[i], 5);    // Y1 commit + 4 scaling warps
+            mbar_init(&bars->xld_empty[i], 8);    // 4 scaling warps + 4 epilogue warps (exact tiles) or the scaling warps again
             mbar_init(&bars->xw_free[i], 1);      // S commit: the scaled tile may be overwritten by y
             mbar_init(&bars->ystage_free[i], 4);  // epilogue warps: their y store has drained the tile
             mbar_init(&bars->cb_full[i], 1);
@@ -296,6 +312,12 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             for (int it = 0; it < total; ++it, tw.next()) {
                 const int b = tw.b, h = tw.h, g = h / hpg;
                 const int st = it & 1, s0 = tw.i * T;
+                // X stage first: it is released early (by the scaling pass of the tile two back; on exact
+                // tiles by Y1 as well) and must not queue behind the wait for the C + B stage
+                BM_WAIT(&bars->xld_empty[st], ((it >> 1) & 1) ^ 1);
+                BM_TRACE(0, it, 1);
+                mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
+                tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, s0, b);
                 // C + B stage: released once CB, Y2 and S of the tile two back have completed
                 BM_WAIT(&bars->cbld_empty[st], ((it >> 1) & 1) ^ 1);
                 BM_TRACE(0, it, 0);
@@ -306,11 +328,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 tma_load_4d(cs + kPanel, &prm.tm_c, &bars->cbld_full[st], 64, g, s0, b);
                 tma_load_4d(bs, &prm.tm_b, &bars->cbld_full[st], 0, g, s0, b);
                 tma_load_4d(bs + kPanel, &prm.tm_b, &bars->cbld_full[st], 64, g, s0, b);
-                // X stage: released by the scaling pass and Y1 of the tile two back
-                BM_WAIT(&bars->xld_empty[st], ((it >> 1) & 1) ^ 1);
-                BM_TRACE(0, it, 1);
-                mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
-                tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, s0, b);
             }
         }
     } else if (warp == 1) {
@@ -326,19 +343,20 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     BM_WAIT(&bars->cbld_full[st], (nx >> 1) & 1);
                     BM_TRACE(1, nx, 0);
                     const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
+                    const uint64_t da = umma_desc_kmajor(cs), db = umma_desc_kmajor(bs);
 #pragma unroll 1
                     for (int k = 0; k < 8; ++k) {
                         const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                        umma_ss(tmem + kColCB + st * 128, umma_desc_kmajor(cs + off), umma_desc_kmajor(bs + off), id_cb, k > 0);
+                        umma_ss(tmem + kColCB + st * 128, desc_advance(da, off), desc_advance(db, off), id_cb, k > 0);
                     }
                     umma_commit(&bars->cb_full[st]);
                     umma_commit(&bars->cbld_empty[st]);
                 }
                 if (it >= 0) {
                     const int st = it & 1, cst = (it & (kCumStages - 1));
-                    BM_WAIT(&bars->xld_full[st], (it >> 1) & 1);
+                    // xw_ready implies the X tile has landed and p_ready implies the decay scan of the
+                    // tile is published (their producers waited for exactly that)
                     BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
-                    BM_WAIT(&bars->cum_full[cst], (it >> 2) & 1);
                     BM_WAIT(&bars->y1_empty, (it & 1) ^ 1);
                     BM_WAIT(&bars->p_ready[st], (it >> 1) & 1);
                     BM_TRACE(1, it, 1);
@@ -348,45 +366,50 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     const bool factored = *reinterpret_cast<const volatile float*>(flag) != 0.f;
                     mbar_arrive(&bars->cum_empty[cst]);
                     const uint32_t xs = factored ? xw_base + st * kPanel : x_base + st * kPanel;
+                    const uint64_t dx = umma_desc_mnmajor(xs, kPanel);
+                    const uint32_t pa = tmem + kColCB + st * 128;
 #pragma unroll 1
                     for (int k = 0; k < 8; ++k)
-                        umma_ts(tmem + kColY1, tmem + kColCB + st * 128 + k * 8, umma_desc_mnmajor(xs + k * 2048, kPanel), id_kmn, k > 0);
+                        umma_ts(tmem + kColY1, pa + k * 8, desc_advance(dx, k * 2048), id_kmn, k > 0);
                     umma_commit(&bars->y1_full);
-                    umma_commit(&bars->xld_empty[st]);
                 }
             }
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ MMA issuer, state chain
-        // Per tile: S(it) = B^T Xw first (its inputs are ready earliest and it feeds the state update),
-        // then Y2(it) = C h^T once the state entering the tile has been published.
+        // Per tile: Y2(it) = C h^T as soon as the state entering the tile is published, then S(it) = B^T Xw.
+        // With the readout first, it has completed by the time S(it) is folded into the state, so the
+        // state update can write the next operand tile in the same pass.
         if (lane == 0) {
             const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
             const uint32_t id_mnmn = umma_idesc_bf16(128, 64, true, true);
+            const uint64_t dh = umma_desc_mnmajor(h_base, kPanel);
             for (int it = 0; it < total; ++it) {
                 const int st = it & 1;
                 const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
                 BM_WAIT(&bars->cbld_full[st], (it >> 1) & 1);
-                BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
-                BM_WAIT(&bars->s_empty, (it & 1) ^ 1);
-                BM_TRACE(2, it, 1);
-                tc_fence_after();
-#pragma unroll 1
-                for (int k = 0; k < 8; ++k)
-                    umma_ss(tmem + kColS, umma_desc_mnmajor(bs + k * 2048, kPanel), umma_desc_mnmajor(xw + k * 2048, kPanel), id_mnmn, k > 0);
-                umma_commit(&bars->s_full);
-                umma_commit(&bars->xw_free[st]);
                 BM_WAIT(&bars->h_ready, it & 1);
                 BM_WAIT(&bars->y2_empty[st], ((it >> 1) & 1) ^ 1);
                 BM_TRACE(2, it, 0);
                 tc_fence_after();
+                const uint64_t dc = umma_desc_kmajor(cs);
 #pragma unroll 1
                 for (int k = 0; k < 8; ++k) {
                     const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                    umma_ss(tmem + kColY2 + st * 64, umma_desc_kmajor(cs + off), umma_desc_mnmajor(h_base + k * 2048, kPanel), id_kmn, k > 0);
+                    umma_ss(tmem + kColY2 + st * 64, desc_advance(dc, off), desc_advance(dh, k * 2048), id_kmn, k > 0);
                 }
                 umma_commit(&bars->y2_full[st]);
                 umma_commit(&bars->h_free);
+                BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
+                BM_WAIT(&bars->s_empty, (it & 1) ^ 1);
+                BM_TRACE(2, it, 1);
+                tc_fence_after();
+                const uint64_t dbm = umma_desc_mnmajor(bs, kPanel), dxw = umma_desc_mnmajor(xw, kPanel);
+#pragma unroll 1
+                for (int k = 0; k < 8; ++k)
+                    umma_ss(tmem + kColS, desc_advance(dbm, k * 2048), desc_advance(dxw, k * 2048), id_mnmn, k > 0);
+                umma_commit(&bars->s_full);
+                umma_commit(&bars->xw_free[st]);
                 umma_commit(&bars->cbld_empty[st]);
             }
         }
@@ -403,41 +426,51 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             float *dtv = cum2 + T, *erow = cum2 + 2 * T, *wv = cum2 + 3 * T, *colf = cum2 + 4 * T;
             const float ah = prm.a[h] * log2e;
             const float bias = prm.dt_bias ? prm.dt_bias[h] : 0.f;
-            float d4[4], c4[4];
-            float run = 0.f;
+            const float* dt_row = prm.dt + ((int64_t)b * prm.S + i * T) * prm.H + h;
+            const int left = prm.S - i * T;      // tokens of the sequence from the start of this tile on
+            // the four global loads of a lane are issued together (their latency would otherwise serialise)
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int s = i * T + lane * 4 + k;
+                const int t = k * 32 + lane;
                 float v = 0.f;
-                if (s < prm.S) {
-                    v = prm.dt[((int64_t)b * prm.S + s) * prm.H + h];
-                    if (prm.dt_bias) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
-                }
-                d4[k] = v;
-                run += v * ah;
-                c4[k] = run;
+                if (t < left) v = dt_row[(int64_t)t * prm.H];
+                dtv[t] = v;
             }
-            float incl = run;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                float up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += up;
-            }
-            const float excl = incl - run;
-            const float cend_tile = __shfl_sync(0xffffffffu, incl, 31);
-            // end-of-32-block cumulative value: lane 8*blk+7 holds it as its inclusive total
-            const float cend_blk = __shfl_sync(0xffffffffu, incl, (lane & ~7) | 7);
-#pragma unroll
+            // pass 1, one 32-token block per step: inclusive scan within the block plus the carry of the
+            // blocks before it; the block's last lane holds the block-end value the column factor refers to
+            float carry = 0.f;
+            bool any_zero = false;
+#pragma unroll 1
             for (int k = 0; k < 4; ++k) {
-                const int t = lane * 4 + k;
-                const float c = excl + c4[k];
+                const int t = k * 32 + lane;
+                float v = dtv[t];
+                if (prm.dt_bias && t < left) {
+                    v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
+                    dtv[t] = v;
+                }
+                float incl = v * ah;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const float up = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += up;
+                }
+                any_zero |= __any_sync(0xffffffffu, t < left && !(v > 0.f));
+                const float c = carry + incl;
+                carry = __shfl_sync(0xffffffffu, c, 31);
                 cum2[t] = c;
-                dtv[t] = d4[k];
                 erow[t] = ex2(c);
-                wv[t] = d4[k] * ex2(cend_tile - c);
-                colf[t] = d4[k] * ex2(cend_blk - c);
+                colf[t] = v * ex2(carry - c);
             }
-            if (lane == 0) cum2[5 * T] = fabsf(cend_tile) <= kFactoredMaxLog2Decay ? 1.f : 0.f;
+            const float cend_tile = carry;
+            // pass 2: the state weight needs the tile-end value
+#pragma unroll 1
+            for (int k = 0; k < 4; ++k) {
+                const int t = k * 32 + lane;
+                wv[t] = dtv[t] * ex2(cend_tile - cum2[t]);
+            }
+            // the factored form divides by dt_t (the D x term), so a tile with a zero step inside the
+            // sequence takes the exact form as well
+            if (lane == 0) cum2[5 * T] = (fabsf(cend_tile) <= kFactoredMaxLog2Decay && !any_zero) ? 1.f : 0.f;
             __syncwarp();
             BM_TRACE(3, it, 0);
             if (lane == 0) mbar_arrive(&bars->cum_full[cst]);
@@ -446,12 +479,18 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // ------------------------------------------------------------------ mask pass: CB -> P
         const int q = warp & 3, t = q * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        // bf16-pair masks of the diagonal block: column 32q + j is kept for row 32q + lane when j <= lane
+        uint32_t causal[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            causal[j] = (2 * j <= lane ? 0x0000ffffu : 0u) | (2 * j + 1 <= lane ? 0xffff0000u : 0u);
+            asm volatile("" : "+r"(causal[j]));   // keep the masks in registers instead of recomputing them per tile
+        }
         TileWalk tw(tpu, prm.H);
         for (int it = 0; it < total; ++it, tw.next()) {
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + T, *colf = cum2 + 4 * T;
-            const float dskip = prm.d ? prm.d[tw.h] : 0.f;
             BM_TRACE(4, it, 0);
             BM_WAIT_WARP(&bars->cum_full[cst], (it >> 2) & 1);
             BM_WAIT_WARP(&bars->cb_full[st], (it >> 1) & 1);
@@ -468,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     uint32_t r[32];
                     tmem_ld32(cb + c * 32, r);
                     tmem_wait_ld();
-                    mask_block(r, out, factored, c == q, c, t, ct, dskip, cum2, dtv, colf);
+                    mask_block(r, out, factored, c == q, c, ct, cum2, dtv, colf, causal);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) out[j] = 0u;
@@ -513,6 +552,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             if (lane == 0) {
                 mbar_arrive(&bars->xw_ready[st]);
                 mbar_arrive(&bars->xld_empty[st]);
+                // factored tiles: nothing reads X after this pass, so each warp also makes the arrival that
+                // the epilogue warp of the same rows makes on exact tiles (where Y1 and D x still read X)
+                if (wv[2 * T] != 0.f) mbar_arrive(&bars->xld_empty[st]);
             }
         };
         auto publish_state = [&]() {
@@ -530,8 +572,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->h_ready);
         };
-        // Iteration `it` publishes the state entering tile it, scales the X tile of tile it+1 (one
-        // tile ahead, so S(it+1) can be issued early) and then folds S(it) into the state.
+        // Iteration `it` scales the X tile of tile it+1 (one tile ahead, so S(it+1) can be issued early),
+        // then folds S(it) into the state and publishes the result as the readout operand of tile it+1.
+        // At the first tile of a unit the initial state is loaded and published instead.
         TileWalk tw(tpu, prm.H);
         for (int it = -1; it < total; ++it) {
             if (it > 0) tw.next();
@@ -542,9 +585,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
             if (it >= 0) {
                 if (i == 0) {
-                    // unit start: initial state -> registers
+                    // unit start: initial state -> registers, published as the operand of this tile's
+                    // readout (the operand tile is free once Y2(it-1) has completed)
 #pragma unroll
                     for (int p = 0; p < P; ++p) hst[p] = prm.h0 ? prm.h0[state_base + (int64_t)p * R + t] : 0.f;
+                    if (it > 0) BM_WAIT_WARP(&bars->h_free, (it - 1) & 1);
+                    publish_state();
+                    BM_TRACE(5, it, 3);
                 }
                 if (prm.chunk_states && (i * T) % prm.Q == 0) {
                     const int n = (i * T) / prm.Q;
@@ -552,10 +599,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
 #pragma unroll
                     for (int p = 0; p < P; ++p) cs[(int64_t)p * R + t] = hst[p];
                 }
-                // the operand tile is free once Y2(it-1) has completed
-                if (it > 0) BM_WAIT_WARP(&bars->h_free, (it - 1) & 1);
-                publish_state();
-                BM_TRACE(5, it, 3);
             }
             if (it + 1 < total) {
                 // scaled X of the next tile: its buffer was last read by S(it-1) (observed through
@@ -573,19 +616,40 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 BM_TRACE(5, it, 1);
                 tc_fence_after();
                 const float decay = erow[T - 1];
+                const uint64_t decay2 = pair_f32(decay, decay);
+                // unless the unit ends here, the updated state is also the readout operand of the next
+                // tile: written in the same pass, once Y2(it) has finished reading the operand tile
+                const bool more = i + 1 < tpu;
+                if (more) BM_WAIT_WARP(&bars->h_free, it & 1);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t sv[16];
                     tmem_ld16(lane_addr + kColS + c * 16, sv);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) hst[c * 16 + j] = fmaf(decay, hst[c * 16 + j], __uint_as_float(sv[j]));
+                    for (int j = 0; j < 16; j += 2) {
+                        const uint64_t r = fma2(decay2, pair_f32(hst[c * 16 + j], hst[c * 16 + j + 1]), pair_u32(sv[j], sv[j + 1]));
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(hst[c * 16 + j]), "=f"(hst[c * 16 + j + 1]) : "l"(r));
+                    }
+                    if (more) {
+#pragma unroll
+                        for (int k = 2 * c; k < 2 * c + 2; ++k) {
+                            uint4 v;
+                            v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
+                            v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
+                            v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
+                            v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
+                            *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
+                        }
+                    }
                 }
                 tc_fence_before();
+                if (more) fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(&bars->s_empty);
                     mbar_arrive(&bars->cum_empty[cst]);
+                    if (more) mbar_arrive(&bars->h_ready);
                 }
                 BM_TRACE(5, it, 2);
                 if (i + 1 == tpu) {
@@ -610,7 +674,17 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const float e = erow[t];
             // row factor of the factored mask: exp2(cum_t - cend); 1 for exact tiles
             const float* cum2 = erow - 2 * T;
-            const float e1 = cum2[5 * T] != 0.f ? ex2(cum2[t] - cum2[T - 1]) : 1.f;
+            const bool factored = cum2[5 * T] != 0.f;
+            const float e1 = factored ? ex2(cum2[t] - cum2[T - 1]) : 1.f;
+            // skip term D x: factored tiles recover x from the scaled tile (x w = Xw, w > 0 on these tiles;
+            // it is the very buffer this warp is about to overwrite with y), exact tiles read the X tile,
+            // which they hold until this pass has read it
+            const float wt = cum2[3 * T + t];
+            const float dsk = prm.d ? prm.d[h] : 0.f;
+            const float dxw = factored ? (wt > 0.f ? dsk / wt : 0.f) : dsk;   // wt = 0 only on padding rows
+            const unsigned char* xsrc = factored ? ys : smem + kOffX + st * kPanel;
+            const uint64_t ee = pair_f32(e, e), ee1 = pair_f32(e1, e1);
+            const uint32_t dd = pack_bf16x2(dxw, dxw);
             BM_WAIT_WARP(&bars->xw_free[st], (it >> 1) & 1);
             BM_WAIT_WARP(&bars->y2_full[st], (it >> 1) & 1);
             BM_WAIT_WARP(&bars->y1_full, it & 1);
@@ -634,22 +708,27 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int j = k * 8;
-                    uint4 o;
-                    o.x = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 0]), e1 * __uint_as_float(y1[j + 0])),
-                                      fmaf(e, __uint_as_float(y2[j + 1]), e1 * __uint_as_float(y1[j + 1])));
-                    o.y = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 2]), e1 * __uint_as_float(y1[j + 2])),
-                                      fmaf(e, __uint_as_float(y2[j + 3]), e1 * __uint_as_float(y1[j + 3])));
-                    o.z = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 4]), e1 * __uint_as_float(y1[j + 4])),
-                                      fmaf(e, __uint_as_float(y2[j + 5]), e1 * __uint_as_float(y1[j + 5])));
-                    o.w = pack_bf16x2(fmaf(e, __uint_as_float(y2[j + 6]), e1 * __uint_as_float(y1[j + 6])),
-                                      fmaf(e, __uint_as_float(y2[j + 7]), e1 * __uint_as_float(y1[j + 7])));
-                    *reinterpret_cast<uint4*>(ys + sw128_offset(t, half * 4 + k)) = o;
+                    const uint32_t off = sw128_offset(t, half * 4 + k);
+                    uint4* slot = reinterpret_cast<uint4*>(ys + off);
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xsrc + off);
+                    const uint32_t xw4[4] = {xv.x, xv.y, xv.z, xv.w};
+                    uint32_t o4[4];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        uint64_t acc = mul2(ee1, pair_u32(y1[j + 2 * m], y1[j + 2 * m + 1]));
+                        acc = fma2(ee, pair_u32(y2[j + 2 * m], y2[j + 2 * m + 1]), acc);
+                        // + (D / w_t) * Xw as one packed bf16 fma on the rounded result
+                        asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o4[m]) : "r"(xw4[m]), "r"(dd), "r"(pack_bf16x2_pair(acc)));
+                    }
+                    const uint4 o = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+                    *slot = o;
                 }
             }
             fence_proxy_async_smem();
             __syncwarp();
             BM_TRACE(6, it, 1);
             if (lane == 0) {
+                if (!factored) mbar_arrive(&bars->xld_empty[st]);   // exact tiles: the X tile has been read
                 tma_store_4d(&prm.tm_y, ys + q * 4096, 0, h, i * T + q * 32, b);
                 tma_store_commit();
                 mbar_arrive(&bars->cum_empty[cst]);
@@ -661,6 +740,10 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             BM_TRACE(6, it, 2);
         }
     }
+    goto done;
+timed_out:
+    atomicExch(prm.status, (int)BM_ERR_TIMEOUT);
+    *abort_flag = 1;
 done:
     if (warp >= 12 && lane == 0) tma_store_wait_all<0>();
     tc_fence_before();

@@ -52,6 +52,14 @@ def _workspace(nbytes, device):
     return buf
 
 
+def last_workspace_status():
+    """Device status word left by the most recent SSD launch on the current device and stream (synchronises);
+    0 when no launch has used a workspace yet."""
+    key = (torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)
+    ws = _ws_cache.get(key)
+    return 0 if ws is None else int(lib.bm_workspace_status(ws.data_ptr(), _stream()))
+
+
 def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bias=None, dt_limit=(0.0, 65504.0),
              z=None, return_chunk_states=False, check_status=False):
     """Mamba-2 chunked SSD forward.  x [b,s,h,p], dt [b,s,h] f32, a [h] f32, b/c [b,s,g,r], d [h] f32,

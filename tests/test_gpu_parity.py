@@ -318,6 +318,37 @@ def test_ssd2_tensor_path_strong_decay_is_finite(bm):
     assert torch.isfinite(y.float()).all() and torch.isfinite(hf).all()
 
 
+def test_ssd2_tensor_path_zero_steps_keep_the_skip_term(bm):
+    """Tokens with dt == 0 contribute nothing to the state but still pass D x through; tiles that contain
+    one take the exact mask form (the factored form would divide by dt)."""
+    cfg = inputs.ssd2_prefill(seed=33, batch=1, seqlen=384, nheads=3, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["dt"][:, 5::7, :] = 0.0
+    cfg["dt"][:, 200:300, 1] = 0.0
+    dt = torch.bfloat16
+    x, bb, cc = (q(cfg[k], dt) for k in ("x", "b", "c"))
+    want_y, want_h = mamba2.ssd_serial(x, cfg["dt"], cfg["a"], bb, cc, cfg["d"], cfg["h0"], 128)
+    y, hf = _ssd2_case(bm, cfg, 128, dt, path="tensor", check_status=True)
+    assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
+    # the rows of the zero steps themselves: y = C h + D x exactly as the oracle has it
+    rows = host(y)[:, 200:300, 1]
+    assert rel_l2(rows, want_y[:, 200:300, 1]) <= 2e-2
+
+
+def test_ssd2_tensor_path_mixed_decay_tiles(bm):
+    """Heads with weak and with very strong decay side by side: factored and exact tiles alternate within
+    one launch (the X stage is released differently by the two forms)."""
+    cfg = inputs.ssd2_prefill(seed=34, batch=2, seqlen=1024, nheads=6, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["a"] = np.float32([-0.5, -16.0, -1.0, -12.0, -0.01, -8.0])
+    rng = np.random.default_rng(7)
+    cfg["dt"] = (rng.random(cfg["dt"].shape) * np.float32([0.01, 0.8, 0.02, 0.5, 0.05, 0.3])).astype(np.float32)
+    cfg["dt"][:, 512:640] *= 40.0       # a stretch of large steps in every head
+    dt = torch.bfloat16
+    x, bb, cc = (q(cfg[k], dt) for k in ("x", "b", "c"))
+    want_y, want_h = mamba2.ssd_serial(x, cfg["dt"], cfg["a"], bb, cc, cfg["d"], cfg["h0"], 256)
+    y, hf = _ssd2_case(bm, cfg, 256, dt, path="tensor", check_status=True)
+    assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
+
+
 # ------------------------------------------------------------------ backward (recompute) vs autodiff oracle
 def _grad_close(got, want, tol=1e-3):
     """The reference's gradient tolerance is max-abs 1e-3 at its tiny shapes; relative-L2 here."""
