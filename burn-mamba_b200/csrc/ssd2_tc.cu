@@ -417,25 +417,33 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // ------------------------------------------------------------------ decay scan of dt
         // log2-domain cumulative sum of dt*A over the tile, plus the derived per-token factors.
         const float log2e = 1.4426950408889634f;
-        TileWalk tw(tpu, prm.H);
+        // The dt values of a tile are fetched one tile ahead (four loads per lane, issued together), so the
+        // global-memory latency is hidden behind the scan of the tile before.
+        TileWalk tw(tpu, prm.H), twn(tpu, prm.H);
+        float nv[4];
+        auto fetch = [&](const TileWalk& w) {
+            const float* row = prm.dt + ((int64_t)w.b * prm.S + w.i * T) * prm.H + w.h;
+            const int left = prm.S - w.i * T;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int t = k * 32 + lane;
+                nv[k] = t < left ? row[(int64_t)t * prm.H] : 0.f;
+            }
+        };
+        if (total > 0) fetch(twn);
         for (int it = 0; it < total; ++it, tw.next()) {
-            const int b = tw.b, h = tw.h, i = tw.i;
+            const int h = tw.h, i = tw.i;
             const int cst = (it & (kCumStages - 1));
             BM_WAIT_WARP(&bars->cum_empty[cst], ((it >> 2) & 1) ^ 1);
             float* cum2 = reinterpret_cast<float*>(smem + kOffCum + cst * kCumStageBytes);
             float *dtv = cum2 + T, *erow = cum2 + 2 * T, *wv = cum2 + 3 * T, *colf = cum2 + 4 * T;
             const float ah = prm.a[h] * log2e;
             const float bias = prm.dt_bias ? prm.dt_bias[h] : 0.f;
-            const float* dt_row = prm.dt + ((int64_t)b * prm.S + i * T) * prm.H + h;
             const int left = prm.S - i * T;      // tokens of the sequence from the start of this tile on
-            // the four global loads of a lane are issued together (their latency would otherwise serialise)
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int t = k * 32 + lane;
-                float v = 0.f;
-                if (t < left) v = dt_row[(int64_t)t * prm.H];
-                dtv[t] = v;
-            }
+            for (int k = 0; k < 4; ++k) dtv[k * 32 + lane] = nv[k];
+            twn.next();
+            if (it + 1 < total) fetch(twn);
             // pass 1, one 32-token block per step: inclusive scan within the block plus the carry of the
             // blocks before it; the block's last lane holds the block-end value the column factor refers to
             float carry = 0.f;
