@@ -53,16 +53,16 @@ constexpr uint32_t kLoadBytesX = kPanel;
 // TMEM columns
 constexpr uint32_t kColCB = 0;     // 2 buffers x 128 columns; P (bf16 pairs) aliases the first 64 of each
 constexpr uint32_t kColY1 = 256;
-constexpr uint32_t kColY2 = 320;   // 2 buffers x 64 columns
-constexpr uint32_t kColS = 448;
+constexpr uint32_t kColY2 = 320;
+constexpr uint32_t kColS = 384;    // 2 buffers x 64 columns
 
 struct Barriers {
     uint64_t cbld_full[2], cbld_empty[2];   // C + B tiles
     uint64_t xld_full[2], xld_empty[2];     // X tile (later the y staging tile)
     uint64_t cum_full[kCumStages], cum_empty[kCumStages];
-    uint64_t cb_full[2], p_ready[2];
-    uint64_t y1_full, y1_empty, y2_full[2], y2_empty[2];
-    uint64_t h_ready, h_free, xw_ready[2], xw_free[2], ystage_free[2], s_full, s_empty;
+    uint64_t cb_full[2], p_ready[2], p_free[2];
+    uint64_t y1_full, y1_empty, y2_full, y2_empty;
+    uint64_t h_ready, h_free, xw_ready[2], xw_free[2], ystage_free[2], s_full[2], s_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -267,20 +267,21 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             mbar_init(&bars->ystage_free[i], 4);  // epilogue warps: their y store has drained the tile
             mbar_init(&bars->cb_full[i], 1);
             mbar_init(&bars->p_ready[i], 4);
-            mbar_init(&bars->y2_full[i], 1);
-            mbar_init(&bars->y2_empty[i], 4);
+            mbar_init(&bars->p_free[i], 1);       // Y1 commit: the P / CB accumulator may be overwritten
+            mbar_init(&bars->s_full[i], 1);
+            mbar_init(&bars->s_empty[i], 4);
             mbar_init(&bars->xw_ready[i], 4);
         }
         for (int i = 0; i < kCumStages; ++i) {
             mbar_init(&bars->cum_full[i], 1);
-            mbar_init(&bars->cum_empty[i], 13);   // 12 consumer warps + the scan-chain MMA issuer
+            mbar_init(&bars->cum_empty[i], 12);   // mask, state and epilogue warps
         }
         mbar_init(&bars->y1_full, 1);
         mbar_init(&bars->y1_empty, 4);
         mbar_init(&bars->h_ready, 4);
         mbar_init(&bars->h_free, 1);
-        mbar_init(&bars->s_full, 1);
-        mbar_init(&bars->s_empty, 4);
+        mbar_init(&bars->y2_full, 1);
+        mbar_init(&bars->y2_empty, 4);
         bars->abort_flag = 0;
         fence_mbar_init();
     }
@@ -332,85 +333,73 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer, scan chain
-        // Per tile: CB(it+1) = C B^T first (its inputs arrive early and the mask pass of tile it+1
-        // needs it soonest), then Y1(it) = P X once the mask pass of tile it has published P.
-        if (lane == 0 && total > 0) {
+        // CB(it) = C B^T as soon as the C + B stage of tile it has landed and Y1(it-2) has finished reading
+        // P from the accumulator CB(it) overwrites.  (Y1 itself is issued by the mask warpgroup, right
+        // where P becomes complete, so that it never queues behind a wait for a TMA stage.)
+        if (lane == 0) {
             const uint32_t id_cb = umma_idesc_bf16(128, 128, false, false);
-            const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
-            for (int it = -1; it < total; ++it) {
-                if (it + 1 < total) {
-                    const int nx = it + 1, st = nx & 1;
-                    BM_WAIT(&bars->cbld_full[st], (nx >> 1) & 1);
-                    BM_TRACE(1, nx, 0);
-                    const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
-                    const uint64_t da = umma_desc_kmajor(cs), db = umma_desc_kmajor(bs);
+            for (int it = 0; it < total; ++it) {
+                const int st = it & 1;
+                BM_WAIT(&bars->cbld_full[st], (it >> 1) & 1);
+                BM_WAIT(&bars->p_free[st], ((it >> 1) & 1) ^ 1);
+                BM_TRACE(1, it, 0);
+                tc_fence_after();
+                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel;
+                const uint64_t da = umma_desc_kmajor(cs), db = umma_desc_kmajor(bs);
 #pragma unroll 1
-                    for (int k = 0; k < 8; ++k) {
-                        const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                        umma_ss(tmem + kColCB + st * 128, desc_advance(da, off), desc_advance(db, off), id_cb, k > 0);
-                    }
-                    umma_commit(&bars->cb_full[st]);
-                    umma_commit(&bars->cbld_empty[st]);
+                for (int k = 0; k < 8; ++k) {
+                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                    umma_ss(tmem + kColCB + st * 128, desc_advance(da, off), desc_advance(db, off), id_cb, k > 0);
                 }
-                if (it >= 0) {
-                    const int st = it & 1, cst = (it & (kCumStages - 1));
-                    // xw_ready implies the X tile has landed and p_ready implies the decay scan of the
-                    // tile is published (their producers waited for exactly that)
-                    BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
-                    BM_WAIT(&bars->y1_empty, (it & 1) ^ 1);
-                    BM_WAIT(&bars->p_ready[st], (it >> 1) & 1);
-                    BM_TRACE(1, it, 1);
-                    tc_fence_after();
-                    // factored tiles multiply by the scaled tile Xw, exact tiles by X itself
-                    const float* flag = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 5 * T;
-                    const bool factored = *reinterpret_cast<const volatile float*>(flag) != 0.f;
-                    mbar_arrive(&bars->cum_empty[cst]);
-                    const uint32_t xs = factored ? xw_base + st * kPanel : x_base + st * kPanel;
-                    const uint64_t dx = umma_desc_mnmajor(xs, kPanel);
-                    const uint32_t pa = tmem + kColCB + st * 128;
-#pragma unroll 1
-                    for (int k = 0; k < 8; ++k)
-                        umma_ts(tmem + kColY1, pa + k * 8, desc_advance(dx, k * 2048), id_kmn, k > 0);
-                    umma_commit(&bars->y1_full);
-                }
+                umma_commit(&bars->cb_full[st]);
+                umma_commit(&bars->cbld_empty[st]);
             }
         }
     } else if (warp == 2) {
         // ------------------------------------------------------------------ MMA issuer, state chain
-        // Per tile: Y2(it) = C h^T as soon as the state entering the tile is published, then S(it) = B^T Xw.
-        // With the readout first, it has completed by the time S(it) is folded into the state, so the
-        // state update can write the next operand tile in the same pass.
+        // Per step: Y2(it) = C h^T, then S(it+1) = B^T Xw (one tile ahead, double-buffered accumulator): the
+        // order in which their inputs are produced.
         if (lane == 0) {
             const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
             const uint32_t id_mnmn = umma_idesc_bf16(128, 64, true, true);
             const uint64_t dh = umma_desc_mnmajor(h_base, kPanel);
-            for (int it = 0; it < total; ++it) {
-                const int st = it & 1;
-                const uint32_t cs = c_base + st * 2 * kPanel, bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
-                BM_WAIT(&bars->cbld_full[st], (it >> 1) & 1);
-                BM_WAIT(&bars->h_ready, it & 1);
-                BM_WAIT(&bars->y2_empty[st], ((it >> 1) & 1) ^ 1);
-                BM_TRACE(2, it, 0);
-                tc_fence_after();
-                const uint64_t dc = umma_desc_kmajor(cs);
+            for (int it = -1; it < total; ++it) {
+                if (it >= 0) {
+                    // Y2(it) = C h^T once the state entering the tile is published; last reader of the C + B
+                    // stage (S(it) was issued in the previous step)
+                    const int st = it & 1;
+                    const uint32_t cs = c_base + st * 2 * kPanel;
+                    BM_WAIT(&bars->h_ready, it & 1);
+                    BM_WAIT(&bars->y2_empty, (it & 1) ^ 1);
+                    BM_TRACE(2, it, 0);
+                    tc_fence_after();
+                    const uint64_t dc = umma_desc_kmajor(cs);
 #pragma unroll 1
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
-                    umma_ss(tmem + kColY2 + st * 64, desc_advance(dc, off), desc_advance(dh, k * 2048), id_kmn, k > 0);
+                    for (int k = 0; k < 8; ++k) {
+                        const uint32_t off = (k >> 2) * kPanel + (k & 3) * 32;
+                        umma_ss(tmem + kColY2, desc_advance(dc, off), desc_advance(dh, k * 2048), id_kmn, k > 0);
+                    }
+                    umma_commit(&bars->y2_full);
+                    umma_commit(&bars->h_free);
+                    umma_commit(&bars->cbld_empty[st]);
                 }
-                umma_commit(&bars->y2_full[st]);
-                umma_commit(&bars->h_free);
-                BM_WAIT(&bars->xw_ready[st], (it >> 1) & 1);
-                BM_WAIT(&bars->s_empty, (it & 1) ^ 1);
-                BM_TRACE(2, it, 1);
-                tc_fence_after();
-                const uint64_t dbm = umma_desc_mnmajor(bs, kPanel), dxw = umma_desc_mnmajor(xw, kPanel);
+                if (it + 1 < total) {
+                    // S(it+1) = B^T Xw: independent of the state, so it runs one tile ahead into the other
+                    // of its two accumulators while the state update of tile it is still reading its own
+                    const int nx = it + 1, st = nx & 1;
+                    const uint32_t bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
+                    BM_WAIT(&bars->cbld_full[st], (nx >> 1) & 1);
+                    BM_WAIT(&bars->xw_ready[st], (nx >> 1) & 1);
+                    BM_WAIT(&bars->s_empty[st], ((nx >> 1) & 1) ^ 1);
+                    BM_TRACE(2, nx, 1);
+                    tc_fence_after();
+                    const uint64_t dbm = umma_desc_mnmajor(bs, kPanel), dxw = umma_desc_mnmajor(xw, kPanel);
 #pragma unroll 1
-                for (int k = 0; k < 8; ++k)
-                    umma_ss(tmem + kColS, desc_advance(dbm, k * 2048), desc_advance(dxw, k * 2048), id_mnmn, k > 0);
-                umma_commit(&bars->s_full);
-                umma_commit(&bars->xw_free[st]);
-                umma_commit(&bars->cbld_empty[st]);
+                    for (int k = 0; k < 8; ++k)
+                        umma_ss(tmem + kColS + st * 64, desc_advance(dbm, k * 2048), desc_advance(dxw, k * 2048), id_mnmn, k > 0);
+                    umma_commit(&bars->s_full[st]);
+                    umma_commit(&bars->xw_free[st]);
+                }
             }
         }
     } else if (warp == 3) {
@@ -530,6 +519,29 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 mbar_arrive(&bars->p_ready[st]);
                 mbar_arrive(&bars->cum_empty[cst]);
             }
+            if (q == 0) {
+                // The warp with the least mask work (one block) also issues Y1(it) = P X: it waits, as a
+                // whole, for the other three warps' parts of P, for the B operand and for the epilogue to
+                // have drained Y1(it-1); then one lane issues.  Factored tiles multiply by the scaled tile
+                // Xw, exact tiles by X itself.
+                BM_WAIT_WARP(&bars->p_ready[st], (it >> 1) & 1);
+                BM_WAIT_WARP(&bars->xw_ready[st], (it >> 1) & 1);
+                BM_WAIT_WARP(&bars->y1_empty, (it & 1) ^ 1);
+                BM_TRACE(1, it, 1);
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t xs = factored ? xw_base + st * kPanel : x_base + st * kPanel;
+                    const uint64_t dx = umma_desc_mnmajor(xs, kPanel);
+                    const uint32_t pa = tmem + kColCB + st * 128;
+                    const uint32_t id_kmn = umma_idesc_bf16(128, 64, false, true);
+#pragma unroll 1
+                    for (int k = 0; k < 8; ++k)
+                        umma_ts(tmem + kColY1, pa + k * 8, desc_advance(dx, k * 2048), id_kmn, k > 0);
+                    umma_commit(&bars->y1_full);
+                    umma_commit(&bars->p_free[st]);
+                }
+                __syncwarp();
+            }
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ X scaling and state update
@@ -544,16 +556,23 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const unsigned char* xs = smem + kOffX + st * kPanel;
             unsigned char* xw = smem + kOffXw + st * kPanel;
             const float w = wv[t];
-#pragma unroll 2
-            for (int k = 0; k < 8; ++k) {
-                const uint32_t off = sw128_offset(t, k);
-                uint4 v = *reinterpret_cast<const uint4*>(xs + off);
-                float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-                v.x = pack_bf16x2(f0.x * w, f0.y * w);
-                v.y = pack_bf16x2(f1.x * w, f1.y * w);
-                v.z = pack_bf16x2(f2.x * w, f2.y * w);
-                v.w = pack_bf16x2(f3.x * w, f3.y * w);
-                *reinterpret_cast<uint4*>(xw + off) = v;
+            // two batches of four 16-byte chunks: the four loads of a batch are in flight together
+#pragma unroll 1
+            for (int kb = 0; kb < 8; kb += 4) {
+                uint4 v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const uint4*>(xs + sw128_offset(t, kb + j));
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f0 = unpack_bf16x2(v[j].x), f1 = unpack_bf16x2(v[j].y), f2 = unpack_bf16x2(v[j].z),
+                                 f3 = unpack_bf16x2(v[j].w);
+                    uint4 o;
+                    o.x = pack_bf16x2(f0.x * w, f0.y * w);
+                    o.y = pack_bf16x2(f1.x * w, f1.y * w);
+                    o.z = pack_bf16x2(f2.x * w, f2.y * w);
+                    o.w = pack_bf16x2(f3.x * w, f3.y * w);
+                    *reinterpret_cast<uint4*>(xw + sw128_offset(t, kb + j)) = o;
+                }
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -580,8 +599,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->h_ready);
         };
-        // Iteration `it` scales the X tile of tile it+1 (one tile ahead, so S(it+1) can be issued early),
-        // then folds S(it) into the state and publishes the result as the readout operand of tile it+1.
+        // Iteration `it` scales the X tile of tile it+1 (so that S(it+1) can run while this warpgroup is
+        // still busy with tile it), folds S(it) into the state and publishes the result as the readout
+        // operand of tile it+1.
         // At the first tile of a unit the initial state is loaded and published instead.
         TileWalk tw(tpu, prm.H);
         for (int it = -1; it < total; ++it) {
@@ -619,45 +639,34 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 BM_TRACE(3, itc, 1);
             }
             if (it >= 0) {
-                // state update h <- exp(cum_end) h + S
-                BM_WAIT_WARP(&bars->s_full, it & 1);
+                // state update h <- exp(cum_end) h + S(it)
+                BM_WAIT_WARP(&bars->s_full[it & 1], (it >> 1) & 1);
                 BM_TRACE(5, it, 1);
                 tc_fence_after();
                 const float decay = erow[T - 1];
                 const uint64_t decay2 = pair_f32(decay, decay);
-                // unless the unit ends here, the updated state is also the readout operand of the next
-                // tile: written in the same pass, once Y2(it) has finished reading the operand tile
-                const bool more = i + 1 < tpu;
-                if (more) BM_WAIT_WARP(&bars->h_free, it & 1);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t sv[16];
-                    tmem_ld16(lane_addr + kColS + c * 16, sv);
+                    tmem_ld16(lane_addr + kColS + (it & 1) * 64 + c * 16, sv);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 16; j += 2) {
                         const uint64_t r = fma2(decay2, pair_f32(hst[c * 16 + j], hst[c * 16 + j + 1]), pair_u32(sv[j], sv[j + 1]));
                         asm("mov.b64 {%0, %1}, %2;" : "=f"(hst[c * 16 + j]), "=f"(hst[c * 16 + j + 1]) : "l"(r));
                     }
-                    if (more) {
-#pragma unroll
-                        for (int k = 2 * c; k < 2 * c + 2; ++k) {
-                            uint4 v;
-                            v.x = pack_bf16x2(hst[8 * k], hst[8 * k + 1]);
-                            v.y = pack_bf16x2(hst[8 * k + 2], hst[8 * k + 3]);
-                            v.z = pack_bf16x2(hst[8 * k + 4], hst[8 * k + 5]);
-                            v.w = pack_bf16x2(hst[8 * k + 6], hst[8 * k + 7]);
-                            *reinterpret_cast<uint4*>(hs + sw128_offset(t, k)) = v;
-                        }
-                    }
                 }
                 tc_fence_before();
-                if (more) fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&bars->s_empty);
+                    mbar_arrive(&bars->s_empty[it & 1]);
                     mbar_arrive(&bars->cum_empty[cst]);
-                    if (more) mbar_arrive(&bars->h_ready);
+                }
+                // unless the unit ends here, the updated state is the readout operand of the next tile;
+                // the operand tile is free once Y2(it) has completed
+                if (i + 1 < tpu) {
+                    BM_WAIT_WARP(&bars->h_free, it & 1);
+                    publish_state();
                 }
                 BM_TRACE(5, it, 2);
                 if (i + 1 == tpu) {
@@ -694,7 +703,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const uint64_t ee = pair_f32(e, e), ee1 = pair_f32(e1, e1);
             const uint32_t dd = pack_bf16x2(dxw, dxw);
             BM_WAIT_WARP(&bars->xw_free[st], (it >> 1) & 1);
-            BM_WAIT_WARP(&bars->y2_full[st], (it >> 1) & 1);
+            BM_WAIT_WARP(&bars->y2_full, it & 1);
             BM_WAIT_WARP(&bars->y1_full, it & 1);
             BM_TRACE(6, it, 0);
             tc_fence_after();
@@ -702,7 +711,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             for (int half = 0; half < 2; ++half) {
                 uint32_t y1[32], y2[32];
                 tmem_ld32(lane_addr + kColY1 + half * 32, y1);
-                tmem_ld32(lane_addr + kColY2 + st * 64 + half * 32, y2);
+                tmem_ld32(lane_addr + kColY2 + half * 32, y2);
                 tmem_wait_ld();
                 if (half == 1) {
                     // both accumulators are in registers: release them to the MMA issuers
@@ -710,7 +719,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     __syncwarp();
                     if (lane == 0) {
                         mbar_arrive(&bars->y1_empty);
-                        mbar_arrive(&bars->y2_empty[st]);
+                        mbar_arrive(&bars->y2_empty);
                     }
                 }
 #pragma unroll
