@@ -11,7 +11,6 @@ using namespace bm;
 
 namespace {
 
-constexpr int CH = 32;    // channels per CTA
 constexpr int TCH = 64;   // tokens per staged chunk
 constexpr int RPT = 2;    // states per thread
 constexpr int TU = 4;     // tokens processed together (independent loads / exps issued ahead of the recurrence)
@@ -24,22 +23,30 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
+// Shared-memory layout of one pipeline stage for CH channels and state rank R (element counts of T):
+// delta, u, z as [TCH][CH], then the B and C rows of the chunk as [TCH][R].
 template <typename T>
-struct Stage {
-    T delta[TCH][CH];
-    T u[TCH][CH];
-    T z[TCH][CH];
-    T bmat[TCH * 64];  // [TCH][R], R <= 64
-    T cmat[TCH * 64];
+struct StageView {
+    T *delta, *u, *z, *bmat, *cmat;
+    __device__ StageView(unsigned char* base, int ch, int r) {
+        delta = reinterpret_cast<T*>(base);
+        u = delta + TCH * ch;
+        z = u + TCH * ch;
+        bmat = z + TCH * ch;
+        cmat = bmat + TCH * r;
+    }
 };
+template <typename T>
+__host__ __device__ constexpr size_t stage_bytes(int ch, int r) { return sizeof(T) * (size_t)TCH * (3 * ch + 2 * r); }
 
 // Fast kernel: d_inner % CH == 0, state_rank % RPT == 0, state_rank <= 64, 16-byte-aligned rows.
-template <typename T>
+// CH (channels per CTA) is chosen by the launcher so that the grid fills the machine in one wave.
+template <typename T, int CH>
 __global__ void selscan1_kernel(bm_selscan1_args a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    Stage<T>* stages = reinterpret_cast<Stage<T>*>(smem_raw);
-    float* ytile = reinterpret_cast<float*>(smem_raw + 2 * sizeof(Stage<T>));  // [TCH][CH] pre-gate outputs
     const int R = a.state_rank, I = a.d_inner, S = a.seqlen;
+    const size_t sbytes = stage_bytes<T>(CH, R);
+    float* ytile = reinterpret_cast<float*>(smem_raw + 2 * sbytes);  // [TCH][CH] pre-gate outputs
     const int tpc = R / RPT;  // threads per channel
     const int tid = threadIdx.x, nthreads = blockDim.x;
     const int cl = tid / tpc, q = tid % tpc;  // channel in tile, state quarter
@@ -66,13 +73,13 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
     auto issue = [&](int chunk, int stg) {
         const int t0 = chunk * TCH;
         const int nt = min(TCH, S - t0);
-        Stage<T>& st = stages[stg];
+        StageView<T> st(smem_raw + stg * sbytes, CH, R);
         constexpr int VPR = CH / EPV;  // vectors per token row
         for (int e = tid; e < nt * VPR; e += nthreads) {
             int t = e / VPR, vv = (e % VPR) * EPV;
-            cp_async16(&st.delta[t][vv], dg + (int64_t)(t0 + t) * I + vv);
-            cp_async16(&st.u[t][vv], ug + (int64_t)(t0 + t) * I + vv);
-            if (zg) cp_async16(&st.z[t][vv], zg + (int64_t)(t0 + t) * I + vv);
+            cp_async16(&st.delta[t * CH + vv], dg + (int64_t)(t0 + t) * I + vv);
+            cp_async16(&st.u[t * CH + vv], ug + (int64_t)(t0 + t) * I + vv);
+            if (zg) cp_async16(&st.z[t * CH + vv], zg + (int64_t)(t0 + t) * I + vv);
         }
         const int bcv = nt * R / EPV;  // B / C rows of a chunk are contiguous in memory
         for (int e = tid; e < bcv; e += nthreads) {
@@ -90,7 +97,7 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
-        Stage<T>& st = stages[stg];
+        StageView<T> st(smem_raw + stg * sbytes, CH, R);
         const int t0 = chunk * TCH, nt = min(TCH, S - t0);
         // The recurrence only chains through h; everything else of TU tokens (loads, softplus, exp,
         // input term) is issued first so the dependent FMAs of the TU steps run back to back.
@@ -99,9 +106,9 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
             float dl[TU], uu[TU], ea[TU][RPT], bu[TU][RPT], ck[TU][RPT], part[TU];
 #pragma unroll
             for (int j = 0; j < TU; ++j) {
-                dl[j] = to_f32(st.delta[t + j][cl]);
+                dl[j] = to_f32(st.delta[(t + j) * CH + cl]);
                 if (a.delta_softplus) dl[j] = softplus_stock(dl[j] + dbias);
-                uu[j] = to_f32(st.u[t + j][cl]);
+                uu[j] = to_f32(st.u[(t + j) * CH + cl]);
                 const float du = dl[j] * uu[j];
 #pragma unroll
                 for (int k = 0; k < RPT; ++k) {
@@ -129,9 +136,9 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
             }
         }
         for (; t < nt; ++t) {
-            float delta = to_f32(st.delta[t][cl]);
+            float delta = to_f32(st.delta[t * CH + cl]);
             if (a.delta_softplus) delta = softplus_stock(delta + dbias);
-            const float u = to_f32(st.u[t][cl]);
+            const float u = to_f32(st.u[t * CH + cl]);
             const float du = delta * u;
             float part = 0.f;
 #pragma unroll
@@ -153,7 +160,7 @@ __global__ void selscan1_kernel(bm_selscan1_args a) {
 #pragma unroll
             for (int j = 0; j < EPV; ++j) {
                 float y = ytile[tt * CH + vv + j];
-                if (zg) y *= silu_f32(to_f32(st.z[tt][vv + j]));
+                if (zg) y *= silu_f32(to_f32(st.z[tt * CH + vv + j]));
                 outv[j] = from_f32<T>(y);
             }
             *reinterpret_cast<uint4*>(yg + (int64_t)(t0 + tt) * I + vv) = *reinterpret_cast<const uint4*>(outv);
@@ -204,13 +211,18 @@ int32_t launch(const bm_selscan1_args& a, cudaStream_t st) {
     const int tpc = R / RPT;
     const bool pow2 = tpc > 0 && (tpc & (tpc - 1)) == 0;
     constexpr int EPV = 16 / sizeof(T);
-    const bool fast = I % CH == 0 && R % RPT == 0 && R <= 64 && pow2 && tpc <= 32 && (R % EPV == 0);
+    const bool fast = I % 32 == 0 && R % RPT == 0 && R <= 64 && pow2 && tpc <= 32 && (R % EPV == 0);
     if (fast) {
-        size_t smem = 2 * sizeof(Stage<T>) + sizeof(float) * TCH * CH;
-        cudaError_t e = cudaFuncSetAttribute(selscan1_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        // 16 channels per CTA unless 32 already give every SM several CTAs: the sequence is walked serially,
+        // so the only parallelism is across CTAs and a second, partly filled wave doubles the run time
+        const bool wide = (int64_t)a.batch * (I / 32) >= 4 * 148;
+        const int ch = wide ? 32 : 16;
+        size_t smem = 2 * stage_bytes<T>(ch, R) + sizeof(float) * TCH * ch;
+        auto kern = wide ? selscan1_kernel<T, 32> : selscan1_kernel<T, 16>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(selscan1)");
-        unsigned grid = (unsigned)((int64_t)a.batch * (I / CH));
-        selscan1_kernel<T><<<grid, CH * tpc, smem, st>>>(a);
+        unsigned grid = (unsigned)((int64_t)a.batch * (I / ch));
+        kern<<<grid, ch * tpc, smem, st>>>(a);
         return check_launch("selscan1");
     }
     if (R > 256) return fail(BM_ERR_UNSUPPORTED, "state_rank %d above 256", R);
