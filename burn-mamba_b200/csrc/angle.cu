@@ -1,43 +1,95 @@
 // Cumulative data-dependent rotation angles of Mamba-3's Complex2D rotation
 // (src/mamba3/rotation/mod.rs:559-567, :653-679):
 //   theta[b, s, h, j] = prev[b, h, j] + sum_{t <= s} dt[b, t, h] * range * pi * tanh(rot[b, t, j]).
-// HBM-bound on the theta write.  One thread per (b, h, j) lane walks the sequence; consecutive
-// threads are consecutive j, so every load of rot and store of theta is coalesced, and the loop is
-// unrolled so several independent loads are in flight per thread.
+// HBM-bound on the theta write (b*s*h*a*4 bytes).  The sequence is cut into chunks of kChunk tokens and
+// scanned in three passes without any scratch memory: theta itself carries the chunk totals between them.
+//   pass A  one thread per (b, chunk, block of kHB heads, j): the chunk's sums -> theta[b, last row of chunk, h, j]
+//   pass B  one thread per (b, h, j): exclusive scan of those totals over the chunks, in place
+//           (+ prev), and the wrapped final angle -> last
+//   pass C  same threads as pass A: each reads its carries from the row pass B left them in, then walks the
+//           chunk writing theta (the carry row is the last row it overwrites)
+// A thread of passes A and C owns one rotation lane j for kHB heads, so tanh(rot) is evaluated once per
+// kHB heads, dt[b, t, h] is a warp-uniform (broadcast) load, and every theta
+// store is a full 128-byte line across the lanes of a warp.
 #include "common.cuh"
 
 using namespace bm;
 
 namespace {
 
-__global__ void angle_cumsum_kernel(bm_angle_cumsum_args a) {
+constexpr int kChunk = 64;   // tokens per chunk
+constexpr int kHB = 8;       // heads per thread
+
+__device__ __forceinline__ int chunk_last_row(int c, int S) { return min((c + 1) * kChunk, S) - 1; }
+
+template <bool kWrite>
+__global__ void angle_chunk_kernel(bm_angle_cumsum_args a, int nchunks, int nhb) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int A = a.nangles, H = a.nheads, S = a.seqlen;
+    if (idx >= (int64_t)a.batch * nchunks * nhb * A) return;
+    const int j = idx % A, hb = (idx / A) % nhb, c = (idx / ((int64_t)A * nhb)) % nchunks;
+    const int b = idx / ((int64_t)A * nhb * nchunks);
+    const int h0 = hb * kHB;
+    const float scale = a.range * 3.14159265358979323846f;
+    const int t0 = c * kChunk, t1 = min(t0 + kChunk, S);
+    const float* rot = a.rot + (int64_t)b * S * A + j;
+    const float* dt = a.dt + (int64_t)b * S * H + h0;
+    float* th = a.theta + (int64_t)b * S * H * A + (int64_t)h0 * A + j;
+    const int64_t carry_row = (int64_t)chunk_last_row(c, S) * H * A;
+    float run[kHB];
+#pragma unroll
+    for (int k = 0; k < kHB; ++k) run[k] = (kWrite && h0 + k < H) ? th[carry_row + (int64_t)k * A] : 0.f;
+    constexpr int U = 4;   // tokens whose loads are issued together
+    int t = t0;
+    for (; t + U <= t1; t += U) {
+        float r[U], d[U][kHB];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            r[u] = rot[(int64_t)(t + u) * A];
+#pragma unroll
+            for (int k = 0; k < kHB; ++k) d[u][k] = h0 + k < H ? dt[(int64_t)(t + u) * H + k] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const float v = tanhf(r[u]) * scale;
+            float* tr = th + (int64_t)(t + u) * H * A;
+#pragma unroll
+            for (int k = 0; k < kHB; ++k) {
+                run[k] = fmaf(d[u][k], v, run[k]);
+                if (kWrite && h0 + k < H) tr[(int64_t)k * A] = run[k];
+            }
+        }
+    }
+    for (; t < t1; ++t) {
+        const float v = tanhf(rot[(int64_t)t * A]) * scale;
+        float* tr = th + (int64_t)t * H * A;
+#pragma unroll
+        for (int k = 0; k < kHB; ++k) {
+            if (h0 + k < H) {
+                run[k] = fmaf(dt[(int64_t)t * H + k], v, run[k]);
+                if (kWrite) tr[(int64_t)k * A] = run[k];
+            }
+        }
+    }
+    if (!kWrite) {
+#pragma unroll
+        for (int k = 0; k < kHB; ++k)
+            if (h0 + k < H) th[carry_row + (int64_t)k * A] = run[k];
+    }
+}
+
+__global__ void angle_carry_kernel(bm_angle_cumsum_args a, int nchunks) {
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int A = a.nangles, H = a.nheads, S = a.seqlen;
     if (idx >= (int64_t)a.batch * H * A) return;
     const int j = idx % A, h = (idx / A) % H, b = idx / ((int64_t)A * H);
-    const float scale = a.range * 3.14159265358979323846f;
-    float run = a.prev ? a.prev[idx] : 0.f;
-    const float* rot = a.rot + (int64_t)b * S * A + j;
-    const float* dt = a.dt + (int64_t)b * S * H + h;
     float* th = a.theta + ((int64_t)b * S * H + h) * A + j;
-    constexpr int U = 8;
-    int s = 0;
-    for (; s + U <= S; s += U) {
-        float r[U], d[U];
-#pragma unroll
-        for (int k = 0; k < U; ++k) {
-            r[k] = rot[(int64_t)(s + k) * A];
-            d[k] = dt[(int64_t)(s + k) * H];
-        }
-#pragma unroll
-        for (int k = 0; k < U; ++k) {
-            run += d[k] * (tanhf(r[k]) * scale);
-            th[(int64_t)(s + k) * H * A] = run;
-        }
-    }
-    for (; s < S; ++s) {
-        run += dt[(int64_t)s * H] * (tanhf(rot[(int64_t)s * A]) * scale);
-        th[(int64_t)s * H * A] = run;
+    float run = a.prev ? a.prev[idx] : 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+        float* slot = th + (int64_t)chunk_last_row(c, S) * H * A;
+        const float total = *slot;
+        *slot = run;     // carry entering chunk c
+        run += total;
     }
     if (a.last) a.last[idx] = wrap_angle(run);
 }
@@ -54,7 +106,15 @@ extern "C" int32_t bm_angle_cumsum(const bm_angle_cumsum_args* a, void* stream) 
     BM_REQUIRE_PTR(a->theta);
     BM_OPTIONAL_PTR(a->prev);
     BM_OPTIONAL_PTR(a->last);
-    int64_t total = (int64_t)a->batch * a->nheads * a->nangles;
-    angle_cumsum_kernel<<<(unsigned)cdiv(total, 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(*a);
-    return check_launch("angle_cumsum");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int nchunks = (a->seqlen + kChunk - 1) / kChunk;
+    const int nhb = (a->nheads + kHB - 1) / kHB;
+    const int64_t per_chunk = (int64_t)a->batch * nchunks * nhb * a->nangles;
+    const int64_t per_lane = (int64_t)a->batch * a->nheads * a->nangles;
+    angle_chunk_kernel<false><<<(unsigned)cdiv(per_chunk, 128), 128, 0, st>>>(*a, nchunks, nhb);
+    if (int32_t e = check_launch("angle_cumsum (chunk totals)")) return e;
+    angle_carry_kernel<<<(unsigned)cdiv(per_lane, 128), 128, 0, st>>>(*a, nchunks);
+    if (int32_t e = check_launch("angle_cumsum (carries)")) return e;
+    angle_chunk_kernel<true><<<(unsigned)cdiv(per_chunk, 128), 128, 0, st>>>(*a, nchunks, nhb);
+    return check_launch("angle_cumsum (write)");
 }

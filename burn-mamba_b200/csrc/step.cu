@@ -251,8 +251,12 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
     float* st = a.state + (int64_t)bh * P * R;
     if (R % 4 == 0 && R <= 128 && M <= 4) {
         // Fast path: a lane owns 4 consecutive state columns of every row (one 128-bit load / store per
-        // row), keeps its slice of the rotated B / C and of the previous B in registers, and the warp
-        // works on two rows at a time so that two independent row loads are in flight.
+        // row) and keeps its slice of the rotated B / C and of the previous B in registers.  The warp
+        // works on NB rows at a time: all NB row loads are issued before the first is used, so that each
+        // warp keeps NB x 512 bytes in flight, and the NB x 4 per-lane partial outputs are reduced with
+        // one transposing butterfly (31 shuffles instead of 5 per value); lane 4 j + m then holds
+        // y[row j][m].
+        constexpr int NB = 8;
         const int r4 = lane * 4;
         const bool act = r4 < R;
         float4 bq[4], cq[4], pq[4];
@@ -263,56 +267,57 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
             cq[m] = on ? ld4(cs + m * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
             pq[m] = on ? ld4(bp + m * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        for (int p0 = warp; p0 < P; p0 += 2 * nwarps) {
-            const int rows[2] = {p0, p0 + nwarps};
-            float4 hv[2];
-            float xr[2], xp[2];
+        for (int p0 = warp * NB; p0 < P; p0 += NB * nwarps) {
+            float4 hv[NB];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const bool live = rows[j] < P;
-                hv[j] = (live && act) ? ld4(st + (int64_t)rows[j] * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                xr[j] = live ? a.x[(int64_t)bh * P + rows[j]] : 0.f;
-                xp[j] = live ? a.v_state[(int64_t)bh * P + rows[j]] : 0.f;
-            }
-            float part[2][4];
+            for (int j = 0; j < NB; ++j)
+                hv[j] = (p0 + j < P && act) ? ld4(st + (int64_t)(p0 + j) * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            // per-row scalars: lane j of the warp fetches those of row p0 + j, then they are broadcast
+            const int prow = p0 + (lane & (NB - 1));
+            const bool plive = prow < P;
+            const float xl = plive ? a.x[(int64_t)bh * P + prow] : 0.f;
+            const float xpl = plive ? a.v_state[(int64_t)bh * P + prow] : 0.f;
+            float mxl[4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int m = 0; m < 4; ++m)
+                mxl[m] = (m < M && plive && a.mimo_x) ? a.mimo_x[((int64_t)h * M + m) * P + prow] : 1.f;
+            float v[NB * 4];
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+                const float xr = __shfl_sync(0xffffffffu, xl, j), xp = __shfl_sync(0xffffffffu, xpl, j);
                 float4 h4 = make_float4(alpha * hv[j].x, alpha * hv[j].y, alpha * hv[j].z, alpha * hv[j].w);
 #pragma unroll
                 for (int m = 0; m < 4; ++m) {
+                    const float mx = __shfl_sync(0xffffffffu, mxl[m], j);
                     if (m < M) {
-                        const float mx = (a.mimo_x && rows[j] < P) ? a.mimo_x[((int64_t)h * M + m) * P + rows[j]] : 1.f;
-                        const float g = gamma * xr[j] * mx, bt = beta * xp[j] * mx;
+                        const float g = gamma * xr * mx, bt = beta * xp * mx;
                         h4.x = fmaf(g, bq[m].x, fmaf(bt, pq[m].x, h4.x));
                         h4.y = fmaf(g, bq[m].y, fmaf(bt, pq[m].y, h4.y));
                         h4.z = fmaf(g, bq[m].z, fmaf(bt, pq[m].z, h4.z));
                         h4.w = fmaf(g, bq[m].w, fmaf(bt, pq[m].w, h4.w));
                     }
                 }
-                if (rows[j] < P && act) st4(st + (int64_t)rows[j] * R + r4, h4);
+                if (p0 + j < P && act) st4(st + (int64_t)(p0 + j) * R + r4, h4);
 #pragma unroll
                 for (int m = 0; m < 4; ++m)
-                    part[j][m] = h4.x * cq[m].x + h4.y * cq[m].y + h4.z * cq[m].z + h4.w * cq[m].w;
+                    v[j * 4 + m] = h4.x * cq[m].x + h4.y * cq[m].y + h4.z * cq[m].z + h4.w * cq[m].w;
             }
+            // transposing butterfly: after the round with offset o a lane keeps the half of its values
+            // whose index bit matches its own lane bit, summed with the partner's copy of that half
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
+            for (int o = 16, n = NB * 2; o > 0; o >>= 1, n >>= 1) {
+                const bool up = (lane & o) != 0;
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
-#pragma unroll
-                    for (int m = 0; m < 4; ++m)
-                        if (m < M) part[j][m] += __shfl_xor_sync(0xffffffffu, part[j][m], o);
-            }
-            if (lane == 0) {
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    if (rows[j] < P) {
-#pragma unroll
-                        for (int m = 0; m < 4; ++m)
-                            if (m < M) a.y[(((int64_t)b * M + m) * H + h) * P + rows[j]] = part[j][m];
-                        a.v_state[(int64_t)bh * P + rows[j]] = xr[j];
-                    }
+                for (int k = 0; k < n; ++k) {
+                    const float send = up ? v[k] : v[k + n];
+                    const float keep = up ? v[k + n] : v[k];
+                    v[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
                 }
             }
+            // v[0] of lane l is the total of value index l = 4 * row + m
+            const int yrow = p0 + (lane >> 2), ym = lane & 3;
+            if (yrow < P && ym < M) a.y[(((int64_t)b * M + ym) * H + h) * P + yrow] = v[0];
+            if (plive && lane < NB) a.v_state[(int64_t)bh * P + prow] = xl;
         }
     } else {
     for (int p = warp; p < P; p += nwarps) {

@@ -1,10 +1,12 @@
 """Block-level GPU parity through the reference-shaped host interface (Mamba2.forward / step,
-Mamba2SsdInput.run): the CPU-runnable benchmark configuration and the forward == step property."""
+Mamba2SsdInput.run, Mamba3.forward_single_ssd / forward_double_ssd / step_double_ssd): the CPU-runnable
+benchmark configuration and the forward == step property."""
 import numpy as np
 import pytest
 import torch
 
 from oracle import mamba2 as o2
+from oracle import mamba3 as o3
 from oracle.numerics import rel_l2, bf16_round
 
 pytestmark = pytest.mark.gpu
@@ -88,3 +90,58 @@ def test_decode_prefix_equals_forward_at_the_2_7b_head_shape(bm):
     got = torch.stack(steps, 1)
     assert rel_l2(got.float().cpu().numpy(), out.float().cpu().numpy()) <= 2e-2
     assert rel_l2(c.ssm_bhpr.cpu().numpy(), cache.ssm_bhpr.cpu().numpy()) <= 2e-2
+
+
+# ------------------------------------------------------------------ Mamba-3 block
+def _m3_cache(rng, w, bsz, scale=0.1):
+    c = o3.zero_cache(w, bsz)
+    return {k: (scale * rng.standard_normal(v.shape)).astype(np.float32) for k, v in c.items()}
+
+
+def _to_dev(cache):
+    return {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in cache.items()}
+
+
+@pytest.mark.parametrize("m,g,frac", [(1, 1, 1.0), (2, 1, 1.0), (4, 2, 0.5)])
+def test_mamba3_block_forward_matches_oracle(bm, m, g, frac):
+    """Both prefill pathways of the block against the oracle's float64 block (which itself holds
+    single == double == recurrence, tests/test_oracle_invariants.py) from a random cache: output and all
+    four cache tensors."""
+    rng = np.random.Generator(np.random.PCG64(11 + m))
+    w = o3.Mamba3Weights(rng, d_model=48, d_inner=64, nheads=4, state_rank=16, ngroups=g, mimo_rank=m,
+                         rope_fraction=frac)
+    bsz, s = 2, 37
+    u = rng.standard_normal((bsz, s, 48)).astype(np.float32)
+    c0 = _m3_cache(rng, w, bsz)
+    c64 = {k: v.astype(np.float64) for k, v in c0.items()}
+    want_out, want_cache, _ = o3.block_forward_single(w, u.astype(np.float64), c64, chunk_len=8)
+    blk = bm.Mamba3.from_oracle_weights(w, "cuda")
+    for fwd in (blk.forward_single_ssd, blk.forward_double_ssd):
+        out, cache = fwd(torch.from_numpy(u).cuda(), _to_dev(c0), chunk_len=8)
+        assert rel_l2(out.cpu().numpy(), want_out) <= 1e-4, fwd.__name__
+        for k in ("ssm", "k", "v"):
+            assert rel_l2(cache[k].cpu().numpy(), want_cache[k]) <= 1e-4, (fwd.__name__, k)
+        assert np.abs(cache["angle"].cpu().numpy() - want_cache["angle"]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_mamba3_block_forward_equals_unrolled_step(bm, m):
+    """forward == unrolled step_double_ssd on the output and the cache, CUDA vs CUDA
+    (the property the reference asserts for its block, src/mamba3/mamba3/tests.rs)."""
+    rng = np.random.Generator(np.random.PCG64(21 + m))
+    w = o3.Mamba3Weights(rng, d_model=32, d_inner=64, nheads=4, state_rank=16, ngroups=1, mimo_rank=m)
+    blk = bm.Mamba3.from_oracle_weights(w, "cuda")
+    bsz, s = 2, 19
+    u = torch.from_numpy(rng.standard_normal((bsz, s, 32)).astype(np.float32)).cuda()
+    c0 = _m3_cache(rng, w, bsz)
+    out, cache = blk.forward_double_ssd(u, _to_dev(c0), chunk_len=8)
+    c = _to_dev(c0)
+    outs = []
+    for t in range(s):
+        o, c = blk.step_double_ssd(u[:, t].contiguous(), c)
+        outs.append(o)
+    stepped = torch.stack(outs, dim=1)
+    assert (out - stepped).abs().max().item() <= 1e-4
+    for k in ("ssm", "k", "v"):
+        assert rel_l2(cache[k].cpu().numpy(), c[k].cpu().numpy()) <= 1e-4, k
+    assert (cache["angle"] - c["angle"]).abs().max().item() <= 1e-4
