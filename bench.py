@@ -186,24 +186,58 @@ def run_ours(args):
         return bm.ops.ssd2_fwd(devt["x"], devt["dt"], devt["a"], devt["b"], devt["c"], devt["d"], None,
                                chunk_len=c["chunk_len"], path="auto")
 
+    # End-to-end leg: every step copies its inputs from pinned host memory, runs the SSD and reads y and the
+    # final state back.  The three stages run on three streams with two sets of device input buffers, so
+    # the upload of step i+1 and the download of step i-1 overlap the kernel of step i (PCIe is full duplex);
+    # a step still cannot start before its own inputs have landed, nor finish before its outputs are home.
+    s_in, s_comp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    in_bufs = [{k: torch.empty_like(devt[k]) for k in ("x", "dt", "b", "c")} for _ in range(2)]
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    in_free = [torch.cuda.Event() for _ in range(2)]
+    e2e_count = [0]
+
     def step_e2e():
-        t = {k: host[k].to(dev, non_blocking=True) for k in ("x", "dt", "b", "c")}
-        y, hf = bm.ops.ssd2_fwd(t["x"], t["dt"], devt["a"], t["b"], t["c"], devt["d"], None,
-                                chunk_len=c["chunk_len"], path="auto")
-        y_host.copy_(y, non_blocking=True)
-        h_host.copy_(hf, non_blocking=True)
+        i = e2e_count[0] & 1
+        e2e_count[0] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(in_free[i])            # the kernel two steps back has finished with this set
+            for k in ("x", "dt", "b", "c"):
+                in_bufs[i][k].copy_(host[k], non_blocking=True)
+            in_ready[i].record(s_in)
+        with torch.cuda.stream(s_comp):
+            s_comp.wait_event(in_ready[i])
+            t = in_bufs[i]
+            y, hf = bm.ops.ssd2_fwd(t["x"], t["dt"], devt["a"], t["b"], t["c"], devt["d"], None,
+                                    chunk_len=c["chunk_len"], path="auto")
+            in_free[i].record(s_comp)
+            done = torch.cuda.Event()
+            done.record(s_comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            y_host.copy_(y, non_blocking=True)
+            h_host.copy_(hf, non_blocking=True)
+            y.record_stream(s_out)
+            hf.record_stream(s_out)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, steps, streams=()):
+        """CUDA-event time of `steps` calls of fn.  `streams`: side streams fn issues work on; they start
+        after the first event and the second event waits for all of them."""
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         ev0.record()
+        for st in streams:
+            st.wait_event(ev0)
         for _ in range(steps):
             fn()
+        for st in streams:
+            e = torch.cuda.Event()
+            e.record(st)
+            torch.cuda.current_stream().wait_event(e)
         ev1.record()
         barrier()
         ms = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
@@ -241,13 +275,13 @@ def run_ours(args):
     st = bm.ops.last_workspace_status()
     if st != 0:
         raise RuntimeError(f"tensor-core kernel reported status {st} during the timed region")
-    e2e_steps = max(1, min(args.steps, 10))
+    e2e_steps = max(1, min(args.steps, 20))
     if args.profile:  # kernel-only run for ncu captures: no end-to-end leg, no CPU arm
         ms_e2e = float("nan")
     else:
         for _ in range(2):
             step_e2e()
-        ms_e2e = timed(step_e2e, e2e_steps)
+        ms_e2e = timed(step_e2e, e2e_steps, streams=(s_in, s_comp, s_out))
 
     tokens = c["batch"] * c["seqlen"]
     ms_step = ms / args.steps

@@ -41,12 +41,17 @@ constexpr uint32_t kPanel = 16384;               // [128 rows x 128 B]
 constexpr uint32_t kOffC = 0;                    // 2 stages x 2 panels
 constexpr uint32_t kOffB = 65536;                // 2 stages x 2 panels
 constexpr uint32_t kOffX = 131072;               // 2 stages x 1 panel
-constexpr uint32_t kOffXw = 163840;              // 2 buffers x 1 panel (each reused as the y staging tile)
+constexpr uint32_t kOffXw = 163840;              // 2 buffers x 1 panel
 constexpr uint32_t kOffH = 196608;
-constexpr uint32_t kOffCum = 212992;             // kCumStages x (5 arrays x 128 floats + flag)
-constexpr uint32_t kCumStageBytes = 5 * T * 4 + 16;  // + the tile's factored-path flag
-constexpr uint32_t kOffBar = kOffCum + kCumStages * kCumStageBytes;
-constexpr uint32_t kSmemBytes = kOffBar + 512 + 1024;  // barriers + alignment slack
+constexpr uint32_t kOffCum = 212992;             // kCumStages x (4 arrays x 128 floats + flag)
+constexpr uint32_t kCumStageBytes = 4 * T * 4 + 16;  // cum, dt, state weight, column factor + the tile's flag
+constexpr int kCumDt = T, kCumW = 2 * T, kCumColf = 3 * T, kCumFlag = 4 * T;   // float offsets inside a stage
+constexpr uint32_t kOffStage = 222208;           // y staging: 4 warps x [32 rows x 64 B], 64-byte swizzle (1024-aligned)
+constexpr uint32_t kStageWarpBytes = 2048;
+constexpr uint32_t kOffBar = kOffStage + 4 * kStageWarpBytes;
+constexpr uint32_t kSmemBytes = kOffBar + 384 + 1024;  // barriers + alignment slack
+static_assert(kOffCum + kCumStages * kCumStageBytes <= kOffStage, "decay ring overlaps the staging tile");
+static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit of a CTA");
 constexpr uint32_t kLoadBytesCB = 4 * kPanel;
 constexpr uint32_t kLoadBytesX = kPanel;
 
@@ -62,7 +67,7 @@ struct Barriers {
     uint64_t cum_full[kCumStages], cum_empty[kCumStages];
     uint64_t cb_full[2], p_ready[2], p_free[2];
     uint64_t y1_full, y1_empty, y2_full, y2_empty;
-    uint64_t h_ready, h_free, xw_ready[2], xw_free[2], ystage_free[2], s_full[2], s_empty[2];
+    uint64_t h_ready, h_free, xw_ready[2], xw_free[2], xsrc_read[2], s_full[2], s_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -264,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             mbar_init(&bars->xld_full[i], 1);
             mbar_init(&bars->xld_empty[i], 8);    // 4 scaling warps + 4 epilogue warps (exact tiles) or the scaling warps again
             mbar_init(&bars->xw_free[i], 1);      // S commit: the scaled tile may be overwritten by y
-            mbar_init(&bars->ystage_free[i], 4);  // epilogue warps: their y store has drained the tile
+            mbar_init(&bars->xsrc_read[i], 4);    // epilogue warps: their rows of the skip-term source are in registers
             mbar_init(&bars->cb_full[i], 1);
             mbar_init(&bars->p_ready[i], 4);
             mbar_init(&bars->p_free[i], 1);       // Y1 commit: the P / CB accumulator may be overwritten
@@ -406,8 +411,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // ------------------------------------------------------------------ decay scan of dt
         // log2-domain cumulative sum of dt*A over the tile, plus the derived per-token factors.
         const float log2e = 1.4426950408889634f;
-        // The dt values of a tile are fetched one tile ahead (four loads per lane, issued together), so the
-        // global-memory latency is hidden behind the scan of the tile before.
+        // A lane owns four consecutive tokens: a serial sum over its four steps, one warp scan over the lane
+        // totals, and the per-token factors follow.  The dt values of a tile are fetched one tile ahead
+        // (four loads per lane, issued together), so the global-memory latency is hidden behind the tile before.
         TileWalk tw(tpu, prm.H), twn(tpu, prm.H);
         float nv[4];
         auto fetch = [&](const TileWalk& w) {
@@ -415,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const int left = prm.S - w.i * T;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int t = k * 32 + lane;
+                const int t = lane * 4 + k;
                 nv[k] = t < left ? row[(int64_t)t * prm.H] : 0.f;
             }
         };
@@ -423,51 +429,50 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         for (int it = 0; it < total; ++it, tw.next()) {
             const int h = tw.h, i = tw.i;
             const int cst = (it & (kCumStages - 1));
-            BM_WAIT_WARP(&bars->cum_empty[cst], ((it >> 2) & 1) ^ 1);
             float* cum2 = reinterpret_cast<float*>(smem + kOffCum + cst * kCumStageBytes);
-            float *dtv = cum2 + T, *erow = cum2 + 2 * T, *wv = cum2 + 3 * T, *colf = cum2 + 4 * T;
+            float *dtv = cum2 + kCumDt, *wv = cum2 + kCumW, *colf = cum2 + kCumColf;
             const float ah = prm.a[h] * log2e;
             const float bias = prm.dt_bias ? prm.dt_bias[h] : 0.f;
             const int left = prm.S - i * T;      // tokens of the sequence from the start of this tile on
+            float d4[4], c4[4];
+            float run = 0.f;
+            bool zero = false;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) dtv[k * 32 + lane] = nv[k];
+            for (int k = 0; k < 4; ++k) {
+                float v = nv[k];
+                const bool live = lane * 4 + k < left;
+                if (prm.dt_bias && live) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
+                zero |= live && !(v > 0.f);
+                d4[k] = v;
+                run = fmaf(v, ah, run);
+                c4[k] = run;
+            }
             twn.next();
             if (it + 1 < total) fetch(twn);
-            // pass 1, one 32-token block per step: inclusive scan within the block plus the carry of the
-            // blocks before it; the block's last lane holds the block-end value the column factor refers to
-            float carry = 0.f;
-            bool any_zero = false;
-#pragma unroll 1
-            for (int k = 0; k < 4; ++k) {
-                const int t = k * 32 + lane;
-                float v = dtv[t];
-                if (prm.dt_bias && t < left) {
-                    v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
-                    dtv[t] = v;
-                }
-                float incl = v * ah;
+            float incl = run;
 #pragma unroll
-                for (int o = 1; o < 32; o <<= 1) {
-                    const float up = __shfl_up_sync(0xffffffffu, incl, o);
-                    if (lane >= o) incl += up;
-                }
-                any_zero |= __any_sync(0xffffffffu, t < left && !(v > 0.f));
-                const float c = carry + incl;
-                carry = __shfl_sync(0xffffffffu, c, 31);
-                cum2[t] = c;
-                erow[t] = ex2(c);
-                colf[t] = v * ex2(carry - c);
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
             }
-            const float cend_tile = carry;
-            // pass 2: the state weight needs the tile-end value
-#pragma unroll 1
+            const float excl = incl - run;
+            const float cend_tile = __shfl_sync(0xffffffffu, incl, 31);
+            // end-of-32-block cumulative value: lane 8*blk+7 holds it as its inclusive total
+            const float cend_blk = __shfl_sync(0xffffffffu, incl, (lane & ~7) | 7);
+            const bool any_zero = __any_sync(0xffffffffu, zero);
+            BM_WAIT_WARP(&bars->cum_empty[cst], ((it >> 2) & 1) ^ 1);
+#pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int t = k * 32 + lane;
-                wv[t] = dtv[t] * ex2(cend_tile - cum2[t]);
+                const int t = lane * 4 + k;
+                const float c = excl + c4[k];
+                cum2[t] = c;
+                dtv[t] = d4[k];
+                wv[t] = d4[k] * ex2(cend_tile - c);
+                colf[t] = d4[k] * ex2(cend_blk - c);
             }
             // the factored form divides by dt_t (the D x term), so a tile with a zero step inside the
             // sequence takes the exact form as well
-            if (lane == 0) cum2[5 * T] = (fabsf(cend_tile) <= kFactoredMaxLog2Decay && !any_zero) ? 1.f : 0.f;
+            if (lane == 0) cum2[kCumFlag] = (fabsf(cend_tile) <= kFactoredMaxLog2Decay && !any_zero) ? 1.f : 0.f;
             __syncwarp();
             BM_TRACE(3, it, 0);
             if (lane == 0) mbar_arrive(&bars->cum_full[cst]);
@@ -487,14 +492,14 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         for (int it = 0; it < total; ++it, tw.next()) {
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
-            const float *dtv = cum2 + T, *colf = cum2 + 4 * T;
+            const float *dtv = cum2 + kCumDt, *colf = cum2 + kCumColf;
             BM_TRACE(4, it, 0);
             BM_WAIT_WARP(&bars->cum_full[cst], (it >> 2) & 1);
             BM_WAIT_WARP(&bars->cb_full[st], (it >> 1) & 1);
             BM_TRACE(4, it, 1);
             tc_fence_after();
             const float ct = cum2[t];
-            const bool factored = cum2[5 * T] != 0.f;
+            const bool factored = cum2[kCumFlag] != 0.f;
             const uint32_t cb = lane_addr + kColCB + st * 128;
             // blocks 0..q carry data (block q holds the diagonal), blocks above are zero
 #pragma unroll 1
@@ -552,7 +557,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         auto scale_x = [&](int it) {
             // Xw = X * dt * exp(cum_end - cum) for tile `it` (rows keep their swizzled positions)
             const int st = it & 1, cst = (it & (kCumStages - 1));
-            const float* wv = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 3 * T;
+            const float* wv = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + kCumW;
             const unsigned char* xs = smem + kOffX + st * kPanel;
             unsigned char* xw = smem + kOffXw + st * kPanel;
             const float w = wv[t];
@@ -581,7 +586,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 mbar_arrive(&bars->xld_empty[st]);
                 // factored tiles: nothing reads X after this pass, so each warp also makes the arrival that
                 // the epilogue warp of the same rows makes on exact tiles (where Y1 and D x still read X)
-                if (wv[2 * T] != 0.f) mbar_arrive(&bars->xld_empty[st]);
+                if (wv[kCumFlag - kCumW] != 0.f) mbar_arrive(&bars->xld_empty[st]);
             }
         };
         auto publish_state = [&]() {
@@ -609,10 +614,10 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const int itc = it < 0 ? 0 : it;
             const int i = tw.i, b = tw.b, h = tw.h;
             const int cst = (itc & (kCumStages - 1));
-            const float* erow = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 2 * T;
+            const float* cumv = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
             if (it >= 0) {
-                if (i == 0) {
+                if (__builtin_expect(i == 0, 0)) {
                     // unit start: initial state -> registers, published as the operand of this tile's
                     // readout (the operand tile is free once Y2(it-1) has completed)
 #pragma unroll
@@ -621,7 +626,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     publish_state();
                     BM_TRACE(5, it, 3);
                 }
-                if (prm.chunk_states && (i * T) % prm.Q == 0) {
+                if (__builtin_expect(prm.chunk_states != nullptr, 0) && (i * T) % prm.Q == 0) {
                     const int n = (i * T) / prm.Q;
                     float* cs = prm.chunk_states + (((int64_t)b * prm.NC + n) * prm.H + h) * P * R;
 #pragma unroll
@@ -629,11 +634,12 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 }
             }
             if (it + 1 < total) {
-                // scaled X of the next tile: its buffer was last read by S(it-1) (observed through
-                // s_full in the previous iteration) and, as y staging tile, by the store of tile it-1
                 BM_WAIT_WARP(&bars->xld_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
                 BM_WAIT_WARP(&bars->cum_full[((it + 1) & (kCumStages - 1))], ((it + 1) >> 2) & 1);
-                BM_WAIT_WARP(&bars->ystage_free[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
+                // the scaled tile of this parity still serves tile it-1: S(it-1) (seen complete through s_full
+                // in the previous iteration), Y1(it-1) on factored tiles, and the epilogue's skip-term rows
+                BM_WAIT_WARP(&bars->p_free[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
+                BM_WAIT_WARP(&bars->xsrc_read[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
                 BM_TRACE(5, itc, 0);
                 scale_x(it + 1);
                 BM_TRACE(3, itc, 1);
@@ -643,7 +649,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 BM_WAIT_WARP(&bars->s_full[it & 1], (it >> 1) & 1);
                 BM_TRACE(5, it, 1);
                 tc_fence_after();
-                const float decay = erow[T - 1];
+                const float decay = ex2(cumv[T - 1]);
                 const uint64_t decay2 = pair_f32(decay, decay);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -664,12 +670,12 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 }
                 // unless the unit ends here, the updated state is the readout operand of the next tile;
                 // the operand tile is free once Y2(it) has completed
-                if (i + 1 < tpu) {
+                if (__builtin_expect(i + 1 < tpu, 1)) {
                     BM_WAIT_WARP(&bars->h_free, it & 1);
                     publish_state();
                 }
                 BM_TRACE(5, it, 2);
-                if (i + 1 == tpu) {
+                if (__builtin_expect(i + 1 == tpu, 0)) {
 #pragma unroll
                     for (int p = 0; p < P; ++p) prm.h_final[state_base + (int64_t)p * R + t] = hst[p];
                 }
@@ -677,37 +683,48 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         }
     } else {
         // ------------------------------------------------------------------ epilogue
-        // y = Y1 + exp(cum_t) Y2, staged in the scaled-X tile of the same parity (dead once S(it) has
-        // completed) and written with one TMA store per warp (its own 32 rows).
+        // y = E' Y1 + exp(cum_t) Y2 + D x, written in two column halves through a small staging tile of
+        // the warp's own (32 rows x 64 bytes, 64-byte swizzle) with one TMA store each; the store of one
+        // half drains while the next half is computed.
         const int q = warp & 3, t = q * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+        unsigned char* stage = smem + kOffStage + q * kStageWarpBytes;
+        const uint32_t srow = lane * 64, sxor = (lane >> 1) & 3;   // 64-byte swizzle: chunk ^ ((row >> 1) & 3)
         TileWalk tw(tpu, prm.H);
         for (int it = 0; it < total; ++it, tw.next()) {
             const int i = tw.i, b = tw.b, h = tw.h;
             const int st = it & 1, cst = (it & (kCumStages - 1));
-            const float* erow = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes) + 2 * T;
-            unsigned char* ys = smem + kOffXw + st * kPanel;
+            const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             BM_WAIT_WARP(&bars->cum_full[cst], (it >> 2) & 1);
-            const float e = erow[t];
+            const float e = ex2(cum2[t]);
             // row factor of the factored mask: exp2(cum_t - cend); 1 for exact tiles
-            const float* cum2 = erow - 2 * T;
-            const bool factored = cum2[5 * T] != 0.f;
+            const bool factored = cum2[kCumFlag] != 0.f;
             const float e1 = factored ? ex2(cum2[t] - cum2[T - 1]) : 1.f;
-            // skip term D x: factored tiles recover x from the scaled tile (x w = Xw, w > 0 on these tiles;
-            // it is the very buffer this warp is about to overwrite with y), exact tiles read the X tile,
-            // which they hold until this pass has read it
-            const float wt = cum2[3 * T + t];
+            // skip term D x: factored tiles recover x from the scaled tile (x w = Xw, w > 0 on these tiles),
+            // exact tiles read the X tile, which they hold until Y1 has completed and this row is read
+            const float wt = cum2[kCumW + t];
             const float dsk = prm.d ? prm.d[h] : 0.f;
             const float dxw = factored ? (wt > 0.f ? dsk / wt : 0.f) : dsk;   // wt = 0 only on padding rows
-            const unsigned char* xsrc = factored ? ys : smem + kOffX + st * kPanel;
+            const unsigned char* xsrc = smem + (factored ? kOffXw : kOffX) + st * kPanel;
             const uint64_t ee = pair_f32(e, e), ee1 = pair_f32(e1, e1);
             const uint32_t dd = pack_bf16x2(dxw, dxw);
-            BM_WAIT_WARP(&bars->xw_free[st], (it >> 1) & 1);
+            // the source row is fetched before the accumulators are waited for (the tile has been in place
+            // since the scaling pass), so the scaled tile can be handed back for tile it+2 early
+            BM_WAIT_WARP(&bars->xw_ready[st], (it >> 1) & 1);
+            uint4 xrow[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                xrow[k] = *reinterpret_cast<const uint4*>(xsrc + sw128_offset(t, k));
+                asm volatile("" ::"r"(xrow[k].x), "r"(xrow[k].y), "r"(xrow[k].z), "r"(xrow[k].w));   // loads have landed
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->xsrc_read[st]);
             BM_WAIT_WARP(&bars->y2_full, it & 1);
             BM_WAIT_WARP(&bars->y1_full, it & 1);
+            if (!factored && lane == 0) mbar_arrive(&bars->xld_empty[st]);   // exact tiles: Y1 and this warp are done with X
             BM_TRACE(6, it, 0);
             tc_fence_after();
-#pragma unroll 1
+#pragma unroll
             for (int half = 0; half < 2; ++half) {
                 uint32_t y1[32], y2[32];
                 tmem_ld32(lane_addr + kColY1 + half * 32, y1);
@@ -722,12 +739,11 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                         mbar_arrive(&bars->y2_empty);
                     }
                 }
+                uint4 o[4];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int j = k * 8;
-                    const uint32_t off = sw128_offset(t, half * 4 + k);
-                    uint4* slot = reinterpret_cast<uint4*>(ys + off);
-                    const uint4 xv = *reinterpret_cast<const uint4*>(xsrc + off);
+                    const uint4 xv = xrow[half * 4 + k];
                     const uint32_t xw4[4] = {xv.x, xv.y, xv.z, xv.w};
                     uint32_t o4[4];
 #pragma unroll
@@ -737,22 +753,22 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                         // + (D / w_t) * Xw as one packed bf16 fma on the rounded result
                         asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(o4[m]) : "r"(xw4[m]), "r"(dd), "r"(pack_bf16x2_pair(acc)));
                     }
-                    const uint4 o = make_uint4(o4[0], o4[1], o4[2], o4[3]);
-                    *slot = o;
+                    o[k] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+                }
+                // the previous store of this warp must have drained the staging tile
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(stage + srow + ((k ^ sxor) << 4)) = o[k];
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_4d(&prm.tm_y, stage, half * 32, h, i * T + q * 32, b);
+                    tma_store_commit();
                 }
             }
-            fence_proxy_async_smem();
-            __syncwarp();
             BM_TRACE(6, it, 1);
-            if (lane == 0) {
-                if (!factored) mbar_arrive(&bars->xld_empty[st]);   // exact tiles: the X tile has been read
-                tma_store_4d(&prm.tm_y, ys + q * 4096, 0, h, i * T + q * 32, b);
-                tma_store_commit();
-                mbar_arrive(&bars->cum_empty[cst]);
-                BM_TRACE(3, it, 2);
-                tma_store_wait_read<0>();
-                mbar_arrive(&bars->ystage_free[st]);
-            }
+            if (lane == 0) mbar_arrive(&bars->cum_empty[cst]);
             __syncwarp();
             BM_TRACE(6, it, 2);
         }
@@ -805,16 +821,16 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     {
         const uint64_t dims[4] = {(uint64_t)P, H, S, B};
         const uint64_t strides[3] = {(uint64_t)P * 2, H * P * 2, S * H * P * 2};
-        const uint32_t box_y[4] = {64, 1, 32, 1};  // one epilogue warp's rows per store
-        if (!make_tensor_map_bf16(&prm.tm_x, a->x, 4, dims, strides, box, true, &err) ||
-            !make_tensor_map_bf16(&prm.tm_y, a->y, 4, dims, strides, box_y, true, &err))
+        const uint32_t box_y[4] = {32, 1, 32, 1};  // one column half of one epilogue warp's rows per store
+        if (!make_tensor_map_bf16(&prm.tm_x, a->x, 4, dims, strides, box, 128, &err) ||
+            !make_tensor_map_bf16(&prm.tm_y, a->y, 4, dims, strides, box_y, 64, &err))
             return fail(BM_ERR_CUDA, "tensor map (x/y): %s", err);
     }
     {
         const uint64_t dims[4] = {(uint64_t)R, G, S, B};
         const uint64_t strides[3] = {(uint64_t)R * 2, G * R * 2, S * G * R * 2};
-        if (!make_tensor_map_bf16(&prm.tm_b, a->b, 4, dims, strides, box, true, &err) ||
-            !make_tensor_map_bf16(&prm.tm_c, a->c, 4, dims, strides, box, true, &err))
+        if (!make_tensor_map_bf16(&prm.tm_b, a->b, 4, dims, strides, box, 128, &err) ||
+            !make_tensor_map_bf16(&prm.tm_c, a->c, 4, dims, strides, box, 128, &err))
             return fail(BM_ERR_CUDA, "tensor map (b/c): %s", err);
     }
     prm.dt = a->dt, prm.a = a->a, prm.d = a->d, prm.h0 = a->h0, prm.dt_bias = a->dt_bias;

@@ -19,7 +19,7 @@ namespace tc {
 // byte strides of dims 1..rank-1.  Returns false (with *err set) if the driver entry point is missing
 // or the encode call fails.
 bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                          const uint32_t* box, bool swizzle128, const char** err);
+                          const uint32_t* box, int swizzle_bytes, const char** err);
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------

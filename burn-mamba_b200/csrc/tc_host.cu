@@ -25,7 +25,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
-                          const uint32_t* box, bool swizzle128, const char** err) {
+                          const uint32_t* box, int swizzle_bytes, const char** err) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) {
         *err = "cuTensorMapEncodeTiled not available from the driver";
@@ -40,7 +40,10 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const ui
         if (i + 1 < rank) s[i] = strides[i];
     }
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                    : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                          : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         *err = "cuTensorMapEncodeTiled failed";
