@@ -361,7 +361,7 @@ def decode_step_leg(torch, bm, dev, layers=64, batch=256, steps=8):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one ssd2_tc_kernel launch, from the ncu capture
 # summarised under profiles/, scaled by units from the batch-2 capture to the batch-8 launch.
-TRAFFIC_BYTES_PER_LAUNCH = 550.3e6  # 137.6 MB captured at batch 2 (profiles/ssd2_tc_kernel_prefill_2.7B.md) x 4
+TRAFFIC_BYTES_PER_LAUNCH = 556.1e6  # 139.0 MB captured at batch 2 (profiles/ssd2_tc_kernel_prefill_2.7B.md) x 4
 
 
 def cpu_sample(batch, nheads):
