@@ -184,6 +184,26 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
         if (!__all_sync(0xffffffffu, ok_)) goto timed_out;         \
     } while (0)
 
+// Several barriers at once: the phases are first tested without blocking, back to back, so that the usual
+// case (all of them already complete) costs one shared-memory round trip instead of one per barrier.
+#define BM_WAIT_WARP2(b1, p1, b2, p2)                                              \
+    do {                                                                           \
+        const bool f_ = mbar_test((b1), (p1)) & mbar_test((b2), (p2));             \
+        if (!__all_sync(0xffffffffu, f_)) {                                        \
+            BM_WAIT_WARP((b1), (p1));                                              \
+            BM_WAIT_WARP((b2), (p2));                                              \
+        }                                                                          \
+    } while (0)
+#define BM_WAIT_WARP3(b1, p1, b2, p2, b3, p3)                                      \
+    do {                                                                           \
+        const bool f_ = mbar_test((b1), (p1)) & mbar_test((b2), (p2)) & mbar_test((b3), (p3)); \
+        if (!__all_sync(0xffffffffu, f_)) {                                        \
+            BM_WAIT_WARP((b1), (p1));                                              \
+            BM_WAIT_WARP((b2), (p2));                                              \
+            BM_WAIT_WARP((b3), (p3));                                              \
+        }                                                                          \
+    } while (0)
+
 // One 32-column block of the decay mask: out = bf16 pairs of P for columns [32c, 32c + 32).
 // Exact form (any decay): the kernel exp(cum_t - cum_s) dt_s is applied here.
 //   below the diagonal block:  rowfac * colf[s]   (both factors <= 1, reference = end of column block)
@@ -494,8 +514,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + kCumDt, *colf = cum2 + kCumColf;
             BM_TRACE(4, it, 0);
-            BM_WAIT_WARP(&bars->cum_full[cst], (it >> 2) & 1);
-            BM_WAIT_WARP(&bars->cb_full[st], (it >> 1) & 1);
+            BM_WAIT_WARP2(&bars->cum_full[cst], (it >> 2) & 1, &bars->cb_full[st], (it >> 1) & 1);
             BM_TRACE(4, it, 1);
             tc_fence_after();
             const float ct = cum2[t];
@@ -529,9 +548,8 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 // whole, for the other three warps' parts of P, for the B operand and for the epilogue to
                 // have drained Y1(it-1); then one lane issues.  Factored tiles multiply by the scaled tile
                 // Xw, exact tiles by X itself.
-                BM_WAIT_WARP(&bars->p_ready[st], (it >> 1) & 1);
-                BM_WAIT_WARP(&bars->xw_ready[st], (it >> 1) & 1);
-                BM_WAIT_WARP(&bars->y1_empty, (it & 1) ^ 1);
+                BM_WAIT_WARP3(&bars->p_ready[st], (it >> 1) & 1, &bars->xw_ready[st], (it >> 1) & 1,
+                              &bars->y1_empty, (it & 1) ^ 1);
                 BM_TRACE(1, it, 1);
                 tc_fence_after();
                 if (lane == 0) {
@@ -634,12 +652,12 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 }
             }
             if (it + 1 < total) {
-                BM_WAIT_WARP(&bars->xld_full[(it + 1) & 1], ((it + 1) >> 1) & 1);
-                BM_WAIT_WARP(&bars->cum_full[((it + 1) & (kCumStages - 1))], ((it + 1) >> 2) & 1);
+                BM_WAIT_WARP2(&bars->xld_full[(it + 1) & 1], ((it + 1) >> 1) & 1,
+                              &bars->cum_full[((it + 1) & (kCumStages - 1))], ((it + 1) >> 2) & 1);
                 // the scaled tile of this parity still serves tile it-1: S(it-1) (seen complete through s_full
                 // in the previous iteration), Y1(it-1) on factored tiles, and the epilogue's skip-term rows
-                BM_WAIT_WARP(&bars->p_free[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
-                BM_WAIT_WARP(&bars->xsrc_read[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
+                BM_WAIT_WARP2(&bars->p_free[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1,
+                              &bars->xsrc_read[(it + 1) & 1], (((it + 1) >> 1) & 1) ^ 1);
                 BM_TRACE(5, itc, 0);
                 scale_x(it + 1);
                 BM_TRACE(3, itc, 1);
@@ -719,8 +737,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->xsrc_read[st]);
-            BM_WAIT_WARP(&bars->y2_full, it & 1);
-            BM_WAIT_WARP(&bars->y1_full, it & 1);
+            BM_WAIT_WARP2(&bars->y2_full, it & 1, &bars->y1_full, it & 1);
             if (!factored && lane == 0) mbar_arrive(&bars->xld_empty[st]);   // exact tiles: Y1 and this warp are done with X
             BM_TRACE(6, it, 0);
             tc_fence_after();
