@@ -16,6 +16,7 @@ BM_ERR_WORKSPACE_TOO_SMALL, BM_ERR_CUDA, BM_ERR_TIMEOUT = -5, -6, -7
 BM_DTYPE_F32, BM_DTYPE_BF16 = 0, 1
 BM_PATH_AUTO, BM_PATH_EXACT, BM_PATH_TENSOR = 0, 1, 2
 BM_SSD2_NOALLOC_SCRATCH_BYTES = 32 << 20
+BM_DEBUG_STALL_LOADS = 0x57A11   # bm_ssd2_fwd_args.reserved: test hook that makes a bounded wait run out
 
 _i32, _f32, _vp = C.c_int32, C.c_float, C.c_void_p
 

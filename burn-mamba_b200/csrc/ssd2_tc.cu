@@ -18,7 +18,9 @@
 // allocation + MMA issue for the state chain, warp 3 decay scan of dt, warps 4-7 mask pass (CB -> P),
 // warps 8-11 X scaling and state update, warps 12-15 epilogue.
 // Every wait is bounded; a wait that gives up stores BM_ERR_TIMEOUT in the status word of the
-// workspace and all roles leave their loops.
+// workspace and raises the CTA's abort flag, which every other wait loop polls, so all roles leave
+// their loops within a few thousand polls; the MMA issuers and the TMA producer then wait (bounded
+// again) for what they still have in flight before TMEM is released.
 #include "ssd2_tc.cuh"
 #include "tc_common.cuh"
 
@@ -34,7 +36,10 @@ constexpr int kThreads = 512;
 constexpr int kCumStages = 4;
 // Tiles whose total log2 decay |cend| stays below this use the factored mask: every factor
 // exp2(+-cend) then stays far inside the float32 / bfloat16 exponent range.
-constexpr float kFactoredMaxLog2Decay = 100.f;  // non-blocking polls of an idle issuer before it gives up (~ seconds)
+constexpr float kFactoredMaxLog2Decay = 100.f;
+// ... and whose per-row weight dt_t * 2^(cend - cum_t) of every live row stays above this floor: the
+// factored form recovers the skip term D x by dividing the scaled tile by that weight.
+constexpr float kFactoredMinRowWeight = 8.6736174e-19f;   // 2^-60
 
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kPanel = 16384;               // [128 rows x 128 B]
@@ -68,6 +73,7 @@ struct Barriers {
     uint64_t cb_full[2], p_ready[2], p_free[2];
     uint64_t y1_full, y1_empty, y2_full, y2_empty;
     uint64_t h_ready, h_free, xw_ready[2], xw_free[2], xsrc_read[2], s_full[2], s_empty[2];
+    uint64_t drain[3];                      // timeout path only: one per MMA-issuing thread
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -85,6 +91,8 @@ struct alignas(64) Params {
     int* status;
     long long* trace;
     int B, S, H, G, Q, NC, tiles_per_unit, num_units;
+    uint32_t wait_budget;   // polls per bounded wait
+    int stall_loads;        // test hook: the TMA producer issues nothing, so the first wait runs out
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -160,14 +168,15 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
 
 // Bounded waits, inline: a short try_wait loop with an iteration budget.  A wait that runs out of budget
 // leaves through the `timed_out` label at the end of the kernel, which records BM_ERR_TIMEOUT and raises
-// the CTA's abort flag.  (Calls into an out-of-line wait cost the single-thread roles more than the wait
+// the CTA's abort flag; the budget and the flag are looked at once every 1024 polls.  (Calls into an out-of-line wait cost the single-thread roles more than the wait
 // itself: their code is executed once per tile and every jump is a fresh instruction fetch.)
+#define BM_GIVE_UP(n) ((((n) & 1023u) == 0u) && ((n) >= prm.wait_budget || *abort_flag != 0u))
 #define BM_WAIT(bar, par)                                          \
     do {                                                           \
         uint32_t n_ = 0;                                           \
         _Pragma("unroll 1")                                        \
         while (!mbar_try_wait((bar), (par)))                       \
-            if (++n_ >= kWaitBudget) goto timed_out;               \
+            if (++n_, BM_GIVE_UP(n_)) goto timed_out;              \
     } while (0)
 // The same for a whole warp; the leave/stay decision is made warp-uniform so that no lane is left behind
 // at a later __syncwarp or .aligned tcgen05 instruction.
@@ -177,7 +186,7 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
         bool ok_ = true;                                           \
         _Pragma("unroll 1")                                        \
         while (!mbar_try_wait((bar), (par)))                       \
-            if (++n_ >= kWaitBudget) {                             \
+            if (++n_, BM_GIVE_UP(n_)) {                            \
                 ok_ = false;                                       \
                 break;                                             \
             }                                                      \
@@ -307,6 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         mbar_init(&bars->h_free, 1);
         mbar_init(&bars->y2_full, 1);
         mbar_init(&bars->y2_empty, 4);
+        for (int i = 0; i < 3; ++i) mbar_init(&bars->drain[i], 1);
         bars->abort_flag = 0;
         fence_mbar_init();
     }
@@ -327,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
     const uint32_t c_base = smem_u32(smem + kOffC), b_base = smem_u32(smem + kOffB);
     const uint32_t x_base = smem_u32(smem + kOffX), xw_base = smem_u32(smem + kOffXw), h_base = smem_u32(smem + kOffH);
 
+    int x_issued = 0, cb_issued = 0;   // TMA producer: tiles whose X / C+B loads have been issued
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -335,7 +346,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             tma_prefetch_desc(&prm.tm_c);
             tma_prefetch_desc(&prm.tm_y);
             TileWalk tw(tpu, prm.H);
-            for (int it = 0; it < total; ++it, tw.next()) {
+            for (int it = 0; it < (prm.stall_loads ? 0 : total); ++it, tw.next()) {
                 const int b = tw.b, h = tw.h, g = h / hpg;
                 const int st = it & 1, s0 = tw.i * T;
                 // X stage first: it is released early (by the scaling pass of the tile two back; on exact
@@ -344,6 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 BM_TRACE(0, it, 1);
                 mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
                 tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, s0, b);
+                x_issued = it + 1;
                 // C + B stage: released once CB, Y2 and S of the tile two back have completed
                 BM_WAIT(&bars->cbld_empty[st], ((it >> 1) & 1) ^ 1);
                 BM_TRACE(0, it, 0);
@@ -354,6 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 tma_load_4d(cs + kPanel, &prm.tm_c, &bars->cbld_full[st], 64, g, s0, b);
                 tma_load_4d(bs, &prm.tm_b, &bars->cbld_full[st], 0, g, s0, b);
                 tma_load_4d(bs + kPanel, &prm.tm_b, &bars->cbld_full[st], 64, g, s0, b);
+                cb_issued = it + 1;
             }
         }
     } else if (warp == 1) {
@@ -481,18 +494,22 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const float cend_blk = __shfl_sync(0xffffffffu, incl, (lane & ~7) | 7);
             const bool any_zero = __any_sync(0xffffffffu, zero);
             BM_WAIT_WARP(&bars->cum_empty[cst], ((it >> 2) & 1) ^ 1);
+            bool weak = false;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const int t = lane * 4 + k;
                 const float c = excl + c4[k];
+                const float w = d4[k] * ex2(cend_tile - c);
                 cum2[t] = c;
                 dtv[t] = d4[k];
-                wv[t] = d4[k] * ex2(cend_tile - c);
+                wv[t] = w;
                 colf[t] = d4[k] * ex2(cend_blk - c);
+                weak |= (t < left) && !(w >= kFactoredMinRowWeight);
             }
-            // the factored form divides by dt_t (the D x term), so a tile with a zero step inside the
-            // sequence takes the exact form as well
-            if (lane == 0) cum2[kCumFlag] = (fabsf(cend_tile) <= kFactoredMaxLog2Decay && !any_zero) ? 1.f : 0.f;
+            // the factored form divides by the row weight w_t (the D x term): a tile with a live row whose
+            // weight is zero, denormal or merely tiny takes the exact form
+            const bool any_weak = __any_sync(0xffffffffu, weak) || any_zero;
+            if (lane == 0) cum2[kCumFlag] = (fabsf(cend_tile) <= kFactoredMaxLog2Decay && !any_weak) ? 1.f : 0.f;
             __syncwarp();
             BM_TRACE(3, it, 0);
             if (lane == 0) mbar_arrive(&bars->cum_full[cst]);
@@ -798,6 +815,25 @@ done:
     if (warp >= 12 && lane == 0) tma_store_wait_all<0>();
     tc_fence_before();
     __syncthreads();
+    if (*abort_flag != 0u) {
+        // A wait gave up somewhere in this CTA and every role has left its loop.  Before TMEM goes back,
+        // each thread that issued asynchronous work waits -- bounded again -- for what it may still have in
+        // flight: the MMA issuers through a commit onto a barrier of their own, the producer through the
+        // full barriers of the (at most two) stages it loaded last.
+        if (lane == 0 && (warp == 1 || warp == 2 || warp == 4)) {
+            uint64_t* db = &bars->drain[warp == 4 ? 2 : warp - 1];
+            umma_commit(db);
+            for (uint32_t n = 0; n < prm.wait_budget && !mbar_try_wait(db, 0); ++n) {}
+        }
+        if (warp == 0 && lane == 0) {
+            for (int k = x_issued - 1; k >= 0 && k >= x_issued - 2; --k)
+                for (uint32_t n = 0; n < prm.wait_budget && !mbar_try_wait(&bars->xld_full[k & 1], (k >> 1) & 1); ++n) {}
+            for (int k = cb_issued - 1; k >= 0 && k >= cb_issued - 2; --k)
+                for (uint32_t n = 0; n < prm.wait_budget && !mbar_try_wait(&bars->cbld_full[k & 1], (k >> 1) & 1); ++n) {}
+        }
+        tc_fence_before();
+        __syncthreads();
+    }
     if (warp == 2) tmem_dealloc(tmem, 512);
 }
 
@@ -859,6 +895,10 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     prm.NC = (int)cdiv(a->seqlen, a->chunk_len);
     prm.tiles_per_unit = (int)cdiv(a->seqlen, T);
     prm.num_units = a->batch * a->nheads;
+    // `reserved` carries one test-only request: BM_DEBUG_STALL_LOADS makes the producer issue nothing and
+    // shortens the wait budget, so that a bounded wait runs out and the error path can be exercised
+    prm.stall_loads = (a->reserved == BM_DEBUG_STALL_LOADS) ? 1 : 0;
+    prm.wait_budget = prm.stall_loads ? (1u << 12) : kWaitBudget;
     {
         cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd2_tc_kernel)");

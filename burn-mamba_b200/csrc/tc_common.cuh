@@ -1,7 +1,6 @@
 // Blackwell (sm_100a) primitives used by the tensor-core kernels: mbarrier, TMA (no multicast),
 // TMEM allocation, tcgen05.mma / commit / ld / st, UMMA shared-memory and instruction descriptors.
-// Every wait is bounded: a wait that runs out of its budget returns false and the caller records a
-// timeout status instead of spinning forever.
+// Waits are built by the kernels from mbar_try_wait / mbar_test with an iteration budget (kWaitBudget).
 #pragma once
 
 #include <cuda.h>
@@ -61,14 +60,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: ~kWaitBudget polls (each try_wait itself blocks for a short hardware-defined time).
-// Returns false when the budget ran out; the caller must then bail out through its error path.
+// Budget of a bounded wait in polls (each try_wait itself blocks for a short hardware-defined time).  A
+// wait that runs out of it makes the kernel record a timeout status and return instead of spinning on.
 constexpr uint32_t kWaitBudget = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kWaitBudget; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operands)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -129,18 +123,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-
 // ---------------------------------------------------------------------------------------------
 // UMMA descriptors (bf16 operands, 128-byte swizzle, tiles based on 1024-byte-aligned addresses)
 // ---------------------------------------------------------------------------------------------

@@ -61,9 +61,10 @@ def last_workspace_status():
 
 
 def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bias=None, dt_limit=(0.0, 65504.0),
-             z=None, return_chunk_states=False, check_status=False):
+             z=None, return_chunk_states=False, check_status=False, debug_reserved=0):
     """Mamba-2 chunked SSD forward.  x [b,s,h,p], dt [b,s,h] f32, a [h] f32, b/c [b,s,g,r], d [h] f32,
-    h0 [b,h,p,r] f32 -> (y [b,s,h,p], h_final [b,h,p,r] f32[, chunk_states [b,n,h,p,r]])."""
+    h0 [b,h,p,r] f32 -> (y [b,s,h,p], h_final [b,h,p,r] f32[, chunk_states [b,n,h,p,r]]).
+    `debug_reserved` goes into the args struct's `reserved` field (0 in production)."""
     bsz, s, h, p = x.shape
     g, r = b.shape[2], b.shape[3]
     act = x.dtype
@@ -78,8 +79,8 @@ def ssd2_fwd(x, dt, a, b, c, d=None, h0=None, chunk_len=256, path="auto", dt_bia
     nchunks = -(-s // max(chunk_len, 1))
     states = torch.empty((bsz, nchunks, h, p, r), dtype=torch.float32, device=x.device) if return_chunk_states else None
     args = _ffi.Ssd2FwdArgs(batch=bsz, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, chunk_len=chunk_len,
-                            dtype=_DT[act], path=PATHS[path], reserved=0, x=_ptr(x), dt=_ptr(dt), a=_ptr(a),
-                            b=_ptr(b), c=_ptr(c), d=_ptr(d), h0=_ptr(h0), dt_bias=_ptr(dt_bias),
+                            dtype=_DT[act], path=PATHS[path], reserved=debug_reserved, x=_ptr(x), dt=_ptr(dt),
+                            a=_ptr(a), b=_ptr(b), c=_ptr(c), d=_ptr(d), h0=_ptr(h0), dt_bias=_ptr(dt_bias),
                             dt_min=dt_limit[0], dt_max=dt_limit[1], z=_ptr(z), y=_ptr(y), h_final=_ptr(h_final),
                             chunk_states=_ptr(states))
     nbytes = lib.bm_ssd2_fwd_workspace_bytes(C.byref(args))

@@ -6,7 +6,8 @@
  *   - is asynchronous on the CUDA stream passed as `stream` (a cudaStream_t cast to void*; NULL =
  *     the legacy default stream) and runs on the caller's current device,
  *   - allocates nothing: scratch memory is a caller-provided workspace whose size the matching
- *     *_workspace_bytes() function reports (a pure host function),
+ *     *_workspace_bytes() function reports (a pure host function); the one exception is
+ *     bm_ssd2_fwd_noalloc, which takes no workspace and uses a scratch array built into the library,
  *   - returns a bm_status (0 = OK, negative = error) and never aborts or throws; the message of the
  *     last error on the calling thread is available from bm_last_error_string().
  *
@@ -16,6 +17,15 @@
  * "act dtype" tensors are float32 or bfloat16 as selected by the `dtype` field; decay inputs
  * (dt, da, A, D, gamma, scale, angles) and every recurrent state are always float32.
  * Pointers must be 16-byte aligned.  Head h reads B/C group h / (nheads / ngroups).
+ *
+ * Tensors are dense: there are no stride arguments.  The reference's slot receives two kinds of views,
+ * and a binding re-bases both without copying:
+ *   - dt arrives as [b, h, n, l], a permute(0, 3, 1, 2) of memory laid out [b, n, l, h]
+ *     (src/mamba2/ssd/serial_recalculated/serial_recalculated.rs:48).  That memory *is* the dense
+ *     [b, s, h] tensor this ABI takes (s = n * l): pass the view's base pointer.
+ *   - B / C arrive group->head expanded (src/modules/misc/gqa.rs:53-55).  Pass the un-expanded
+ *     [b, s, g, r] tensor with `ngroups` = g (head h reads group h / (nheads / ngroups)), or, if only the
+ *     materialised per-head copy exists, pass it with `ngroups` = nheads.
  *
  * Citations are file:line inside swfsql/burn-mamba.
  */
@@ -69,7 +79,7 @@ typedef struct {
     int32_t batch, seqlen, nheads, headdim, state_rank, ngroups, chunk_len;
     int32_t dtype;            /* bm_dtype of x, b, c, y, z */
     int32_t path;             /* bm_path */
-    int32_t reserved;
+    int32_t reserved;         /* 0, or BM_DEBUG_STALL_LOADS (tests only, see below) */
     const void* x;            /* [b, s, h, p] act dtype */
     const float* dt;          /* [b, s, h]   discretised step (post softplus/clamp), or raw when dt_bias set */
     const float* a;           /* [h]         A_h = -exp(a_log_h) */
@@ -91,6 +101,12 @@ typedef struct {
 size_t bm_ssd2_fwd_workspace_bytes(const bm_ssd2_fwd_args* args);
 int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Test-only value of bm_ssd2_fwd_args.reserved (no counterpart in the reference): the tensor-core kernel's
+ * loader issues no loads and the wait budget is shortened to a few milliseconds, so the first bounded wait
+ * runs out, every role leaves its loop and the launch ends with BM_ERR_TIMEOUT in the workspace status
+ * word and unspecified outputs.  Nothing faults or hangs; the next call on the same context runs normally. */
+#define BM_DEBUG_STALL_LOADS 0x57A11
+
 /* Device-side status of the last SSD call that used `workspace` (no counterpart in the reference, whose
  * ops cannot time out).  The tensor-core kernels bound every wait on a barrier; a wait that gives up
  * records BM_ERR_TIMEOUT in the first word of the workspace and the kernel returns early with
@@ -109,7 +125,9 @@ int32_t bm_workspace_status(const void* workspace, void* stream);
  *   - Problems whose scratch need (what bm_ssd2_fwd_workspace_bytes reports for BM_PATH_EXACT) exceeds the
  *     array are refused with BM_ERR_WORKSPACE_TOO_SMALL; nothing is launched.
  *   - The first call on each device looks the array's device address up (with that device current);
- *     make that first call outside any stream capture.
+ *     make that first call outside any stream capture.  The address is cached for the life of the
+ *     device's primary context: after cudaDeviceReset(), or any other teardown of that context, the
+ *     library must be reloaded before this entry point is used again on that device.
  *   - All calls on a device share the one array and it keeps the previous call's contents; nothing in
  *     it needs clearing between calls, but two calls that overlap on the GPU (different streams) race
  *     on it: serialise them. */

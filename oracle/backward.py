@@ -115,3 +115,36 @@ def finite_difference(fn, arrays, name, index, eps=1e-6):
     hi[name][index] += eps
     lo[name][index] -= eps
     return (fn(**hi) - fn(**lo)) / (2 * eps)
+
+
+def rope_halves_torch(x, angles):
+    """Half-and-half rotation (pairs (j, j + r/2)) of the last axis of x by `angles` (last axis r/2), as the
+    reference applies it when the MIMO rank is above one (src/mamba3/rotation/mod.rs:665,
+    src/modules/misc/rope.rs:112-170 with the full width rotated)."""
+    half = x.shape[-1] // 2
+    cos, sin = torch.cos(angles), torch.sin(angles)
+    x0, x1 = x[..., :half], x[..., half:]
+    return torch.cat([cos * x0 - sin * x1, sin * x0 + cos * x1], dim=-1)
+
+
+def ssd3_single_chain_grads(x, b_raw, c_raw, dt, a, lam, theta, h0, dy, dhf, chunk_len, mimo_rank):
+    """The Mamba-3 forward + backward configuration as one differentiable chain (float64 autodiff):
+    v_m = x / m;  da = dt A_h;  gamma = lambda dt;  scale_t = gamma_t + (1 - lambda_{t+1}) dt_{t+1} (last: gamma)
+    (src/mamba3/single_ssd/single_ssd/mod.rs:111-149, src/mamba3/helpers.rs:42-73); B, C rotated by the given
+    angles theta [b,s,h,r/2]; then the single-SSD core.  lambda and theta are inputs, not differentiated.
+    Returns y, h_final and dx, dB, dC (w.r.t. the un-rotated tensors), ddt, dA."""
+    f64 = lambda v, g=True: torch.tensor(np.asarray(v, np.float64), requires_grad=g)
+    t = dict(x=f64(x), b=f64(b_raw), c=f64(c_raw), dt=f64(dt), a=f64(a))
+    lam_t, th = f64(lam, False), f64(theta, False)
+    v = (t["x"] / mimo_rank)[:, :, None].expand(-1, -1, mimo_rank, -1, -1)
+    da = t["dt"] * t["a"][None, None]
+    gamma = lam_t * t["dt"]
+    nxt = torch.cat([((1.0 - lam_t) * t["dt"])[:, 1:], torch.zeros_like(gamma[:, :1])], dim=1)
+    scale = gamma + nxt
+    b_rot = rope_halves_torch(t["b"], th[:, :, None])
+    c_rot = rope_halves_torch(t["c"], th[:, :, None])
+    y, hf = mimo_ssd_forward_torch(v, da, b_rot, c_rot, scale, gamma, f64(h0, False), chunk_len, True)
+    loss = (y * f64(dy, False)).sum() + (hf * f64(dhf, False)).sum()
+    loss.backward()
+    return dict(y=y.detach().numpy(), h_final=hf.detach().numpy(), dx=t["x"].grad.numpy(), dB=t["b"].grad.numpy(),
+                dC=t["c"].grad.numpy(), ddt=t["dt"].grad.numpy(), dA=t["a"].grad.numpy())

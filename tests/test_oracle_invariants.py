@@ -244,3 +244,48 @@ def test_backward_oracle_m3_single_equals_double_gradients():
     for k in ("dda", "db", "dc", "dh0"):
         assert np.max(np.abs(g1[k] - g2[k])) < 1e-9, k
     assert np.max(np.abs(g1["dv"] - g2["dv"] * gamma[:, :, None, :, None])) < 1e-9
+
+
+def test_backward_oracle_m3_chain_agrees_with_finite_differences_and_the_closed_form_chain():
+    """The forward + backward configuration's chain (dt, A, lambda, theta -> da, gamma, scale, rotated B / C):
+    autodiff of the whole chain == central differences, and == the closed form that the GPU test harness
+    applies to the slot's gradients (ddt_t = A d_da_t + lambda_t (d_gamma_t + d_scale_t) + (1 - lambda_t) d_scale_{t-1})."""
+    from oracle import backward, mamba3
+    rng = np.random.default_rng(8)
+    b, s, m, h, p, r, Q = 1, 7, 2, 2, 3, 4, 4
+    arr = dict(x=rng.standard_normal((b, s, h, p)), b=rng.standard_normal((b, s, m, h, r)),
+               c=rng.standard_normal((b, s, m, h, r)), dt=rng.uniform(0.05, 0.3, (b, s, h)), a=-rng.uniform(1, 4, h))
+    lam = rng.uniform(0.2, 0.8, (b, s, h))
+    theta = rng.standard_normal((b, s, h, r // 2))
+    h0 = 0.1 * rng.standard_normal((b, h, p, r))
+    dy = rng.standard_normal((b, s, m, h, p))
+    dhf = rng.standard_normal(h0.shape)
+    g = backward.ssd3_single_chain_grads(arr["x"], arr["b"], arr["c"], arr["dt"], arr["a"], lam, theta, h0, dy, dhf, Q, m)
+
+    def slot_inputs(a):
+        v = np.repeat(a["x"][:, :, None] / m, m, axis=2)
+        da = a["dt"] * a["a"][None, None]
+        gamma = lam * a["dt"]
+        scale = gamma.copy()
+        scale[:, :-1] += ((1 - lam) * a["dt"])[:, 1:]
+        ang = theta[:, :, None]
+        return (v, da, mamba3.apply_rope_partial(a["b"], ang, r, False), mamba3.apply_rope_partial(a["c"], ang, r, False),
+                gamma, scale)
+
+    def loss(**a):
+        y, hf = mamba3.single_ssd_serial(*slot_inputs(a), h0, Q)
+        return float((y * dy).sum() + (hf * dhf).sum())
+
+    for name, key, idx in (("x", "dx", (0, 3, 1, 2)), ("dt", "ddt", (0, 2, 1)), ("dt", "ddt", (0, 6, 0)), ("a", "dA", (1,)),
+                           ("b", "dB", (0, 2, 1, 0, 3)), ("c", "dC", (0, 5, 0, 1, 1))):
+        fd = backward.finite_difference(loss, arr, name, idx)
+        assert abs(fd - g[key][idx]) < 1e-6 * max(1.0, abs(fd)), (name, fd, g[key][idx])
+    # closed-form chain on the slot's own gradients
+    sg = backward.ssd3_grads(*slot_inputs(arr), h0, dy, dhf, Q, single=True)
+    prev = np.concatenate([np.zeros_like(sg["dscale"][:, :1]), sg["dscale"][:, :-1]], axis=1)
+    ddt = arr["a"][None, None] * sg["dda"] + lam * (sg["dgamma"] + sg["dscale"]) + (1 - lam) * prev
+    assert np.max(np.abs(ddt - g["ddt"])) < 1e-6
+    assert np.max(np.abs((sg["dda"] * arr["dt"]).sum((0, 1)) - g["dA"])) < 1e-6
+    ang = theta[:, :, None]
+    assert np.max(np.abs(mamba3.apply_rope_partial(sg["db"], -ang, r, False) - g["dB"])) < 1e-6
+    assert np.max(np.abs(sg["dv"].sum(2) / m - g["dx"])) < 1e-6

@@ -13,10 +13,11 @@ import pytest
 import torch
 
 
-def _inputs(seed, b, s, h, p, r, g):
+def _inputs(seed, b, s, h, p, r, g, with_host=False):
     from oracle import inputs
     cfg = inputs.ssd2_prefill(seed=seed, batch=b, seqlen=s, nheads=h, headdim=p, state_rank=r, ngroups=g, h0_std=0.1)
-    return {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in cfg.items()}
+    t = {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in cfg.items()}
+    return (t, cfg) if with_host else t
 
 
 @pytest.mark.gpu
@@ -25,7 +26,7 @@ def test_noalloc_matches_workspace_entry_point_on_two_calls_in_a_row(bm):
     # two different problems back to back: the second must not see anything of the first in the scratch
     cases = [(3, 2, 200, 4, 32, 64, 2, 64), (4, 1, 130, 8, 64, 64, 1, 32)]
     for seed, b, s, h, p, r, g, q in cases:
-        t = _inputs(seed, b, s, h, p, r, g)
+        t, cfg = _inputs(seed, b, s, h, p, r, g, with_host=True)
         want_y, want_h = bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=q,
                                          path="exact")
         before = torch.cuda.memory_allocated()
@@ -35,6 +36,10 @@ def test_noalloc_matches_workspace_entry_point_on_two_calls_in_a_row(bm):
         assert torch.cuda.memory_allocated() - before <= y.numel() * y.element_size() + hf.numel() * 4 + 1024
         assert rel_l2(y.cpu().numpy(), want_y.cpu().numpy()) <= 1e-4
         assert rel_l2(hf.cpu().numpy(), want_h.cpu().numpy()) <= 1e-4
+        # and to the CPU oracle directly, so that this test stands without the other entry point
+        from oracle import mamba2
+        ref_y, ref_h = mamba2.ssd_serial(cfg["x"], cfg["dt"], cfg["a"], cfg["b"], cfg["c"], cfg["d"], cfg["h0"], q)
+        assert rel_l2(y.cpu().numpy(), ref_y) <= 1e-4 and rel_l2(hf.cpu().numpy(), ref_h) <= 1e-4
     # and the same problem twice in a row gives the same answer both times
     t = _inputs(5, 2, 96, 4, 16, 16, 1)
     y1, h1 = bm.ops.ssd2_fwd_noalloc(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], chunk_len=32)
