@@ -18,9 +18,9 @@
 // allocation + MMA issue for the state chain, warp 3 decay scan of dt, warps 4-7 mask pass (CB -> P),
 // warps 8-11 X scaling and state update, warps 12-15 epilogue.
 // Every wait is bounded; a wait that gives up stores BM_ERR_TIMEOUT in the status word of the
-// workspace and raises the CTA's abort flag, which every other wait loop polls, so all roles leave
-// their loops within a few thousand polls; the MMA issuers and the TMA producer then wait (bounded
-// again) for what they still have in flight before TMEM is released.
+// workspace and raises the CTA's abort flag; the other roles leave as their own budgets run out.  Once
+// all have left, the MMA issuers and the TMA producer wait (bounded again) for what they still have in
+// flight before TMEM is released.
 #include "ssd2_tc.cuh"
 #include "tc_common.cuh"
 
@@ -39,7 +39,9 @@ constexpr int kCumStages = 4;
 constexpr float kFactoredMaxLog2Decay = 100.f;
 // ... and whose per-row weight dt_t * 2^(cend - cum_t) of every live row stays above this floor: the
 // factored form recovers the skip term D x by dividing the scaled tile by that weight.
-constexpr float kFactoredMinRowWeight = 8.6736174e-19f;   // 2^-60
+// Together with |cend| <= 100 this only excludes rows whose step dt is itself below ~2^-12 of a tile's
+// weakest weight: D / w stays below 2^112 (inside bf16) and x * w stays a normal number.
+constexpr float kFactoredMinRowWeight = 1.9259299e-34f;   // 2^-112
 
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kPanel = 16384;               // [128 rows x 128 B]
@@ -76,6 +78,7 @@ struct Barriers {
     uint64_t drain[3];                      // timeout path only: one per MMA-issuing thread
     uint32_t tmem_base;
     uint32_t abort_flag;
+    int x_issued, cb_issued;                // TMA producer: tiles whose X / C+B loads have been issued
 };
 
 struct alignas(64) Params {
@@ -91,7 +94,6 @@ struct alignas(64) Params {
     int* status;
     long long* trace;
     int B, S, H, G, Q, NC, tiles_per_unit, num_units;
-    uint32_t wait_budget;   // polls per bounded wait
     int stall_loads;        // test hook: the TMA producer issues nothing, so the first wait runs out
 };
 
@@ -166,17 +168,18 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
 #define BM_TRACE(role, it, ev) do { } while (0)
 #endif
 
-// Bounded waits, inline: a short try_wait loop with an iteration budget.  A wait that runs out of budget
-// leaves through the `timed_out` label at the end of the kernel, which records BM_ERR_TIMEOUT and raises
-// the CTA's abort flag; the budget and the flag are looked at once every 1024 polls.  (Calls into an out-of-line wait cost the single-thread roles more than the wait
-// itself: their code is executed once per tile and every jump is a fresh instruction fetch.)
-#define BM_GIVE_UP(n) ((((n) & 1023u) == 0u) && ((n) >= prm.wait_budget || *abort_flag != 0u))
+// Bounded waits, inline: a short try_wait loop with an iteration budget (each try_wait itself blocks for a
+// short hardware-defined time).  A wait that runs out of budget leaves through the `timed_out` label at the
+// end of the kernel, which records BM_ERR_TIMEOUT and raises the CTA's abort flag.  The loops are kept to
+// the bare minimum of instructions (there are dozens of them and the roles' hot code has to fit the
+// instruction cache): they do not look at the abort flag, so after one role has given up the others leave
+// when their own budgets run out, all of which count down concurrently.
 #define BM_WAIT(bar, par)                                          \
     do {                                                           \
         uint32_t n_ = 0;                                           \
         _Pragma("unroll 1")                                        \
         while (!mbar_try_wait((bar), (par)))                       \
-            if (++n_, BM_GIVE_UP(n_)) goto timed_out;              \
+            if (++n_ >= kWaitBudget) goto timed_out;               \
     } while (0)
 // The same for a whole warp; the leave/stay decision is made warp-uniform so that no lane is left behind
 // at a later __syncwarp or .aligned tcgen05 instruction.
@@ -186,7 +189,7 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
         bool ok_ = true;                                           \
         _Pragma("unroll 1")                                        \
         while (!mbar_try_wait((bar), (par)))                       \
-            if (++n_, BM_GIVE_UP(n_)) {                            \
+            if (++n_ >= kWaitBudget) {                             \
                 ok_ = false;                                       \
                 break;                                             \
             }                                                      \
@@ -282,6 +285,25 @@ struct TileWalk {
     }
 };
 
+// Timeout path only (kept out of line, away from the hot code).  A wait gave up somewhere in this CTA and
+// every role has left its loop.  Before TMEM goes back, each thread that issued asynchronous work waits --
+// bounded again -- for what it may still have in flight: the MMA issuers through a commit onto a barrier of
+// their own, the producer through the full barriers of the (at most two) stages it loaded last.
+__device__ __noinline__ void drain_after_timeout(Barriers* bars, int warp, int lane, uint32_t budget) {
+    const int x_issued = bars->x_issued, cb_issued = bars->cb_issued;
+    if (lane == 0 && (warp == 1 || warp == 2 || warp == 4)) {
+        uint64_t* db = &bars->drain[warp == 4 ? 2 : warp - 1];
+        umma_commit(db);
+        for (uint32_t n = 0; n < budget && !mbar_try_wait(db, 0); ++n) {}
+    }
+    if (warp == 0 && lane == 0) {
+        for (int k = x_issued - 1; k >= 0 && k >= x_issued - 2; --k)
+            for (uint32_t n = 0; n < budget && !mbar_try_wait(&bars->xld_full[k & 1], (k >> 1) & 1); ++n) {}
+        for (int k = cb_issued - 1; k >= 0 && k >= cb_issued - 2; --k)
+            for (uint32_t n = 0; n < budget && !mbar_try_wait(&bars->cbld_full[k & 1], (k >> 1) & 1); ++n) {}
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_constant__ Params prm) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte aligned base, formed as an offset on the __shared__ array so that the compiler keeps the
@@ -318,6 +340,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         mbar_init(&bars->y2_empty, 4);
         for (int i = 0; i < 3; ++i) mbar_init(&bars->drain[i], 1);
         bars->abort_flag = 0;
+        bars->x_issued = bars->cb_issued = 0;
         fence_mbar_init();
     }
     if (warp == 2) {
@@ -337,7 +360,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
     const uint32_t c_base = smem_u32(smem + kOffC), b_base = smem_u32(smem + kOffB);
     const uint32_t x_base = smem_u32(smem + kOffX), xw_base = smem_u32(smem + kOffXw), h_base = smem_u32(smem + kOffH);
 
-    int x_issued = 0, cb_issued = 0;   // TMA producer: tiles whose X / C+B loads have been issued
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -355,7 +377,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 BM_TRACE(0, it, 1);
                 mbar_expect_tx(&bars->xld_full[st], kLoadBytesX);
                 tma_load_4d(smem + kOffX + st * kPanel, &prm.tm_x, &bars->xld_full[st], 0, h, s0, b);
-                x_issued = it + 1;
+                bars->x_issued = it + 1;
                 // C + B stage: released once CB, Y2 and S of the tile two back have completed
                 BM_WAIT(&bars->cbld_empty[st], ((it >> 1) & 1) ^ 1);
                 BM_TRACE(0, it, 0);
@@ -366,7 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 tma_load_4d(cs + kPanel, &prm.tm_c, &bars->cbld_full[st], 64, g, s0, b);
                 tma_load_4d(bs, &prm.tm_b, &bars->cbld_full[st], 0, g, s0, b);
                 tma_load_4d(bs + kPanel, &prm.tm_b, &bars->cbld_full[st], 64, g, s0, b);
-                cb_issued = it + 1;
+                bars->cb_issued = it + 1;
             }
         }
     } else if (warp == 1) {
@@ -816,21 +838,7 @@ done:
     tc_fence_before();
     __syncthreads();
     if (*abort_flag != 0u) {
-        // A wait gave up somewhere in this CTA and every role has left its loop.  Before TMEM goes back,
-        // each thread that issued asynchronous work waits -- bounded again -- for what it may still have in
-        // flight: the MMA issuers through a commit onto a barrier of their own, the producer through the
-        // full barriers of the (at most two) stages it loaded last.
-        if (lane == 0 && (warp == 1 || warp == 2 || warp == 4)) {
-            uint64_t* db = &bars->drain[warp == 4 ? 2 : warp - 1];
-            umma_commit(db);
-            for (uint32_t n = 0; n < prm.wait_budget && !mbar_try_wait(db, 0); ++n) {}
-        }
-        if (warp == 0 && lane == 0) {
-            for (int k = x_issued - 1; k >= 0 && k >= x_issued - 2; --k)
-                for (uint32_t n = 0; n < prm.wait_budget && !mbar_try_wait(&bars->xld_full[k & 1], (k >> 1) & 1); ++n) {}
-            for (int k = cb_issued - 1; k >= 0 && k >= cb_issued - 2; --k)
-                for (uint32_t n = 0; n < prm.wait_budget && !mbar_try_wait(&bars->cbld_full[k & 1], (k >> 1) & 1); ++n) {}
-        }
+        drain_after_timeout(bars, warp, lane, kWaitBudget);
         tc_fence_before();
         __syncthreads();
     }
@@ -895,10 +903,9 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     prm.NC = (int)cdiv(a->seqlen, a->chunk_len);
     prm.tiles_per_unit = (int)cdiv(a->seqlen, T);
     prm.num_units = a->batch * a->nheads;
-    // `reserved` carries one test-only request: BM_DEBUG_STALL_LOADS makes the producer issue nothing and
-    // shortens the wait budget, so that a bounded wait runs out and the error path can be exercised
+    // `reserved` carries one test-only request: BM_DEBUG_STALL_LOADS makes the producer issue nothing, so
+    // that a bounded wait runs out and the error path can be exercised
     prm.stall_loads = (a->reserved == BM_DEBUG_STALL_LOADS) ? 1 : 0;
-    prm.wait_budget = prm.stall_loads ? (1u << 12) : kWaitBudget;
     {
         cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd2_tc_kernel)");

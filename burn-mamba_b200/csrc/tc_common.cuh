@@ -62,7 +62,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 }
 // Budget of a bounded wait in polls (each try_wait itself blocks for a short hardware-defined time).  A
 // wait that runs out of it makes the kernel record a timeout status and return instead of spinning on.
-constexpr uint32_t kWaitBudget = 1u << 22;
+constexpr uint32_t kWaitBudget = 1u << 20;
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA, tcgen05.mma operands)
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -167,3 +167,20 @@ class Mamba2:
                       dt_bias=self.dt_bias, dt_limit=self.dt_limit)
         out = self._gated_norm(y.reshape(bsz, self.d_inner), z) @ self.w_out
         return out, cache
+
+
+def rms_norm(x, gamma):
+    """RmsNorm (src/modules/norm/rms_norm.rs:53-98): x / sqrt(mean(x^2) + eps) * gamma."""
+    eps = DIV_EPS.get(x.dtype, DIV_EPS[torch.float32])
+    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * gamma
+
+
+def stack_step(blocks, norm_gammas, caches, x_bm):
+    """One decode step through a stack of pre-norm residual layers, the default (no class latents, plain
+    residual) path of Layers::step / Layer::step_one (src/modules/layers.rs:427-497,
+    src/modules/layer.rs:224-229): x <- x + block.step(norm(x)).  `caches` is one Mamba2Cache per layer,
+    updated in place.  Returns the output of the last layer [b, d_model]."""
+    for blk, gamma, cache in zip(blocks, norm_gammas, caches):
+        h1, _ = blk.step(rms_norm(x_bm, gamma), cache)
+        x_bm = x_bm + h1
+    return x_bm

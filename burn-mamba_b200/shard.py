@@ -5,8 +5,8 @@ B/C shared inside a group), so the path shards with no exchange inside the scan.
 each rank a contiguous range of flattened (b, h) units, whole batch rows first; heads of one row are
 split only when there are more ranks than rows.  The one collective this path can need is the
 all-gather of y along the head axis when a row's heads live on several ranks (the gated norm that
-follows the SSD in the block reduces over all of d_inner, src/mamba2/mamba2.rs:776).  Decode steps are
-never sharded.
+follows the SSD in the block reduces over all of d_inner, src/mamba2/mamba2.rs:776).  Ranks that own
+whole rows exchange nothing.  Decode steps are never sharded.
 """
 from dataclasses import dataclass
 
@@ -33,6 +33,18 @@ class UnitRange:
             u += h_hi - h
         return out
 
+    def calls(self):
+        """[(b_lo, b_hi, h_lo, h_hi)]: the rank's units as the fewest rectangular library calls -- runs of
+        whole rows become one call of batch b_hi - b_lo, partial rows one call each."""
+        out = []
+        for b, h_lo, h_hi in self.slices():
+            whole = h_lo == 0 and h_hi == self.nheads
+            if whole and out and out[-1][2] == 0 and out[-1][3] == self.nheads and out[-1][1] == b:
+                out[-1] = (out[-1][0], b + 1, 0, self.nheads)
+            else:
+                out.append((b, b + 1, h_lo, h_hi))
+        return out
+
     @property
     def splits_heads(self):
         return any(h_lo != 0 or h_hi != self.nheads for _, h_lo, h_hi in self.slices())
@@ -50,36 +62,123 @@ def partition_units(batch, nheads, ngroups, world):
     return [UnitRange(cuts[i] * hpg, cuts[i + 1] * hpg, nheads) for i in range(world)]
 
 
-def ssd2_fwd_sharded(fwd, x, dt, a, b, c, d, h0, chunk_len, rank, world, group=None, gather=True):
-    """Runs `fwd` (an ssd2_fwd-compatible callable) on this rank's units and, when `gather`, all-gathers
-    y and the final state so that every rank holds the full result (what the block's gated norm needs).
-    Inputs are the full tensors (each rank slices its own part; B/C are sliced by group).
-    Returns (y, h_final) full-size, or this rank's [(b, h_lo, h_hi, y_part, h_part)] list when not gathering."""
+def partition_heads(batch, nheads, world):
+    """Unit ranges that may cut inside a B/C group (every head of a group reads the same B/C, so a rank that
+    owns part of a group simply reads that group too).  Used when there are more ranks than
+    batch x groups blocks, e.g. one group per row and more GPUs than rows."""
+    if batch <= 0 or nheads <= 0 or world <= 0:
+        raise ValueError("batch, nheads, world must be positive")
+    units = batch * nheads
+    cuts = [round(i * units / world) for i in range(world + 1)]
+    return [UnitRange(cuts[i], cuts[i + 1], nheads) for i in range(world)]
+
+
+def row_owners(parts):
+    """{row: [(rank, h_lo, h_hi), ...]} for the rows whose heads are spread over more than one rank."""
+    owners = {}
+    for rank, pr in enumerate(parts):
+        for b, h_lo, h_hi in pr.slices():
+            owners.setdefault(b, []).append((rank, h_lo, h_hi))
+    return {b: v for b, v in owners.items() if len(v) > 1}
+
+
+def ssd2_fwd_local(fwd, x, dt, a, b, c, d, h0, chunk_len, mine):
+    """Runs `fwd` (an ssd2_fwd-compatible callable) on one rank's units: one call per rectangle of
+    UnitRange.calls().  Inputs are full tensors or any tensors indexable the same way; B/C are sliced by group.
+    Returns [(b_lo, b_hi, h_lo, h_hi, y_part, h_part)]."""
+    h = x.shape[2]
+    g = b.shape[2]
+    hpg = h // g
+    parts = []
+    for b_lo, b_hi, h_lo, h_hi in mine.calls():
+        # a head range that starts or ends inside a B/C group is cut at the group boundaries: every piece then
+        # lies inside one group (the call sees that group as its only one) or covers whole groups
+        cuts = sorted({h_lo, h_hi, min(h_hi, -(-h_lo // hpg) * hpg), max(h_lo, (h_hi // hpg) * hpg)})
+        ys, hs = [], []
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            g_lo, g_hi = lo // hpg, -(-hi // hpg)
+            heads = slice(lo, hi)
+            y_p, hf_p = fwd(x[b_lo:b_hi, :, heads].contiguous(), dt[b_lo:b_hi, :, heads].contiguous(),
+                            a[heads].clone(), b[b_lo:b_hi, :, g_lo:g_hi].contiguous(),
+                            c[b_lo:b_hi, :, g_lo:g_hi].contiguous(), None if d is None else d[heads].clone(),
+                            None if h0 is None else h0[b_lo:b_hi, heads].contiguous(), chunk_len)
+            ys.append(y_p)
+            hs.append(hf_p)
+        if len(ys) > 1:
+            import torch
+            ys, hs = [torch.cat(ys, dim=2)], [torch.cat(hs, dim=1)]
+        parts.append((b_lo, b_hi, h_lo, h_hi, ys[0], hs[0]))
+    return parts
+
+
+_group_cache = {}
+
+
+def _subgroup(ranks, world):
+    """Process group of `ranks` (every rank of the world must call this with the same sequence of rank sets)."""
+    import torch.distributed as dist
+    if len(ranks) == world:
+        return None
+    key = tuple(ranks)
+    if key not in _group_cache:
+        _group_cache[key] = dist.new_group(list(ranks))
+    return _group_cache[key]
+
+
+def gather_heads(parts, parts_of_all, rank, world, nheads):
+    """All-gather along the head axis for the rows whose heads are split: every rank that owns a piece of such
+    a row ends up with the row's full y [1, s, H, p] and final state [1, H, p, r].  One all_gather per tensor and
+    split row, inside the sub-group of the ranks that share the row; pieces of unequal width are padded to
+    the widest.  Rows owned whole by one rank are returned as they are.  -> {row: (y_full, h_full)}."""
     import torch
     import torch.distributed as dist
 
-    bsz, s, h, p = x.shape
-    g = b.shape[2]
-    hpg = h // g
-    mine = partition_units(bsz, h, g, world)[rank]
-    parts = []
-    for bi, h_lo, h_hi in mine.slices():
-        g_lo, g_hi = h_lo // hpg, -(-h_hi // hpg)
-        y_p, hf_p = fwd(x[bi:bi + 1, :, h_lo:h_hi].contiguous(), dt[bi:bi + 1, :, h_lo:h_hi].contiguous(),
-                        a[h_lo:h_hi].contiguous(), b[bi:bi + 1, :, g_lo:g_hi].contiguous(),
-                        c[bi:bi + 1, :, g_lo:g_hi].contiguous(), None if d is None else d[h_lo:h_hi].contiguous(),
-                        None if h0 is None else h0[bi:bi + 1, h_lo:h_hi].contiguous(), chunk_len)
-        parts.append((bi, h_lo, h_hi, y_p, hf_p))
+    split = row_owners(parts_of_all)
+    out = {}
+    for b_lo, b_hi, h_lo, h_hi, y_p, hf_p in parts:
+        if h_lo == 0 and h_hi == nheads:
+            for i, row in enumerate(range(b_lo, b_hi)):
+                out[row] = (y_p[i:i + 1], hf_p[i:i + 1])
+    # every rank walks the split rows in the same order so that group creation and collectives line up
+    for row in sorted(split):
+        owners = split[row]
+        ranks = [r for r, _, _ in owners]
+        group = _subgroup(ranks, world) if world > 1 else None
+        if rank not in ranks:
+            continue
+        mine = next(p for p in parts if p[0] == row and not (p[2] == 0 and p[3] == nheads))
+        _, _, h_lo, h_hi, y_p, hf_p = mine
+        width = max(hi - lo for _, lo, hi in owners)
+        pad = lambda t, dim: t if t.shape[dim] == width else torch.cat(
+            [t, t.new_zeros(t.shape[:dim] + (width - t.shape[dim],) + t.shape[dim + 1:])], dim=dim)
+        ys, hs = pad(y_p, 2).contiguous(), pad(hf_p, 1).contiguous()
+        y_all = ys.new_empty((len(ranks),) + tuple(ys.shape))
+        h_all = hs.new_empty((len(ranks),) + tuple(hs.shape))
+        if world > 1:
+            try:
+                dist.all_gather_into_tensor(y_all, ys, group=group)
+                dist.all_gather_into_tensor(h_all, hs, group=group)
+            except (RuntimeError, NotImplementedError):   # back ends without the flat form
+                yl, hl = list(y_all.unbind(0)), list(h_all.unbind(0))
+                dist.all_gather(yl, ys, group=group)
+                dist.all_gather(hl, hs, group=group)
+                y_all, h_all = torch.stack(yl), torch.stack(hl)
+        else:
+            y_all[0], h_all[0] = ys, hs
+        y_full = torch.cat([y_all[i][:, :, :hi - lo] for i, (_, lo, hi) in enumerate(owners)], dim=2)
+        h_full = torch.cat([h_all[i][:, :hi - lo] for i, (_, lo, hi) in enumerate(owners)], dim=1)
+        out[row] = (y_full, h_full)
+    return out
+
+
+def ssd2_fwd_sharded(fwd, x, dt, a, b, c, d, h0, chunk_len, rank, world, gather=True, by_heads=False):
+    """This rank's share of one SSD problem: runs `fwd` on the rank's units and, when `gather`, completes the
+    rows whose heads are split with an all-gather along heads.  Returns {row: (y [1,s,H,p], h_final [1,H,p,r])}
+    for the rows this rank holds in full afterwards (its own whole rows plus the split rows it shares), or the
+    raw parts list when not gathering."""
+    bsz, _, h, _ = x.shape
+    parts_of_all = partition_heads(bsz, h, world) if by_heads else partition_units(bsz, h, b.shape[2], world)
+    parts = ssd2_fwd_local(fwd, x, dt, a, b, c, d, h0, chunk_len, parts_of_all[rank])
     if not gather:
         return parts
-    r = b.shape[3]
-    y = torch.zeros_like(x)
-    hf = torch.zeros((bsz, h, p, r), dtype=torch.float32, device=x.device)
-    for bi, h_lo, h_hi, y_p, hf_p in parts:
-        y[bi:bi + 1, :, h_lo:h_hi] = y_p
-        hf[bi:bi + 1, h_lo:h_hi] = hf_p
-    if world > 1:
-        # units are disjoint across ranks, so a sum over ranks is the gather (one collective per tensor)
-        dist.all_reduce(y, group=group)
-        dist.all_reduce(hf, group=group)
-    return y, hf
+    return gather_heads(parts, parts_of_all, rank, world, h)

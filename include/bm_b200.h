@@ -102,9 +102,8 @@ size_t bm_ssd2_fwd_workspace_bytes(const bm_ssd2_fwd_args* args);
 int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Test-only value of bm_ssd2_fwd_args.reserved (no counterpart in the reference): the tensor-core kernel's
- * loader issues no loads and the wait budget is shortened to a few milliseconds, so the first bounded wait
- * runs out, every role leaves its loop and the launch ends with BM_ERR_TIMEOUT in the workspace status
- * word and unspecified outputs.  Nothing faults or hangs; the next call on the same context runs normally. */
+ * loader issues no loads, so the first bounded wait runs out (after about a second), every role leaves its
+ * loop and the launch ends with BM_ERR_TIMEOUT in the workspace status word and unspecified outputs.  Nothing faults or hangs; the next call on the same context runs normally. */
 #define BM_DEBUG_STALL_LOADS 0x57A11
 
 /* Device-side status of the last SSD call that used `workspace` (no counterpart in the reference, whose

@@ -42,22 +42,25 @@ def _oracle_fwd(x, dt, a, b, c, d, h0, chunk_len):
     return torch.from_numpy(y), torch.from_numpy(hf)
 
 
-def _worker(rank, world, port, cfg, q):
+def _worker(rank, world, port, cfg, by_heads, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         shard = _shard()
         t = {k: torch.from_numpy(v) for k, v in cfg.items()}
-        y, hf = shard.ssd2_fwd_sharded(_oracle_fwd, t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], 16,
-                                       rank, world)
-        q.put((rank, y.numpy(), hf.numpy()))
+        rows = shard.ssd2_fwd_sharded(_oracle_fwd, t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], t["h0"], 16,
+                                      rank, world, by_heads=by_heads)
+        q.put((rank, {r: (y.numpy(), hf.numpy()) for r, (y, hf) in rows.items()}))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("batch,nheads,ngroups", [(2, 4, 1), (1, 4, 2)])   # batch-sharded and head-sharded
-def test_two_rank_gather_equals_single_rank(batch, nheads, ngroups):
+# whole rows per rank (no collective) / heads split at a group boundary / heads split inside the only group
+@pytest.mark.parametrize("batch,nheads,ngroups,by_heads", [(2, 4, 1, False), (1, 4, 2, False), (1, 4, 1, True),
+                                                           (3, 4, 2, True)])
+def test_two_rank_shards_equal_the_single_rank_result(batch, nheads, ngroups, by_heads):
     from oracle import inputs, mamba2
+    shard = _shard()
     cfg = inputs.ssd2_prefill(seed=21, batch=batch, seqlen=40, nheads=nheads, headdim=8, state_rank=8, ngroups=ngroups,
                               h0_std=0.1)
     cfg = {k: cfg[k] for k in ("x", "dt", "a", "b", "c", "d", "h0")}
@@ -65,12 +68,33 @@ def test_two_rank_gather_equals_single_rank(batch, nheads, ngroups):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29500 + (os.getpid() % 2000)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, cfg, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, cfg, by_heads, q)) for r in range(2)]
     for p in procs:
         p.start()
-    results = [q.get(timeout=120) for _ in range(2)]
+    results = dict(q.get(timeout=120) for _ in range(2))
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
-    for _, y, hf in results:   # every rank holds the full result
-        assert np.max(np.abs(y - want_y)) < 1e-5 and np.max(np.abs(hf - want_h)) < 1e-5
+    parts = shard.partition_heads(batch, nheads, 2) if by_heads else shard.partition_units(batch, nheads, ngroups, 2)
+    split = shard.row_owners(parts)
+    held = {}
+    for rank, rows in results.items():
+        for row, (y, hf) in rows.items():   # whatever a rank holds is a full, correct row
+            assert y.shape[2] == nheads
+            assert np.max(np.abs(y[0] - want_y[row])) < 1e-5 and np.max(np.abs(hf[0] - want_h[row])) < 1e-5
+            held.setdefault(row, set()).add(rank)
+    assert set(held) == set(range(batch))          # every row is held by someone
+    for row, owners in split.items():              # split rows end up on every rank that owns a piece
+        assert held[row] == {r for r, _, _ in owners}
+    for row in set(range(batch)) - set(split):     # whole rows stay where they were computed: no exchange
+        assert len(held[row]) == 1
+
+
+def test_calls_merge_whole_rows_into_one_library_call():
+    shard = _shard()
+    parts = shard.partition_units(8, 80, 1, 2)
+    assert parts[0].calls() == [(0, 4, 0, 80)] and parts[1].calls() == [(4, 8, 0, 80)]
+    parts = shard.partition_heads(4, 80, 8)
+    assert parts[0].calls() == [(0, 1, 0, 40)] and parts[1].calls() == [(0, 1, 40, 80)]
+    ur = shard.UnitRange(40, 280, 80)   # half a row, two whole rows, half a row
+    assert ur.calls() == [(0, 1, 40, 80), (1, 3, 0, 80), (3, 4, 0, 40)]
