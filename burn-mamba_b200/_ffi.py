@@ -14,7 +14,7 @@ BM_OK = 0
 BM_ERR_NULL_POINTER, BM_ERR_BAD_SHAPE, BM_ERR_BAD_ALIGNMENT, BM_ERR_UNSUPPORTED = -1, -2, -3, -4
 BM_ERR_WORKSPACE_TOO_SMALL, BM_ERR_CUDA, BM_ERR_TIMEOUT = -5, -6, -7
 BM_DTYPE_F32, BM_DTYPE_BF16 = 0, 1
-BM_PATH_AUTO, BM_PATH_EXACT, BM_PATH_TENSOR = 0, 1, 2
+BM_PATH_AUTO, BM_PATH_EXACT, BM_PATH_TENSOR, BM_PATH_TENSOR_SINGLE, BM_PATH_TENSOR_PAIR = 0, 1, 2, 3, 4
 BM_SSD2_NOALLOC_SCRATCH_BYTES = 32 << 20
 BM_DEBUG_STALL_LOADS = 0x57A11   # bm_ssd2_fwd_args.reserved: test hook that makes a bounded wait run out
 
@@ -37,6 +37,17 @@ class Step2Args(C.Structure):
 class ConvStepArgs(C.Structure):
     _fields_ = [(n, _i32) for n in ("batch", "channels", "kernel", "dtype")] + [
         ("window", _vp), ("xin", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp)]
+
+
+class Conv1dSiluArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "channels", "kernel", "dtype", "xin_stride", "split_x", "split_bc")] + [
+        ("xin", _vp), ("weight", _vp), ("bias", _vp), ("window", _vp), ("new_window", _vp), ("out_x", _vp),
+        ("out_b", _vp), ("out_c", _vp)]
+
+
+class RmsnormGatedArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("rows", "width", "dtype", "norm_before_gate", "x_stride", "z_stride")] + [
+        ("eps", _f32), ("x", _vp), ("z", _vp), ("gamma", _vp), ("out", _vp)]
 
 
 class Selscan1Args(C.Structure):
@@ -100,7 +111,11 @@ SYMBOLS = {
     "bm_ssd3_double_bwd": (_i32, [C.POINTER(Ssd3BwdArgs), _vp, C.c_size_t, _vp]),
     "bm_step2": (_i32, [C.POINTER(Step2Args), _vp]),
     "bm_conv_step": (_i32, [C.POINTER(ConvStepArgs), _vp]),
+    "bm_conv1d_silu_fwd": (_i32, [C.POINTER(Conv1dSiluArgs), _vp]),
+    "bm_rmsnorm_gated": (_i32, [C.POINTER(RmsnormGatedArgs), _vp]),
     "bm_selscan1_fwd": (_i32, [C.POINTER(Selscan1Args), _vp]),
+    "bm_selscan1_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Selscan1Args)]),
+    "bm_selscan1_fwd_ws": (_i32, [C.POINTER(Selscan1Args), _vp, C.c_size_t, _vp]),
     "bm_step1": (_i32, [C.POINTER(Step1Args), _vp]),
     "bm_ssd3_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Ssd3FwdArgs)]),
     "bm_ssd3_single_fwd": (_i32, [C.POINTER(Ssd3FwdArgs), _vp, C.c_size_t, _vp]),

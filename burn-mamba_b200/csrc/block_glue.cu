@@ -1,0 +1,254 @@
+// Pre- and post-SSD kernels of the Mamba-2 block (HBM-bound elementwise passes):
+//   bm_conv1d_silu_fwd  causal depthwise conv (k taps) + bias + SiLU over the [b, s, v] projection columns,
+//                       left context from the cache window, outputs written as the three tensors the SSD reads
+//                       (src/mamba2/mamba2.rs:618-654: the window slide, Conv1d, SiLU and the x / B / C split);
+//   bm_rmsnorm_gated    RmsNormGated (src/modules/norm/rms_norm_gated.rs:70-135) and, with z = NULL, the plain
+//                       RmsNorm of the layer stack (src/modules/norm/rms_norm.rs:53-98).
+// Both take a row stride for the tensors that are column slices of the in-projection's output, so that no
+// slice is materialised.
+#include "common.cuh"
+
+using namespace bm;
+
+namespace {
+
+constexpr int TL = 32;        // tokens per thread in the conv kernel
+constexpr int VEC = 8;        // channels per thread (16 bytes of bf16, 32 of f32)
+
+template <typename T>
+struct Vec8 {
+    float v[VEC];
+    __device__ __forceinline__ void load(const T* p);
+    __device__ __forceinline__ void store(T* p) const;
+};
+template <>
+__device__ __forceinline__ void Vec8<float>::load(const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void Vec8<float>::store(float* p) const {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void Vec8<__nv_bfloat16>::load(const __nv_bfloat16* p) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+        v[2 * j] = f.x, v[2 * j + 1] = f.y;
+    }
+}
+template <>
+__device__ __forceinline__ void Vec8<__nv_bfloat16>::store(__nv_bfloat16* p) const {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One thread: 8 adjacent channels x TL consecutive tokens, a K-deep window of the inputs in registers.
+// Consecutive threads take consecutive channel vectors, so every row access of a warp is one contiguous run.
+template <typename T, int K>
+__global__ void __launch_bounds__(128) conv1d_silu_kernel(bm_conv1d_silu_args a) {
+    const int V = a.channels, S = a.seqlen;
+    const int nvec = V / VEC;
+    const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int vec = gid % nvec;
+    const int nchunk = (S + TL - 1) / TL;
+    const int chunk = (gid / nvec) % nchunk;
+    const int b = gid / ((int64_t)nvec * nchunk);
+    if (b >= a.batch) return;
+    const int c0 = vec * VEC, t0 = chunk * TL, t1 = min(S, t0 + TL);
+    float w[K][VEC], bias[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        bias[j] = a.bias ? a.bias[c0 + j] : 0.f;
+#pragma unroll
+        for (int k = 0; k < K; ++k) w[k][j] = a.weight[(int64_t)(c0 + j) * K + k];
+    }
+    const T* xin = static_cast<const T*>(a.xin) + (int64_t)b * S * a.xin_stride + c0;
+    // input at token t (t < 0: the cache window's column K + t, i.e. its last K - 1 columns are tokens -K+1 .. -1)
+    auto input = [&](int t, Vec8<T>& out) {
+        if (t >= 0) {
+            out.load(xin + (int64_t)t * a.xin_stride);
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                out.v[j] = a.window ? a.window[((int64_t)b * V + c0 + j) * K + (K + t)] : 0.f;
+        }
+    };
+    // which output tensor this channel vector belongs to
+    T* dst;
+    int64_t dstride;
+    if (a.out_b == nullptr) {
+        dst = static_cast<T*>(a.out_x) + (int64_t)b * S * V + c0, dstride = V;
+    } else if (c0 < a.split_x) {
+        dst = static_cast<T*>(a.out_x) + (int64_t)b * S * a.split_x + c0, dstride = a.split_x;
+    } else if (c0 < a.split_x + a.split_bc) {
+        dst = static_cast<T*>(a.out_b) + (int64_t)b * S * a.split_bc + (c0 - a.split_x), dstride = a.split_bc;
+    } else {
+        dst = static_cast<T*>(a.out_c) + (int64_t)b * S * a.split_bc + (c0 - a.split_x - a.split_bc), dstride = a.split_bc;
+    }
+    Vec8<T> win[K];
+#pragma unroll
+    for (int k = 0; k < K - 1; ++k) input(t0 - (K - 1) + k, win[k]);
+    for (int t = t0; t < t1; ++t) {
+        input(t, win[K - 1]);
+        Vec8<T> o;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            float acc = bias[j];
+#pragma unroll
+            for (int k = 0; k < K; ++k) acc = fmaf(win[k].v[j], w[k][j], acc);
+            o.v[j] = silu_f32(acc);
+        }
+        o.store(dst + (int64_t)t * dstride);
+#pragma unroll
+        for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
+    }
+}
+
+// New cache window: the last K columns of [old window columns 1.. | the sequence's raw inputs].
+template <typename T>
+__global__ void conv_window_kernel(bm_conv1d_silu_args a) {
+    const int V = a.channels, S = a.seqlen, K = a.kernel;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // (b, j, c): c fastest, so the reads run along channels
+    if (idx >= (int64_t)a.batch * K * V) return;
+    const int c = idx % V, j = (idx / V) % K, b = idx / ((int64_t)V * K);
+    const int t = S - K + j;   // token that lands in column j
+    float val;
+    if (t >= 0) val = to_f32(static_cast<const T*>(a.xin)[((int64_t)b * S + t) * a.xin_stride + c]);
+    else val = a.window ? a.window[((int64_t)b * V + c) * K + (K + t)] : 0.f;
+    a.new_window[((int64_t)b * V + c) * K + j] = val;
+}
+
+// ---------------------------------------------------------------------------------------------
+// gated RMS norm: one CTA per row, the row in registers, one pass.
+// ---------------------------------------------------------------------------------------------
+constexpr int NT = 128;            // threads per row
+constexpr int MAXV = 8;            // vectors of 8 per thread: rows up to 8192 wide
+
+template <typename T>
+__global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args a) {
+    __shared__ float red[NT / 32];
+    const int64_t row = blockIdx.x;
+    const int D = a.width;
+    const T* xr = static_cast<const T*>(a.x) + row * a.x_stride;
+    const T* zr = a.z ? static_cast<const T*>(a.z) + row * a.z_stride : nullptr;
+    const T* gr = static_cast<const T*>(a.gamma);
+    T* orow = static_cast<T*>(a.out) + row * (int64_t)D;
+    const bool gate_first = zr != nullptr && !a.norm_before_gate;
+    Vec8<T> xv[MAXV];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int c = (i * NT + threadIdx.x) * VEC;
+        if (c < D) {
+            xv[i].load(xr + c);
+            if (gate_first) {
+                Vec8<T> zv;
+                zv.load(zr + c);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) xv[i].v[j] *= silu_f32(zv.v[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) ss = fmaf(xv[i].v[j], xv[i].v[j], ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NT / 32; ++i) tot += red[i];
+    const float inv = rsqrtf(tot / (float)D + a.eps);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int c = (i * NT + threadIdx.x) * VEC;
+        if (c < D) {
+            Vec8<T> gv, ov;
+            gv.load(gr + c);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) ov.v[j] = xv[i].v[j] * inv * gv.v[j];
+            if (zr != nullptr && a.norm_before_gate) {
+                Vec8<T> zv;
+                zv.load(zr + c);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) ov.v[j] *= silu_f32(zv.v[j]);
+            }
+            ov.store(orow + c);
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int32_t bm_conv1d_silu_fwd(const bm_conv1d_silu_args* a, void* stream) {
+    clear_error();
+    if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
+    BM_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->channels > 0, BM_ERR_BAD_SHAPE, "batch, seqlen, channels must be positive");
+    BM_REQUIRE(a->kernel == 4 || a->kernel == 2 || a->kernel == 3, BM_ERR_UNSUPPORTED, "conv kernel must be 2, 3 or 4 taps");
+    BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
+    const int esz = a->dtype == BM_DTYPE_F32 ? 4 : 2;
+    BM_REQUIRE(a->channels % VEC == 0 && ((int64_t)a->xin_stride * esz) % 16 == 0 && a->xin_stride >= a->channels, BM_ERR_BAD_SHAPE,
+               "channels must be a multiple of 8 and input rows must start 16-byte aligned, stride >= channels");
+    BM_REQUIRE_PTR(a->xin);
+    BM_REQUIRE_PTR(a->weight);
+    BM_REQUIRE_PTR(a->out_x);
+    BM_OPTIONAL_PTR(a->bias);
+    BM_OPTIONAL_PTR(a->window);
+    BM_OPTIONAL_PTR(a->new_window);
+    if (a->out_b != nullptr || a->out_c != nullptr) {
+        BM_REQUIRE_PTR(a->out_b);
+        BM_REQUIRE_PTR(a->out_c);
+        BM_REQUIRE(a->split_x > 0 && a->split_bc > 0 && a->split_x + 2 * a->split_bc == a->channels &&
+                       a->split_x % VEC == 0 && a->split_bc % VEC == 0,
+                   BM_ERR_BAD_SHAPE, "split_x + 2 split_bc must equal channels, both multiples of 8");
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int64_t threads = (int64_t)a->batch * cdiv(a->seqlen, TL) * (a->channels / VEC);
+    const unsigned grid = (unsigned)cdiv(threads, 128);
+    const bool f32 = a->dtype == BM_DTYPE_F32;
+    switch (a->kernel) {
+        case 2: f32 ? conv1d_silu_kernel<float, 2><<<grid, 128, 0, st>>>(*a) : conv1d_silu_kernel<__nv_bfloat16, 2><<<grid, 128, 0, st>>>(*a); break;
+        case 3: f32 ? conv1d_silu_kernel<float, 3><<<grid, 128, 0, st>>>(*a) : conv1d_silu_kernel<__nv_bfloat16, 3><<<grid, 128, 0, st>>>(*a); break;
+        default: f32 ? conv1d_silu_kernel<float, 4><<<grid, 128, 0, st>>>(*a) : conv1d_silu_kernel<__nv_bfloat16, 4><<<grid, 128, 0, st>>>(*a); break;
+    }
+    if (int32_t e = check_launch("conv1d_silu")) return e;
+    if (a->new_window != nullptr) {
+        BM_REQUIRE(a->new_window != a->window, BM_ERR_UNSUPPORTED, "new_window must not alias window");
+        const int64_t total = (int64_t)a->batch * a->kernel * a->channels;
+        if (f32) conv_window_kernel<float><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(*a);
+        else conv_window_kernel<__nv_bfloat16><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(*a);
+        return check_launch("conv_window");
+    }
+    return BM_OK;
+}
+
+extern "C" int32_t bm_rmsnorm_gated(const bm_rmsnorm_gated_args* a, void* stream) {
+    clear_error();
+    if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
+    BM_REQUIRE(a->rows > 0 && a->width > 0, BM_ERR_BAD_SHAPE, "rows and width must be positive");
+    BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
+    BM_REQUIRE(a->width % VEC == 0 && a->width <= NT * MAXV * VEC, BM_ERR_UNSUPPORTED, "width must be a multiple of 8, at most %d",
+               NT * MAXV * VEC);
+    const int esz = a->dtype == BM_DTYPE_F32 ? 4 : 2;
+    BM_REQUIRE(((int64_t)a->x_stride * esz) % 16 == 0 && a->x_stride >= a->width &&
+                   (a->z == nullptr || (((int64_t)a->z_stride * esz) % 16 == 0 && a->z_stride >= a->width)),
+               BM_ERR_BAD_SHAPE, "rows must start 16-byte aligned and strides be at least the width");
+    BM_REQUIRE_PTR(a->x);
+    BM_REQUIRE_PTR(a->gamma);
+    BM_REQUIRE_PTR(a->out);
+    BM_OPTIONAL_PTR(a->z);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (a->dtype == BM_DTYPE_F32) rmsnorm_gated_kernel<float><<<(unsigned)a->rows, NT, 0, st>>>(*a);
+    else rmsnorm_gated_kernel<__nv_bfloat16><<<(unsigned)a->rows, NT, 0, st>>>(*a);
+    return check_launch("rmsnorm_gated");
+}

@@ -233,8 +233,8 @@ int32_t launch(const bm_selscan1_args& a, cudaStream_t st) {
 
 }  // namespace
 
-extern "C" int32_t bm_selscan1_fwd(const bm_selscan1_args* a, void* stream) {
-    clear_error();
+namespace bm {
+int32_t validate_selscan1(const bm_selscan1_args* a) {
     if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
     BM_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->d_inner > 0 && a->state_rank > 0, BM_ERR_BAD_SHAPE,
                "batch, seqlen, d_inner, state_rank must be positive");
@@ -250,6 +250,13 @@ extern "C" int32_t bm_selscan1_fwd(const bm_selscan1_args* a, void* stream) {
     BM_OPTIONAL_PTR(a->delta_bias);
     BM_OPTIONAL_PTR(a->z);
     BM_OPTIONAL_PTR(a->h0);
+    return BM_OK;
+}
+}  // namespace bm
+
+extern "C" int32_t bm_selscan1_fwd(const bm_selscan1_args* a, void* stream) {
+    clear_error();
+    if (int32_t e = validate_selscan1(a)) return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     return a->dtype == BM_DTYPE_F32 ? launch<float>(*a, st) : launch<__nv_bfloat16>(*a, st);
 }

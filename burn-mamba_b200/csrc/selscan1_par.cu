@@ -1,0 +1,269 @@
+// Mamba-1 selective scan, parallel over the sequence (replaces the per-token op loop of
+// src/mamba1/mamba1.rs:422-523: h = h exp(delta (x) A) + delta B u ; y = h . C + D u ; optional gate).
+//
+// The recurrence of one (batch row, channel, state) is a chain of affine maps h -> a_t h + b_t, and affine
+// maps compose associatively: (a, b) o (a', b') = (a a', a' b + b').  The sequence is cut into segments of
+// SEG tokens and scanned on two levels:
+//   1. summary  every (row, channel, segment) runs its segment from a zero state and keeps the segment's
+//               end state and its total step sum(delta)   (the composed map's b and, through A, its a);
+//   2. carry    per (row, channel, state) the segments' maps are applied in order, which gives the state
+//               entering every segment (a few dozen steps);
+//   3. output   every (row, channel, segment) runs its segment again from the right entering state and
+//               writes y (gate fused) and, for the last segment, the final state.
+// One thread owns one channel of one segment with all its states in registers (packed pairs: fma.rn.f32x2
+// does two states per instruction), consecutive threads own consecutive channels, so u / delta / z / y are
+// read and written in full sectors; the B and C rows of the segment are staged once per CTA in shared memory
+// as float32 and read as warp-wide broadcasts.  When a channel's decay row is the S4D-real ramp
+// A[n] = (n + 1) A[0] (the reference's initialisation, src/mamba1/mamba1.rs:184-194), exp(delta A[n]) is
+// formed as powers of one exponential instead of one exponential per state.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+using namespace bm;
+using bm::tc::fma2;
+using bm::tc::mul2;
+using bm::tc::pair_f32;
+
+namespace {
+
+constexpr int SEG = 128;      // tokens per segment
+constexpr int CPB = 128;      // channels (threads) per CTA
+constexpr int NS = 16;        // states handled by the fast kernels
+
+__device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+struct Scratch {
+    float* h_loc;   // [b, nseg, NS, i]  end state of every segment run from zero
+    float* dsum;    // [b, nseg, i]      sum of delta over the segment
+    float* h_in;    // [b, nseg, NS, i]  state entering every segment
+};
+
+// Stages the B (and C) rows of tokens [t0, t0 + nt) of batch row b as float32 [token][NS].
+template <typename T>
+__device__ __forceinline__ void stage_rows(float* dst, const void* src, int64_t row0, int nt) {
+    const T* s = static_cast<const T*>(src) + row0 * NS;
+    for (int e = threadIdx.x; e < nt * NS; e += blockDim.x) dst[e] = to_f32(s[e]);
+}
+
+// Per-token decay factors exp(delta A[n]) of one channel as 8 packed pairs.
+struct Decay {
+    float a[NS];
+    bool ramp;
+    __device__ __forceinline__ void init(const float* arow) {
+        bool r = true;
+#pragma unroll
+        for (int n = 0; n < NS; ++n) {
+            a[n] = arow[n];
+            r &= fabsf(a[n] - (float)(n + 1) * arow[0]) <= 1e-6f * fabsf(a[n]);
+        }
+        ramp = __all_sync(0xffffffffu, r);   // one code path per warp
+    }
+    __device__ __forceinline__ void factors(float delta, uint64_t (&p)[NS / 2]) const {
+        if (ramp) {
+            const float e1 = __expf(delta * a[0]), e2 = e1 * e1;
+            const uint64_t step = pair_f32(e2, e2);
+            p[0] = pair_f32(e1, e2);
+#pragma unroll
+            for (int k = 1; k < NS / 2; ++k) p[k] = mul2(p[k - 1], step);
+        } else {
+#pragma unroll
+            for (int k = 0; k < NS / 2; ++k) p[k] = pair_f32(__expf(delta * a[2 * k]), __expf(delta * a[2 * k + 1]));
+        }
+    }
+};
+
+template <typename T>
+__device__ __forceinline__ float load_delta(const bm_selscan1_args& a, int64_t gi, float dbias) {
+    float d = to_f32(static_cast<const T*>(a.delta)[gi]);
+    if (a.delta_softplus) d = softplus_stock(d + dbias);
+    return d;
+}
+
+// Level 1: segment summaries (all segments but the last, whose end state nobody needs from a zero start).
+template <typename T>
+__global__ void __launch_bounds__(CPB) selscan1_summary_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
+    __shared__ __align__(16) float bsm[SEG * NS];
+    const int I = a.d_inner, S = a.seqlen;
+    const int ntile = (I + CPB - 1) / CPB;
+    const int seg = blockIdx.x % (nseg - 1), tile = (blockIdx.x / (nseg - 1)) % ntile, b = blockIdx.x / ((nseg - 1) * ntile);
+    const int t0 = seg * SEG, nt = min(SEG, S - t0);
+    stage_rows<T>(bsm, a.b, (int64_t)b * S + t0, nt);
+    __syncthreads();
+    // channels past d_inner shadow the last one (the warp-wide vote in Decay::init wants every lane) and store nothing
+    const bool active = tile * CPB + (int)threadIdx.x < I;
+    const int i = active ? tile * CPB + threadIdx.x : I - 1;
+    Decay dec;
+    dec.init(a.a + (int64_t)i * NS);
+    const float dbias = (a.delta_softplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    uint64_t h[NS / 2];
+#pragma unroll
+    for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(0.f, 0.f);
+    float dsum = 0.f;
+    int64_t gi = ((int64_t)b * S + t0) * I + i;
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t, gi += I) {
+        const float delta = load_delta<T>(a, gi, dbias);
+        const float du = delta * to_f32(static_cast<const T*>(a.u)[gi]);
+        dsum += delta;
+        uint64_t p[NS / 2];
+        dec.factors(delta, p);
+        const uint64_t du2 = pair_f32(du, du);
+        const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
+#pragma unroll
+        for (int k = 0; k < NS / 4; ++k) {
+            const ulonglong2 bv = bp[k];
+            h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+            h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+        }
+    }
+    if (!active) return;
+    float* hl = ws.h_loc + (((int64_t)b * nseg + seg) * NS) * I + i;
+#pragma unroll
+    for (int k = 0; k < NS / 2; ++k) {
+        float lo, hi;
+        unpair(h[k], lo, hi);
+        hl[(int64_t)(2 * k) * I] = lo;
+        hl[(int64_t)(2 * k + 1) * I] = hi;
+    }
+    ws.dsum[((int64_t)b * nseg + seg) * I + i] = dsum;
+}
+
+// Level 2: the state entering every segment, per (row, channel, state).
+__global__ void selscan1_carry_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
+    const int I = a.d_inner;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // (b, n, i), i fastest
+    if (idx >= (int64_t)a.batch * NS * I) return;
+    const int i = idx % I, n = (idx / I) % NS, b = idx / ((int64_t)I * NS);
+    const float an = a.a[(int64_t)i * NS + n];
+    float h = a.h0 ? a.h0[((int64_t)b * I + i) * NS + n] : 0.f;
+    for (int seg = 0; seg < nseg; ++seg) {
+        const int64_t o = (((int64_t)b * nseg + seg) * NS + n) * I + i;
+        ws.h_in[o] = h;
+        if (seg + 1 < nseg) h = fmaf(h, __expf(an * ws.dsum[((int64_t)b * nseg + seg) * I + i]), ws.h_loc[o]);
+    }
+}
+
+// Level 3: outputs.  With nseg == 1 the entering state is h0 itself and levels 1-2 are skipped.
+template <typename T>
+__global__ void __launch_bounds__(CPB) selscan1_output_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
+    __shared__ __align__(16) float bsm[SEG * NS];
+    __shared__ __align__(16) float csm[SEG * NS];
+    const int I = a.d_inner, S = a.seqlen;
+    const int ntile = (I + CPB - 1) / CPB;
+    const int seg = blockIdx.x % nseg, tile = (blockIdx.x / nseg) % ntile, b = blockIdx.x / (nseg * ntile);
+    const int t0 = seg * SEG, nt = min(SEG, S - t0);
+    stage_rows<T>(bsm, a.b, (int64_t)b * S + t0, nt);
+    stage_rows<T>(csm, a.c, (int64_t)b * S + t0, nt);
+    __syncthreads();
+    const bool active = tile * CPB + (int)threadIdx.x < I;
+    const int i = active ? tile * CPB + threadIdx.x : I - 1;
+    Decay dec;
+    dec.init(a.a + (int64_t)i * NS);
+    const float dbias = (a.delta_softplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    const float dskip = a.d ? a.d[i] : 0.f;
+    uint64_t h[NS / 2];
+    if (nseg > 1) {
+        const float* hi_ = ws.h_in + (((int64_t)b * nseg + seg) * NS) * I + i;
+#pragma unroll
+        for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(hi_[(int64_t)(2 * k) * I], hi_[(int64_t)(2 * k + 1) * I]);
+    } else {
+        const float* h0 = a.h0 ? a.h0 + ((int64_t)b * I + i) * NS : nullptr;
+#pragma unroll
+        for (int k = 0; k < NS / 2; ++k) h[k] = h0 ? pair_f32(h0[2 * k], h0[2 * k + 1]) : pair_f32(0.f, 0.f);
+    }
+    int64_t gi = ((int64_t)b * S + t0) * I + i;
+#pragma unroll 2
+    for (int t = 0; t < nt; ++t, gi += I) {
+        const float delta = load_delta<T>(a, gi, dbias);
+        const float u = to_f32(static_cast<const T*>(a.u)[gi]);
+        const float zg = a.z ? to_f32(static_cast<const T*>(a.z)[gi]) : 0.f;
+        const float du = delta * u;
+        uint64_t p[NS / 2];
+        dec.factors(delta, p);
+        const uint64_t du2 = pair_f32(du, du);
+        const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
+        const ulonglong2* cp = reinterpret_cast<const ulonglong2*>(csm + t * NS);
+        uint64_t acc0 = pair_f32(0.f, 0.f), acc1 = pair_f32(0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < NS / 4; ++k) {
+            const ulonglong2 bv = bp[k], cv = cp[k];
+            h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+            h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+            acc0 = fma2(h[2 * k], cv.x, acc0);
+            acc1 = fma2(h[2 * k + 1], cv.y, acc1);
+        }
+        float s0, s1, s2, s3;
+        unpair(acc0, s0, s1);
+        unpair(acc1, s2, s3);
+        float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
+        if (a.z) y *= silu_f32(zg);
+        if (active) static_cast<T*>(a.y)[gi] = from_f32<T>(y);
+    }
+    if (active && seg == nseg - 1) {
+        float* hf = a.h_final + ((int64_t)b * I + i) * NS;
+#pragma unroll
+        for (int k = 0; k < NS / 2; ++k) {
+            float lo, hi;
+            unpair(h[k], lo, hi);
+            hf[2 * k] = lo;
+            hf[2 * k + 1] = hi;
+        }
+    }
+}
+
+size_t scratch_layout(const bm_selscan1_args* a, Scratch* ws, void* base) {
+    const int nseg = (int)cdiv(a->seqlen, SEG);
+    if (nseg <= 1) return 0;
+    const size_t n_h = (size_t)a->batch * nseg * NS * a->d_inner * sizeof(float);
+    const size_t n_d = align_up((size_t)a->batch * nseg * a->d_inner * sizeof(float), 256);
+    if (ws) {
+        char* p = static_cast<char*>(base);
+        ws->h_loc = reinterpret_cast<float*>(p);
+        ws->h_in = reinterpret_cast<float*>(p + align_up(n_h, 256));
+        ws->dsum = reinterpret_cast<float*>(p + 2 * align_up(n_h, 256));
+    }
+    return 2 * align_up(n_h, 256) + n_d;
+}
+
+template <typename T>
+int32_t launch_par(const bm_selscan1_args& a, const Scratch& ws, cudaStream_t st) {
+    const int nseg = (int)cdiv(a.seqlen, SEG);
+    const int ntile = (int)cdiv(a.d_inner, CPB);
+    if (nseg > 1) {
+        selscan1_summary_kernel<T><<<(unsigned)((int64_t)a.batch * ntile * (nseg - 1)), CPB, 0, st>>>(a, ws, nseg);
+        if (int32_t e = check_launch("selscan1_summary")) return e;
+        const int64_t total = (int64_t)a.batch * NS * a.d_inner;
+        selscan1_carry_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(a, ws, nseg);
+        if (int32_t e = check_launch("selscan1_carry")) return e;
+    }
+    selscan1_output_kernel<T><<<(unsigned)((int64_t)a.batch * ntile * nseg), CPB, 0, st>>>(a, ws, nseg);
+    return check_launch("selscan1_output");
+}
+
+}  // namespace
+
+namespace bm {
+int32_t validate_selscan1(const bm_selscan1_args* a);   // selscan1.cu
+}
+
+// The sequence-parallel kernels cover state_rank 16 (the reference's default); other ranks go through
+// bm_selscan1_fwd's kernels, which need no workspace.
+extern "C" size_t bm_selscan1_fwd_workspace_bytes(const bm_selscan1_args* a) {
+    if (a == nullptr || a->batch <= 0 || a->seqlen <= 0 || a->d_inner <= 0 || a->state_rank != NS) return 0;
+    return scratch_layout(a, nullptr, nullptr);
+}
+
+extern "C" int32_t bm_selscan1_fwd_ws(const bm_selscan1_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+    clear_error();
+    if (int32_t e = validate_selscan1(a)) return e;
+    if (a->state_rank != NS) return bm_selscan1_fwd(a, stream);
+    Scratch ws{};
+    const size_t need = scratch_layout(a, &ws, workspace);
+    if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+        return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
+    if (need > 0 && !aligned16(workspace)) return fail(BM_ERR_BAD_ALIGNMENT, "workspace is not 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return a->dtype == BM_DTYPE_F32 ? launch_par<float>(*a, ws, st) : launch_par<__nv_bfloat16>(*a, ws, st);
+}

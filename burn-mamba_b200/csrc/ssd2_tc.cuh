@@ -12,5 +12,13 @@ const char* ssd2_why_not(const bm_ssd2_fwd_args* a);
 size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args* a);
 int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+// The same path with two heads of a B/C group per CTA (shared C/B loads and C B^T, 128-wide readout and
+// state MMAs, sequence segments for load balance).  Needs an even number of heads per group.
+bool ssd2_pair_supported(const bm_ssd2_fwd_args* a);
+// True when the paired kernel is the better choice for this problem (more units than SMs).
+bool ssd2_pair_preferred(const bm_ssd2_fwd_args* a);
+size_t ssd2_pair_workspace_bytes(const bm_ssd2_fwd_args* a);
+int32_t ssd2_pair_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 }  // namespace tc
 }  // namespace bm

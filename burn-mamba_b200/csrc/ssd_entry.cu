@@ -13,7 +13,7 @@ static int32_t validate_ssd2(const bm_ssd2_fwd_args* a) {
     BM_REQUIRE(a->chunk_len > 0, BM_ERR_BAD_SHAPE, "chunk_len must be positive");
     BM_REQUIRE(a->ngroups > 0 && a->nheads % a->ngroups == 0, BM_ERR_BAD_SHAPE, "nheads must be divisible by ngroups");
     BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
-    BM_REQUIRE(a->path >= BM_PATH_AUTO && a->path <= BM_PATH_TENSOR, BM_ERR_UNSUPPORTED, "unknown path %d", a->path);
+    BM_REQUIRE(a->path >= BM_PATH_AUTO && a->path <= BM_PATH_TENSOR_PAIR, BM_ERR_UNSUPPORTED, "unknown path %d", a->path);
     BM_REQUIRE_PTR(a->x);
     BM_REQUIRE_PTR(a->dt);
     BM_REQUIRE_PTR(a->a);
@@ -34,6 +34,14 @@ static bool ssd2_use_tensor(const bm_ssd2_fwd_args* a) {
     return tc::ssd2_supported(a);
 }
 
+// Which tensor-core kernel serves the call: two heads per CTA when asked for, or when the problem has more
+// (batch x head) units than SMs and its heads pair up; one head per CTA otherwise.
+static bool ssd2_use_pair(const bm_ssd2_fwd_args* a) {
+    if (a->path == BM_PATH_TENSOR_SINGLE) return false;
+    if (a->path == BM_PATH_TENSOR_PAIR) return true;
+    return tc::ssd2_pair_preferred(a);
+}
+
 static exact::Params ssd2_exact_params(const bm_ssd2_fwd_args* a) {
     exact::Params p{};
     p.B = a->batch, p.S = a->seqlen, p.H = a->nheads, p.P = a->headdim, p.R = a->state_rank;
@@ -51,8 +59,15 @@ extern "C" size_t bm_ssd2_fwd_workspace_bytes(const bm_ssd2_fwd_args* a) {
     size_t ex = exact::workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len,
                                        a->chunk_states == nullptr);
     if (a->path == BM_PATH_EXACT) return ex;
-    size_t t = tc::ssd2_supported(a) ? tc::ssd2_workspace_bytes(a) : 0;
-    if (a->path == BM_PATH_TENSOR) return t;
+    size_t t = 0;
+    if (tc::ssd2_supported(a)) {
+        t = tc::ssd2_workspace_bytes(a);
+        if (tc::ssd2_pair_supported(a) && a->path != BM_PATH_TENSOR_SINGLE) {
+            const size_t tp = tc::ssd2_pair_workspace_bytes(a);
+            t = tp > t ? tp : t;
+        }
+    }
+    if (a->path != BM_PATH_AUTO) return t;
     return t > 0 ? t : ex;
 }
 
@@ -60,16 +75,21 @@ extern "C" int32_t bm_ssd2_fwd(const bm_ssd2_fwd_args* a, void* workspace, size_
     clear_error();
     if (int32_t e = validate_ssd2(a)) return e;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (a->path == BM_PATH_TENSOR && !tc::ssd2_supported(a))
+    if (a->path >= BM_PATH_TENSOR && !tc::ssd2_supported(a))
         return fail(BM_ERR_UNSUPPORTED, "tensor-core SSD path does not cover this shape/dtype: %s", tc::ssd2_why_not(a));
-    if (ssd2_use_tensor(a)) return tc::ssd2_run(a, workspace, workspace_bytes, st);
+    if (a->path == BM_PATH_TENSOR_PAIR && !tc::ssd2_pair_supported(a))
+        return fail(BM_ERR_UNSUPPORTED, "the paired tensor-core kernel needs an even number of heads per group");
+    if (ssd2_use_tensor(a)) {
+        if (ssd2_use_pair(a)) return tc::ssd2_pair_run(a, workspace, workspace_bytes, st);
+        return tc::ssd2_run(a, workspace, workspace_bytes, st);
+    }
     return exact::run(ssd2_exact_params(a), workspace, workspace_bytes, st);
 }
 
 extern "C" int32_t bm_ssd2_fwd_noalloc(const bm_ssd2_fwd_args* a, void* stream) {
     clear_error();
     if (int32_t e = validate_ssd2(a)) return e;
-    if (a->path == BM_PATH_TENSOR)
+    if (a->path >= BM_PATH_TENSOR)
         return fail(BM_ERR_UNSUPPORTED, "bm_ssd2_fwd_noalloc runs the exact path only");
     return exact::run_noalloc(ssd2_exact_params(a), static_cast<cudaStream_t>(stream));
 }
@@ -98,7 +118,7 @@ static int32_t validate_ssd3(const bm_ssd3_fwd_args* a, bool single) {
                    "rope_dim must be even and <= state_rank");
         BM_REQUIRE(a->state_rank % 2 == 0, BM_ERR_BAD_SHAPE, "state_rank must be even when rotating");
     }
-    BM_REQUIRE(a->path != BM_PATH_TENSOR, BM_ERR_UNSUPPORTED, "no tensor-core path for the Mamba-3 SSD yet");
+    BM_REQUIRE(a->path < BM_PATH_TENSOR, BM_ERR_UNSUPPORTED, "no tensor-core path for the Mamba-3 SSD yet");
     return BM_OK;
 }
 

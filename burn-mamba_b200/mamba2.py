@@ -4,8 +4,8 @@ Names, argument meaning and error behaviour follow the reference so that tests r
 `Mamba2SsdPath` (src/mamba2/ssd/ssd_path.rs:20-53), `Mamba2SsdInput.run` (:58-87, :149-155),
 `Mamba2Cache` (src/mamba2/cache.rs:98-122), `Mamba2.forward` / `Mamba2.step`
 (src/mamba2/mamba2.rs:546-786, :820-1004).  The SSM core (SSD, conv-window step, state step) runs in
-libbm_b200; the projections, the prefill convolution and the gated norm around it are plain library ops
-(torch), which is where they sit relative to the hot path in the reference as well.
+libbm_b200; the prefill convolution (+ SiLU, split into x / B / C) and the gated norm around it run in libbm_b200 as well
+(bm_conv1d_silu_fwd, bm_rmsnorm_gated); the two projections are library GEMMs (torch).
 """
 from dataclasses import dataclass
 from typing import Optional
@@ -114,12 +114,9 @@ class Mamba2:
                            torch.zeros((batch, self.nheads, self.per_head_dim, self.state_rank), device=dev))
 
     def _gated_norm(self, y, z):
-        """RmsNormGated (src/modules/norm/rms_norm_gated.rs:70-135)."""
-        silu = lambda t: t / (1.0 + torch.exp(-t))
-        x = y if self.norm_before_gate else y * silu(z)
-        eps = DIV_EPS.get(x.dtype, DIV_EPS[torch.float32])
-        out = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * self.norm_gamma
-        return out * silu(z) if self.norm_before_gate else out
+        """RmsNormGated (src/modules/norm/rms_norm_gated.rs:70-135): one kernel, z read in place from the
+        projection's columns."""
+        return ops.rmsnorm_gated(y, z, self.norm_gamma.to(y.dtype), norm_before_gate=self.norm_before_gate)
 
     def forward(self, input_bsm, cache: Optional[Mamba2Cache] = None, ssd_path: Mamba2SsdPath = Mamba2SsdPath(),
                 kernel_path="auto"):
@@ -131,16 +128,14 @@ class Mamba2:
         act = input_bsm.dtype
         proj = input_bsm @ self.w_in
         z, xbc, dt_raw = torch.split(proj, [self.d_inner, self.conv_dim, self.nheads], dim=2)
-        padded = torch.cat([cache.conv_bvk[:, :, 1:].to(act), xbc.transpose(1, 2)], dim=2)      # b v (k-1+s)
-        new_conv = padded[:, :, s - 1:].float().contiguous()
-        conv = F.conv1d(padded, self.conv_w.to(act).unsqueeze(1), self.conv_b.to(act), groups=self.conv_dim)
-        conv = conv.transpose(1, 2)
-        xbc_act = conv / (1.0 + torch.exp(-conv))
+        # window slide + causal depthwise conv + bias + SiLU in one kernel, reading xbc in place from the
+        # projection's columns and writing x, B, C as the three dense tensors the SSD takes
         gr = self.ngroups * self.state_rank
-        x, bm, cm = torch.split(xbc_act, [self.d_inner, gr, gr], dim=2)
-        x = x.reshape(bsz, s, self.nheads, self.per_head_dim).contiguous()
-        bm = bm.reshape(bsz, s, self.ngroups, self.state_rank).contiguous()
-        cm = cm.reshape(bsz, s, self.ngroups, self.state_rank).contiguous()
+        (x, bm, cm), new_conv = ops.conv1d_silu_fwd(xbc, self.conv_w.float(), self.conv_b.float(), cache.conv_bvk,
+                                                    splits=(self.d_inner, gr, gr))
+        x = x.view(bsz, s, self.nheads, self.per_head_dim)
+        bm = bm.view(bsz, s, self.ngroups, self.state_rank)
+        cm = cm.view(bsz, s, self.ngroups, self.state_rank)
         a = -torch.exp(self.a_log)
         chunk_len = ssd_path.chunk_len_or_optimal(self.state_rank, self.per_head_dim)
         # softplus(dt_raw + dt_bias) and the clamp are fused into the SSD's decay scan; the tail chunk is

@@ -12,7 +12,8 @@ from . import _ffi
 from ._ffi import lib, check
 
 _DT = {torch.float32: _ffi.BM_DTYPE_F32, torch.bfloat16: _ffi.BM_DTYPE_BF16}
-PATHS = {"auto": _ffi.BM_PATH_AUTO, "exact": _ffi.BM_PATH_EXACT, "tensor": _ffi.BM_PATH_TENSOR}
+PATHS = {"auto": _ffi.BM_PATH_AUTO, "exact": _ffi.BM_PATH_EXACT, "tensor": _ffi.BM_PATH_TENSOR,
+         "tensor_single": _ffi.BM_PATH_TENSOR_SINGLE, "tensor_pair": _ffi.BM_PATH_TENSOR_PAIR}
 
 
 def _ptr(t):
@@ -120,8 +121,79 @@ def conv_step(window, xin, weight, bias=None):
     return out
 
 
-def selscan1_fwd(u, delta, a, b, c, d=None, z=None, h0=None, delta_bias=None, delta_softplus=False):
-    """Mamba-1 selective scan.  u/delta/z [b,s,i], a [i,r] f32, b/c [b,s,r] -> (y [b,s,i], h_final [b,i,r] f32)."""
+DIV_EPS = {torch.float32: 8.1584695e-8, torch.bfloat16: 2.0885676e-5}   # src/utils/mod.rs:50-95
+
+
+_keepalive = []   # dense copies made by _rows stay referenced until the next call has been enqueued
+
+
+def _rows(t, name):
+    """(data_ptr, row stride) of a 2-D+ tensor whose last axis is contiguous and whose leading axes collapse
+    into rows of one stride (a dense tensor, or a column slice of one)."""
+    if t.stride(-1) != 1:
+        raise ValueError(f"{name}: last axis must be contiguous")
+    stride = t.stride(-2) if t.dim() >= 2 else t.shape[-1]
+    if (stride * t.element_size()) % 16 or t.data_ptr() % 16:
+        t = t.contiguous()     # rows of a slice that do not start 16-byte aligned: fall back to a dense copy
+        stride = t.shape[-1]
+        _keepalive.append(t)
+    for d in range(t.dim() - 2):
+        if t.stride(d) != t.stride(d + 1) * t.shape[d + 1]:
+            raise ValueError(f"{name}: leading axes must collapse into rows of one stride")
+    return t.data_ptr(), stride
+
+
+def conv1d_silu_fwd(xbc, weight, bias=None, window=None, splits=None, want_window=True):
+    """Prefill causal depthwise conv + bias + SiLU.  xbc [b, s, v] (may be a column slice), weight [v, k] f32,
+    window [b, v, k] f32 or None -> (out [b,s,v] or (x, B, C) when splits = (split_x, split_bc, split_bc), new_window)."""
+    bsz, s, v = xbc.shape
+    k = weight.shape[1]
+    act = xbc.dtype
+    if not xbc.is_cuda:
+        raise ValueError("xbc must be a CUDA tensor (this library has no CPU path)")
+    del _keepalive[:]
+    ptr, stride = _rows(xbc, "xbc")
+    _chk(weight, "weight", torch.float32, (v, k)); _chk(bias, "bias", torch.float32, (v,), optional=True)
+    _chk(window, "window", torch.float32, (bsz, v, k), optional=True)
+    new_window = torch.empty((bsz, v, k), dtype=torch.float32, device=xbc.device) if want_window else None
+    if splits is None:
+        outs = (torch.empty((bsz, s, v), dtype=act, device=xbc.device), None, None)
+        sx = sbc = 0
+    else:
+        sx, sbc, sbc2 = splits
+        if sbc != sbc2 or sx + 2 * sbc != v:
+            raise ValueError("splits must be (split_x, split_bc, split_bc) summing to the channel count")
+        outs = tuple(torch.empty((bsz, s, n), dtype=act, device=xbc.device) for n in (sx, sbc, sbc))
+    args = _ffi.Conv1dSiluArgs(batch=bsz, seqlen=s, channels=v, kernel=k, dtype=_DT[act], xin_stride=stride, split_x=sx,
+                               split_bc=sbc, xin=ptr, weight=_ptr(weight), bias=_ptr(bias), window=_ptr(window),
+                               new_window=_ptr(new_window), out_x=_ptr(outs[0]), out_b=_ptr(outs[1]), out_c=_ptr(outs[2]))
+    check(lib.bm_conv1d_silu_fwd(C.byref(args), _stream()), "bm_conv1d_silu_fwd")
+    return (outs[0] if splits is None else outs), new_window
+
+
+def rmsnorm_gated(x, z, gamma, norm_before_gate=False, eps=None):
+    """RmsNormGated over the last axis (z = None: plain RmsNorm).  x / z [..., d] (may be column slices), gamma [d]."""
+    d = x.shape[-1]
+    act = x.dtype
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor (this library has no CPU path)")
+    del _keepalive[:]
+    xp, xs = _rows(x, "x")
+    zp, zs = (None, 0) if z is None else _rows(z, "z")
+    _chk(gamma, "gamma", act, (d,))
+    out = torch.empty(tuple(x.shape), dtype=act, device=x.device)
+    rows = out.numel() // d
+    args = _ffi.RmsnormGatedArgs(rows=rows, width=d, dtype=_DT[act], norm_before_gate=int(norm_before_gate), x_stride=xs,
+                                 z_stride=zs, eps=DIV_EPS[act] if eps is None else eps, x=xp, z=zp, gamma=_ptr(gamma),
+                                 out=_ptr(out))
+    check(lib.bm_rmsnorm_gated(C.byref(args), _stream()), "bm_rmsnorm_gated")
+    return out
+
+
+def selscan1_fwd(u, delta, a, b, c, d=None, z=None, h0=None, delta_bias=None, delta_softplus=False, serial=False):
+    """Mamba-1 selective scan.  u/delta/z [b,s,i], a [i,r] f32, b/c [b,s,r] -> (y [b,s,i], h_final [b,i,r] f32).
+    The sequence-parallel kernels (bm_selscan1_fwd_ws) are used unless `serial` asks for the kernels that walk
+    the sequence in order and need no workspace (bm_selscan1_fwd)."""
     bsz, s, di = u.shape
     r = a.shape[1]
     act = u.dtype
@@ -135,7 +207,11 @@ def selscan1_fwd(u, delta, a, b, c, d=None, z=None, h0=None, delta_bias=None, de
                              delta_softplus=int(delta_softplus), u=_ptr(u), delta=_ptr(delta), a=_ptr(a), b=_ptr(b),
                              c=_ptr(c), d=_ptr(d), delta_bias=_ptr(delta_bias), z=_ptr(z), h0=_ptr(h0), y=_ptr(y),
                              h_final=_ptr(h_final))
-    check(lib.bm_selscan1_fwd(C.byref(args), _stream()), "bm_selscan1_fwd")
+    if serial:
+        check(lib.bm_selscan1_fwd(C.byref(args), _stream()), "bm_selscan1_fwd")
+    else:
+        ws = _workspace(lib.bm_selscan1_fwd_workspace_bytes(C.byref(args)), u.device)
+        check(lib.bm_selscan1_fwd_ws(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_selscan1_fwd_ws")
     return y, h_final
 
 

@@ -56,7 +56,10 @@ typedef enum { BM_DTYPE_F32 = 0, BM_DTYPE_BF16 = 1 } bm_dtype;
 typedef enum {
     BM_PATH_AUTO = 0,    /* tensor-core path when dtype/shape allow it, else the exact path */
     BM_PATH_EXACT = 1,   /* CUDA-core float32 arithmetic for any shape and dtype */
-    BM_PATH_TENSOR = 2   /* tcgen05/TMEM/TMA path; BM_ERR_UNSUPPORTED if the shape is not covered */
+    BM_PATH_TENSOR = 2,  /* tcgen05/TMEM/TMA path; BM_ERR_UNSUPPORTED if the shape is not covered */
+    /* the two kernels of the tensor-core path, which BM_PATH_AUTO / BM_PATH_TENSOR choose between by problem size */
+    BM_PATH_TENSOR_SINGLE = 3,  /* one head per CTA */
+    BM_PATH_TENSOR_PAIR = 4     /* two heads of a B/C group per CTA (even heads per group), sequence segments */
 } bm_path;
 
 /* ABI version (major << 16 | minor) and a human-readable build string. */
@@ -205,6 +208,49 @@ typedef struct {
 
 int32_t bm_conv_step(const bm_conv_step_args* args, void* stream);
 
+/* Prefill twin of bm_conv_step: causal depthwise conv over a whole sequence + bias + SiLU, with the left context
+ * taken from the cache window and the new window written out (src/mamba2/mamba2.rs:618-654: window slide, Conv1d,
+ * SiLU; Mamba-1 twin src/mamba1/mamba1.rs:316-340).  The input may be a column slice of the in-projection's
+ * output (row stride `xin_stride`, elements).  The output is either one [b, s, v] tensor (out_b = out_c = NULL) or
+ * the three tensors the SSD reads, split along channels exactly like the reference's split of xbc:
+ * x [b, s, split_x], B [b, s, split_bc], C [b, s, split_bc] (split_x + 2 split_bc = v, multiples of 8).
+ *   out[t, c] = silu(bias[c] + sum_k w[c, k] in[t - (K-1) + k, c]),  in[t < 0] = window[c, K + t]. */
+typedef struct {
+    int32_t batch, seqlen, channels, kernel;   /* kernel: 2, 3 or 4 taps */
+    int32_t dtype;            /* bm_dtype of xin and the outputs */
+    int32_t xin_stride;       /* elements between consecutive tokens of xin (>= channels, multiple of 8) */
+    int32_t split_x, split_bc;
+    const void* xin;          /* [b, s, v] rows of stride xin_stride */
+    const float* weight;      /* [v, k] */
+    const float* bias;        /* [v] or NULL */
+    const float* window;      /* [b, v, k] cache window before the sequence (newest column last); NULL = zeros */
+    float* new_window;        /* [b, v, k] window after the sequence, or NULL; must not alias `window` */
+    void* out_x;              /* [b, s, split_x], or the whole [b, s, v] when out_b is NULL */
+    void* out_b;              /* [b, s, split_bc] or NULL */
+    void* out_c;              /* [b, s, split_bc] or NULL */
+} bm_conv1d_silu_args;
+
+int32_t bm_conv1d_silu_fwd(const bm_conv1d_silu_args* args, void* stream);
+
+/* Gated RMS norm over the last axis, one row per token (RmsNormGated, src/modules/norm/rms_norm_gated.rs:70-135;
+ * with z = NULL the plain RmsNorm, src/modules/norm/rms_norm.rs:53-98):
+ *   norm_before_gate = 0 (the reference's default):  g = x silu(z);  out = g / sqrt(mean(g^2) + eps) * gamma
+ *   norm_before_gate = 1:                            out = x / sqrt(mean(x^2) + eps) * gamma * silu(z)
+ * x and z may be column slices of wider rows (row strides in elements); out is dense [rows, width]. */
+typedef struct {
+    int32_t rows, width;      /* width: multiple of 8, at most 8192 */
+    int32_t dtype;            /* bm_dtype of x, z, gamma, out */
+    int32_t norm_before_gate;
+    int32_t x_stride, z_stride;
+    float eps;                /* the reference's per-dtype epsilon (src/utils/mod.rs:50-95) */
+    const void* x;
+    const void* z;            /* or NULL */
+    const void* gamma;        /* [width] */
+    void* out;                /* [rows, width] */
+} bm_rmsnorm_gated_args;
+
+int32_t bm_rmsnorm_gated(const bm_rmsnorm_gated_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Mamba-1 selective scan (sequence) and single-token step.
  * Replace Mamba1::selective_scan (src/mamba1/mamba1.rs:422-523) and
@@ -230,6 +276,13 @@ typedef struct {
 } bm_selscan1_args;
 
 int32_t bm_selscan1_fwd(const bm_selscan1_args* args, void* stream);
+
+/* The same scan, parallel over the sequence as well (replaces the same reference function): the sequence is cut
+ * into segments that are scanned on two levels (segment summaries, a short carry pass, outputs), which needs a
+ * caller-provided workspace for the per-segment states.  Same arguments and results as bm_selscan1_fwd; covers
+ * state_rank 16 (the reference's default) and falls back to bm_selscan1_fwd's kernels for other ranks. */
+size_t bm_selscan1_fwd_workspace_bytes(const bm_selscan1_args* args);
+int32_t bm_selscan1_fwd_ws(const bm_selscan1_args* args, void* workspace, size_t workspace_bytes, void* stream);
 
 typedef struct {
     int32_t batch, d_inner, state_rank;

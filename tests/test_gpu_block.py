@@ -145,3 +145,57 @@ def test_mamba3_block_forward_equals_unrolled_step(bm, m):
     for k in ("ssm", "k", "v"):
         assert rel_l2(cache[k].cpu().numpy(), c[k].cpu().numpy()) <= 1e-4, k
     assert (cache["angle"] - c["angle"]).abs().max().item() <= 1e-4
+
+
+# ------------------------------------------------------------------ pre- / post-SSD kernels of the block
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("b,s,k", [(2, 70, 4), (1, 3, 4), (2, 33, 2), (1, 1, 4)])
+def test_conv1d_silu_prefill_matches_window_slide_and_conv(bm, dtype, b, s, k):
+    """Causal depthwise conv + bias + SiLU over a sequence with the cache window as left context
+    (src/mamba2/mamba2.rs:618-654), input read in place from a column slice, outputs split into x / B / C."""
+    from oracle.numerics import silu
+    rng = np.random.default_rng(5)
+    v, sx, sbc = 48, 32, 8
+    wide = rng.standard_normal((b, s, 16 + v + 8)).astype(np.float32)     # xbc sits in the middle of a wider row
+    win = rng.standard_normal((b, v, k)).astype(np.float32)
+    w = rng.standard_normal((v, k)).astype(np.float32)
+    bias = rng.standard_normal(v).astype(np.float32)
+    wide_t = torch.from_numpy(wide).cuda().to(dtype)
+    xin = wide_t.float().cpu().numpy()[:, :, 16:16 + v]
+    padded = np.concatenate([win[:, :, 1:], xin.transpose(0, 2, 1)], axis=2)           # b v (k-1+s)
+    want = np.stack([(padded[:, :, t:t + k] * w[None]).sum(-1) + bias[None] for t in range(s)], axis=1)
+    want = silu(want)
+    (x, bb, cc), new_win = bm.ops.conv1d_silu_fwd(wide_t[:, :, 16:16 + v], torch.from_numpy(w).cuda(),
+                                                  torch.from_numpy(bias).cuda(), torch.from_numpy(win).cuda(),
+                                                  splits=(sx, sbc, sbc))
+    got = torch.cat([x, bb, cc], dim=2).float().cpu().numpy()
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert rel_l2(got, want) <= tol
+    assert np.array_equal(new_win.cpu().numpy(), padded[:, :, s - 1:].astype(np.float32))
+    whole, _ = bm.ops.conv1d_silu_fwd(wide_t[:, :, 16:16 + v], torch.from_numpy(w).cuda(), torch.from_numpy(bias).cuda(),
+                                      None, want_window=False)
+    padded0 = np.concatenate([np.zeros((b, v, k - 1), np.float32), xin.transpose(0, 2, 1)], axis=2)
+    want0 = silu(np.stack([(padded0[:, :, t:t + k] * w[None]).sum(-1) + bias[None] for t in range(s)], axis=1))
+    assert rel_l2(whole.float().cpu().numpy(), want0) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("norm_before_gate", [False, True])
+def test_rmsnorm_gated_matches_oracle(bm, dtype, norm_before_gate):
+    """RmsNormGated (src/modules/norm/rms_norm_gated.rs:70-135) and the plain RmsNorm (z = None), with z read
+    in place from a column slice of a wider row."""
+    from oracle.numerics import rms_norm, rms_norm_gated
+    rng = np.random.default_rng(6)
+    rows, d = 37, 5120
+    x = rng.standard_normal((rows, d)).astype(np.float32)
+    wide = rng.standard_normal((rows, d + 264)).astype(np.float32)
+    gamma = rng.standard_normal(d).astype(np.float32)
+    xt, wt, gt = (torch.from_numpy(t).cuda().to(dtype) for t in (x, wide, gamma))
+    xq, zq, gq = xt.float().cpu().numpy(), wt.float().cpu().numpy()[:, 8:8 + d], gt.float().cpu().numpy()
+    name = "f32" if dtype == torch.float32 else "bf16"
+    want = rms_norm_gated(xq.astype(np.float64), zq.astype(np.float64), gq.astype(np.float64), norm_before_gate, name)
+    got = bm.ops.rmsnorm_gated(xt, wt[:, 8:8 + d], gt, norm_before_gate=norm_before_gate)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert rel_l2(got.float().cpu().numpy(), want) <= tol
+    plain = bm.ops.rmsnorm_gated(xt.reshape(1, rows, d), None, gt)
+    assert rel_l2(plain.float().cpu().numpy()[0], rms_norm(xq.astype(np.float64), gq.astype(np.float64), name)) <= tol

@@ -391,3 +391,70 @@ def test_ssd3_backward_matches_autodiff_oracle(bm, b, s, h, p, r, m, Q):
     got = bm.ops.ssd3_bwd(*(dev(t) for t in args), dev(dy), dev(dhf), chunk_len=Q, single=False)
     for k in ("dv", "dda", "db", "dc", "dh0"):
         assert _grad_close(got[k], want[k]), ("double", k, rel_l2(host(got[k]), want[k]))
+
+
+# ------------------------------------------------------------------ Mamba-2 SSD, two heads per CTA (opt-in kernel)
+def _pair_case(bm, cfg, Q, oracle=True):
+    dt = torch.bfloat16
+    x, bb, cc = (q(cfg[k], dt) for k in ("x", "b", "c"))
+    args = (dev(x, dt), dev(cfg["dt"]), dev(cfg["a"]), dev(bb, dt), dev(cc, dt), dev(cfg["d"]), dev(cfg["h0"]))
+    y, hf = bm.ops.ssd2_fwd(*args, chunk_len=Q, path="tensor_pair", check_status=True)
+    ye, he = bm.ops.ssd2_fwd(*args, chunk_len=Q, path="exact")
+    assert torch.isfinite(y.float()).all() and torch.isfinite(hf).all()
+    assert rel_l2(host(y), host(ye)) <= 2e-2 and rel_l2(host(hf), host(he)) <= 2e-2
+    if oracle:
+        want_y, want_h = mamba2.ssd_serial(x, cfg["dt"], cfg["a"], bb, cc, cfg["d"], cfg["h0"], Q)
+        assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
+
+
+@pytest.mark.parametrize("b,s,h,g,Q", [
+    (1, 128, 2, 1, 128),     # one pair, one tile
+    (2, 512, 4, 2, 256),     # two groups
+    (1, 300, 2, 1, 128),     # ragged tail (rows past the end are clipped by the store)
+    (1, 100, 2, 1, 64),      # shorter than one tile
+    (1, 4096, 4, 1, 256),    # long sequence
+])
+def test_ssd2_pair_kernel_matches_oracle(bm, b, s, h, g, Q):
+    cfg = inputs.ssd2_prefill(seed=400 + s, batch=b, seqlen=s, nheads=h, headdim=64, state_rank=128, ngroups=g,
+                              h0_std=0.1)
+    _pair_case(bm, cfg, Q)
+
+
+def test_ssd2_pair_kernel_segments_and_many_pairs(bm):
+    """More pairs than SMs and a sequence long enough to be cut into segments whose state is handed from CTA to
+    CTA through the workspace; every unit against the float32 exact path on device."""
+    _pair_case(bm, inputs.ssd2_prefill(seed=41, batch=3, seqlen=384, nheads=160, headdim=64, state_rank=128), 256, oracle=False)
+    _pair_case(bm, inputs.ssd2_prefill(seed=42, batch=4, seqlen=4096, nheads=80, headdim=64, state_rank=128), 256, oracle=False)
+
+
+def test_ssd2_pair_kernel_strong_zero_and_tiny_steps(bm):
+    """Decay far beyond what one pass represents (the tile is walked in sub-ranges), steps of exactly zero, and
+    steps below the kernel's step floor: results stay finite and within tolerance, D x passes through."""
+    cfg = inputs.ssd2_prefill(seed=43, batch=1, seqlen=256, nheads=2, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["dt"] = (cfg["dt"] * 0 + 3.0).astype(np.float32)
+    cfg["a"] = np.float32([-16.0, -0.001])
+    _pair_case(bm, cfg, 256)
+    cfg = inputs.ssd2_prefill(seed=44, batch=1, seqlen=384, nheads=4, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["dt"][:, 5::7, :] = 0.0
+    cfg["dt"][:, 200:300, 1] = 0.0
+    _pair_case(bm, cfg, 128)
+    cfg = inputs.ssd2_prefill(seed=45, batch=2, seqlen=1024, nheads=6, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["a"] = np.float32([-0.5, -16.0, -1.0, -12.0, -0.01, -8.0])
+    rng = np.random.default_rng(7)
+    cfg["dt"] = (rng.random(cfg["dt"].shape) * np.float32([0.01, 0.8, 0.02, 0.5, 0.05, 0.3])).astype(np.float32)
+    cfg["dt"][:, 512:640] *= 40.0
+    _pair_case(bm, cfg, 256)
+    cfg = inputs.ssd2_prefill(seed=46, batch=1, seqlen=256, nheads=2, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["a"] = np.float32([-1.0, -1.0])
+    dtv = np.full((1, 256, 2), 95.0 / (128 * 1.4426950408889634), np.float32)
+    dtv[0, 0, 0], dtv[0, 128, 1] = 1e-9, 1e-30
+    cfg["dt"] = dtv
+    _pair_case(bm, cfg, 128)
+
+
+def test_ssd2_pair_kernel_refuses_odd_heads_per_group(bm):
+    cfg = inputs.ssd2_prefill(seed=47, batch=1, seqlen=128, nheads=3, headdim=64, state_rank=128, ngroups=1)
+    t = {k: dev(v, torch.bfloat16 if k in ("x", "b", "c") else None) for k, v in cfg.items()}
+    with pytest.raises(bm.BmError) as e:
+        bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], None, chunk_len=128, path="tensor_pair")
+    assert e.value.code == bm._ffi.BM_ERR_UNSUPPORTED
