@@ -657,11 +657,8 @@ def decode_step_leg(torch, bm, dev, layers=64, batch=256, steps=8):
 
     def ssm_only():
         for l in range(layers):
-            xbc = bm.ops.conv_step(wins[l], xin, w, bias)
-            x = xbc[:, :H * P].reshape(batch, H, P).contiguous()
-            bb = xbc[:, H * P:H * P + R].reshape(batch, 1, R).contiguous()
-            cc = xbc[:, H * P + R:].reshape(batch, 1, R).contiguous()
-            bm.ops.step2(states[l], x, dt, a, bb, cc, d)
+            x, bb, cc = bm.ops.conv_step(wins[l], xin, w, bias, splits=(H * P, R, R))
+            bm.ops.step2(states[l], x.view(batch, H, P), dt, a, bb.view(batch, 1, R), cc.view(batch, 1, R), d)
 
     def time_steps(fn, n):
         for _ in range(2):

@@ -36,7 +36,8 @@ class Step2Args(C.Structure):
 
 class ConvStepArgs(C.Structure):
     _fields_ = [(n, _i32) for n in ("batch", "channels", "kernel", "dtype")] + [
-        ("window", _vp), ("xin", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp)]
+        ("window", _vp), ("xin", _vp), ("weight", _vp), ("bias", _vp), ("out", _vp), ("out_b", _vp), ("out_c", _vp),
+        ("xin_stride", _i32), ("split_x", _i32), ("split_bc", _i32), ("reserved", _i32)]
 
 
 class Conv1dSiluArgs(C.Structure):

@@ -12,7 +12,7 @@ using namespace bm;
 
 namespace {
 
-constexpr int TL = 32;        // tokens per thread in the conv kernel
+constexpr int TL = 4;         // tokens per thread in the conv kernel
 constexpr int VEC = 8;        // channels per thread (16 bytes of bf16, 32 of f32)
 
 template <typename T>
@@ -52,10 +52,11 @@ __device__ __forceinline__ void Vec8<__nv_bfloat16>::store(__nv_bfloat16* p) con
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// One thread: 8 adjacent channels x TL consecutive tokens, a K-deep window of the inputs in registers.
+// One thread: 8 adjacent channels x TL consecutive tokens.  All TL + K - 1 input rows of the thread are fetched
+// before anything is computed (the loads are independent, so they are all in flight together).
 // Consecutive threads take consecutive channel vectors, so every row access of a warp is one contiguous run.
 template <typename T, int K>
-__global__ void __launch_bounds__(128) conv1d_silu_kernel(bm_conv1d_silu_args a) {
+__global__ void __launch_bounds__(128, 6) conv1d_silu_kernel(bm_conv1d_silu_args a) {
     const int V = a.channels, S = a.seqlen;
     const int nvec = V / VEC;
     const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -64,25 +65,33 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(bm_conv1d_silu_args a)
     const int chunk = (gid / nvec) % nchunk;
     const int b = gid / ((int64_t)nvec * nchunk);
     if (b >= a.batch) return;
-    const int c0 = vec * VEC, t0 = chunk * TL, t1 = min(S, t0 + TL);
+    const int c0 = vec * VEC, t0 = chunk * TL;
+    const T* xin = static_cast<const T*>(a.xin) + (int64_t)b * S * a.xin_stride + c0;
+    Vec8<T> in[TL + K - 1];
+#pragma unroll
+    for (int r = 0; r < TL + K - 1; ++r) {
+        const int t = t0 - (K - 1) + r;
+        if (t >= 0 && t < S) {
+            in[r].load(xin + (int64_t)t * a.xin_stride);
+        } else {
+            // before the sequence: the cache window's column K + t (its last K - 1 columns are tokens -K+1 .. -1)
+#pragma unroll
+            for (int j = 0; j < VEC; ++j)
+                in[r].v[j] = (t < 0 && a.window) ? a.window[((int64_t)b * V + c0 + j) * K + (K + t)] : 0.f;
+        }
+    }
     float w[K][VEC], bias[VEC];
 #pragma unroll
     for (int j = 0; j < VEC; ++j) {
         bias[j] = a.bias ? a.bias[c0 + j] : 0.f;
-#pragma unroll
-        for (int k = 0; k < K; ++k) w[k][j] = a.weight[(int64_t)(c0 + j) * K + k];
-    }
-    const T* xin = static_cast<const T*>(a.xin) + (int64_t)b * S * a.xin_stride + c0;
-    // input at token t (t < 0: the cache window's column K + t, i.e. its last K - 1 columns are tokens -K+1 .. -1)
-    auto input = [&](int t, Vec8<T>& out) {
-        if (t >= 0) {
-            out.load(xin + (int64_t)t * a.xin_stride);
+        if (K == 4) {   // one 16-byte load per channel (rows of the [v, 4] weight are 16-byte aligned)
+            const float4 wv = *reinterpret_cast<const float4*>(a.weight + (int64_t)(c0 + j) * 4);
+            w[0][j] = wv.x, w[1 % K][j] = wv.y, w[2 % K][j] = wv.z, w[3 % K][j] = wv.w;
         } else {
 #pragma unroll
-            for (int j = 0; j < VEC; ++j)
-                out.v[j] = a.window ? a.window[((int64_t)b * V + c0 + j) * K + (K + t)] : 0.f;
+            for (int k = 0; k < K; ++k) w[k][j] = a.weight[(int64_t)(c0 + j) * K + k];
         }
-    };
+    }
     // which output tensor this channel vector belongs to
     T* dst;
     int64_t dstride;
@@ -95,22 +104,19 @@ __global__ void __launch_bounds__(128) conv1d_silu_kernel(bm_conv1d_silu_args a)
     } else {
         dst = static_cast<T*>(a.out_c) + (int64_t)b * S * a.split_bc + (c0 - a.split_x - a.split_bc), dstride = a.split_bc;
     }
-    Vec8<T> win[K];
 #pragma unroll
-    for (int k = 0; k < K - 1; ++k) input(t0 - (K - 1) + k, win[k]);
-    for (int t = t0; t < t1; ++t) {
-        input(t, win[K - 1]);
-        Vec8<T> o;
+    for (int i = 0; i < TL; ++i) {
+        if (t0 + i < S) {
+            Vec8<T> o;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            float acc = bias[j];
+            for (int j = 0; j < VEC; ++j) {
+                float acc = bias[j];
 #pragma unroll
-            for (int k = 0; k < K; ++k) acc = fmaf(win[k].v[j], w[k][j], acc);
-            o.v[j] = silu_f32(acc);
+                for (int k = 0; k < K; ++k) acc = fmaf(in[i + k].v[j], w[k][j], acc);
+                o.v[j] = silu_fast(acc);
+            }
+            o.store(dst + (int64_t)(t0 + i) * dstride);
         }
-        o.store(dst + (int64_t)t * dstride);
-#pragma unroll
-        for (int k = 0; k < K - 1; ++k) win[k] = win[k + 1];
     }
 }
 
@@ -155,7 +161,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args
                 Vec8<T> zv;
                 zv.load(zr + c);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) xv[i].v[j] *= silu_f32(zv.v[j]);
+                for (int j = 0; j < VEC; ++j) xv[i].v[j] *= silu_fast(zv.v[j]);
             }
 #pragma unroll
             for (int j = 0; j < VEC; ++j) ss = fmaf(xv[i].v[j], xv[i].v[j], ss);
@@ -181,7 +187,7 @@ __global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args
                 Vec8<T> zv;
                 zv.load(zr + c);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) ov.v[j] *= silu_f32(zv.v[j]);
+                for (int j = 0; j < VEC; ++j) ov.v[j] *= silu_fast(zv.v[j]);
             }
             ov.store(orow + c);
         }

@@ -55,6 +55,9 @@ __device__ __forceinline__ float softplus_f32(float x) { return x > 18.f ? x : l
 __device__ __forceinline__ float softplus_stock(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 // x / (1 + exp(-x)) (src/modules/activation/silu.rs:24-27)
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.f + expf(-x)); }
+// The same gate with the hardware exponential and reciprocal (about 1e-6 relative): for the streaming kernels
+// that evaluate it once per element of a large activation tensor, where the exact division is most of the work.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 // theta - round(theta / 2pi) * 2pi (src/modules/misc/rope.rs:23-27)
 __device__ __forceinline__ float wrap_angle(float t) {
     const float two_pi = 6.28318530717958647692f;

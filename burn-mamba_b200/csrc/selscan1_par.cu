@@ -29,6 +29,8 @@ namespace {
 constexpr int SEG = 128;      // tokens per segment
 constexpr int CPB = 128;      // channels (threads) per CTA
 constexpr int NS = 16;        // states handled by the fast kernels
+constexpr int PF = 8;         // tokens whose loads are in flight together (summary kernel)
+constexpr int PFO = 4;        // the same for the output kernel, which has fewer registers to spare
 
 __device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
@@ -74,16 +76,9 @@ struct Decay {
     }
 };
 
-template <typename T>
-__device__ __forceinline__ float load_delta(const bm_selscan1_args& a, int64_t gi, float dbias) {
-    float d = to_f32(static_cast<const T*>(a.delta)[gi]);
-    if (a.delta_softplus) d = softplus_stock(d + dbias);
-    return d;
-}
-
 // Level 1: segment summaries (all segments but the last, whose end state nobody needs from a zero start).
 template <typename T>
-__global__ void __launch_bounds__(CPB) selscan1_summary_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
+__global__ void __launch_bounds__(CPB, 6) selscan1_summary_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
     __shared__ __align__(16) float bsm[SEG * NS];
     const int I = a.d_inner, S = a.seqlen;
     const int ntile = (I + CPB - 1) / CPB;
@@ -101,21 +96,35 @@ __global__ void __launch_bounds__(CPB) selscan1_summary_kernel(bm_selscan1_args 
 #pragma unroll
     for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(0.f, 0.f);
     float dsum = 0.f;
-    int64_t gi = ((int64_t)b * S + t0) * I + i;
-#pragma unroll 2
-    for (int t = 0; t < nt; ++t, gi += I) {
-        const float delta = load_delta<T>(a, gi, dbias);
-        const float du = delta * to_f32(static_cast<const T*>(a.u)[gi]);
-        dsum += delta;
-        uint64_t p[NS / 2];
-        dec.factors(delta, p);
-        const uint64_t du2 = pair_f32(du, du);
-        const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
+    const int64_t g0 = ((int64_t)b * S + t0) * I + i;
+    // tokens are taken PF at a time: their loads are issued together, then the recurrence runs over them
+#pragma unroll 1
+    for (int tb = 0; tb < nt; tb += PF) {
+        T draw[PF], uraw[PF];
 #pragma unroll
-        for (int k = 0; k < NS / 4; ++k) {
-            const ulonglong2 bv = bp[k];
-            h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
-            h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+        for (int j = 0; j < PF; ++j) {
+            const int64_t gi = g0 + (int64_t)min(tb + j, nt - 1) * I;
+            draw[j] = static_cast<const T*>(a.delta)[gi];
+            uraw[j] = static_cast<const T*>(a.u)[gi];
+        }
+#pragma unroll
+        for (int j = 0; j < PF; ++j) {
+            if (tb + j < nt) {
+                float delta = to_f32(draw[j]);
+                if (a.delta_softplus) delta = softplus_stock(delta + dbias);
+                const float du = delta * to_f32(uraw[j]);
+                dsum += delta;
+                uint64_t p[NS / 2];
+                dec.factors(delta, p);
+                const uint64_t du2 = pair_f32(du, du);
+                const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + (tb + j) * NS);
+#pragma unroll
+                for (int k = 0; k < NS / 4; ++k) {
+                    const ulonglong2 bv = bp[k];
+                    h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+                    h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+                }
+            }
         }
     }
     if (!active) return;
@@ -147,7 +156,7 @@ __global__ void selscan1_carry_kernel(bm_selscan1_args a, Scratch ws, int nseg) 
 
 // Level 3: outputs.  With nseg == 1 the entering state is h0 itself and levels 1-2 are skipped.
 template <typename T>
-__global__ void __launch_bounds__(CPB) selscan1_output_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
+__global__ void __launch_bounds__(CPB, 6) selscan1_output_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
     __shared__ __align__(16) float bsm[SEG * NS];
     __shared__ __align__(16) float csm[SEG * NS];
     const int I = a.d_inner, S = a.seqlen;
@@ -173,33 +182,46 @@ __global__ void __launch_bounds__(CPB) selscan1_output_kernel(bm_selscan1_args a
 #pragma unroll
         for (int k = 0; k < NS / 2; ++k) h[k] = h0 ? pair_f32(h0[2 * k], h0[2 * k + 1]) : pair_f32(0.f, 0.f);
     }
-    int64_t gi = ((int64_t)b * S + t0) * I + i;
-#pragma unroll 2
-    for (int t = 0; t < nt; ++t, gi += I) {
-        const float delta = load_delta<T>(a, gi, dbias);
-        const float u = to_f32(static_cast<const T*>(a.u)[gi]);
-        const float zg = a.z ? to_f32(static_cast<const T*>(a.z)[gi]) : 0.f;
-        const float du = delta * u;
-        uint64_t p[NS / 2];
-        dec.factors(delta, p);
-        const uint64_t du2 = pair_f32(du, du);
-        const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
-        const ulonglong2* cp = reinterpret_cast<const ulonglong2*>(csm + t * NS);
-        uint64_t acc0 = pair_f32(0.f, 0.f), acc1 = pair_f32(0.f, 0.f);
+    const int64_t g0 = ((int64_t)b * S + t0) * I + i;
+#pragma unroll 1
+    for (int tb = 0; tb < nt; tb += PFO) {
+        T draw[PFO], uraw[PFO], zraw[PFO];
 #pragma unroll
-        for (int k = 0; k < NS / 4; ++k) {
-            const ulonglong2 bv = bp[k], cv = cp[k];
-            h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
-            h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
-            acc0 = fma2(h[2 * k], cv.x, acc0);
-            acc1 = fma2(h[2 * k + 1], cv.y, acc1);
+        for (int j = 0; j < PFO; ++j) {
+            const int64_t gi = g0 + (int64_t)min(tb + j, nt - 1) * I;
+            draw[j] = static_cast<const T*>(a.delta)[gi];
+            uraw[j] = static_cast<const T*>(a.u)[gi];
+            if (a.z) zraw[j] = static_cast<const T*>(a.z)[gi];
         }
-        float s0, s1, s2, s3;
-        unpair(acc0, s0, s1);
-        unpair(acc1, s2, s3);
-        float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
-        if (a.z) y *= silu_f32(zg);
-        if (active) static_cast<T*>(a.y)[gi] = from_f32<T>(y);
+#pragma unroll
+        for (int j = 0; j < PFO; ++j) {
+            if (tb + j < nt) {
+                float delta = to_f32(draw[j]);
+                if (a.delta_softplus) delta = softplus_stock(delta + dbias);
+                const float u = to_f32(uraw[j]);
+                const float du = delta * u;
+                uint64_t p[NS / 2];
+                dec.factors(delta, p);
+                const uint64_t du2 = pair_f32(du, du);
+                const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + (tb + j) * NS);
+                const ulonglong2* cp = reinterpret_cast<const ulonglong2*>(csm + (tb + j) * NS);
+                uint64_t acc0 = pair_f32(0.f, 0.f), acc1 = pair_f32(0.f, 0.f);
+#pragma unroll
+                for (int k = 0; k < NS / 4; ++k) {
+                    const ulonglong2 bv = bp[k], cv = cp[k];
+                    h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+                    h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+                    acc0 = fma2(h[2 * k], cv.x, acc0);
+                    acc1 = fma2(h[2 * k + 1], cv.y, acc1);
+                }
+                float s0, s1, s2, s3;
+                unpair(acc0, s0, s1);
+                unpair(acc1, s2, s3);
+                float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
+                if (a.z) y *= silu_fast(to_f32(zraw[j]));
+                if (active) static_cast<T*>(a.y)[g0 + (int64_t)(tb + j) * I] = from_f32<T>(y);
+            }
+        }
     }
     if (active && seg == nseg - 1) {
         float* hf = a.h_final + ((int64_t)b * I + i) * NS;

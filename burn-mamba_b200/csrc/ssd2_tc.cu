@@ -94,7 +94,13 @@ struct alignas(64) Params {
     int* status;
     long long* trace;
     int B, S, H, G, Q, NC, tiles_per_unit, num_units;
-    int stall_loads;        // test hook: the TMA producer issues nothing, so the first wait runs out
+    int stall_loads;
+    // Mamba-3 cores (kMode 1): S counts fused (time x rank) rows, St time steps, rows per step = 1 << log2m;
+    // `dt` holds the column scale (NULL = 1, the generic core), `da` the per-step log decay, `gamma` the same-step
+    // weight (NULL = 1)
+    const float* da;
+    const float* gamma;
+    int St, log2m;        // test hook: the TMA producer issues nothing, so the first wait runs out
 };
 
 // Optional timeline instrumentation (development builds only, -DBM_SSD2_TRACE): CTA 0 records
@@ -200,6 +206,29 @@ __device__ __forceinline__ void mask_block(const uint32_t (&r)[32], uint32_t (&o
     }
 }
 
+// Diagonal block of the Mamba-3 cores (src/mamba3/single_ssd/ssd/serial.rs:216-258): rows and columns are fused
+// (time, rank) indices, 1 << log2m per time step.  A column of an earlier step takes the decay kernel times
+// its column scale, a column of the same step (any rank, also above the diagonal) takes the same-step weight,
+// later steps are cut.  Factored form: the column scale and the decay are in Xw and in the epilogue's row
+// factor, so the same-step entries carry rho = gamma / scale instead.
+__device__ __forceinline__ void mask_block_m3(const uint32_t (&r)[32], uint32_t (&out)[16], bool factored, int c, int lane,
+                                              int log2m, float ct, float same, const float* cum2, const float* dtv) {
+    const int tr = lane >> log2m;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        float f[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int col = 2 * j + e, tc_ = col >> log2m;
+            float w = 0.f;
+            if (tc_ == tr) w = same;
+            else if (tc_ < tr) w = factored ? 1.f : ex2(ct - cum2[c * 32 + col]) * dtv[c * 32 + col];
+            f[e] = w;
+        }
+        out[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * f[0], __uint_as_float(r[2 * j + 1]) * f[1]);
+    }
+}
+
 // clamp(softplus(x)) of the fused dt path (src/mamba2/mamba2.rs:692-697); out of line: rarely used
 __device__ __noinline__ float dt_activation(float x, float lo, float hi) { return fminf(fmaxf(softplus_f32(x), lo), hi); }
 
@@ -245,6 +274,9 @@ __device__ __noinline__ void drain_after_timeout(Barriers* bars, int warp, int l
     }
 }
 
+// kMode 0: Mamba-2.  kMode 1: the Mamba-3 cores on the fused (time x rank) axis (single-pass core with column
+// scale and same-step weight, or the generic core with both equal to one).
+template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_constant__ Params prm) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte aligned base, formed as an offset on the __shared__ array so that the compiler keeps the
@@ -411,14 +443,27 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // totals, and the per-token factors follow.  The dt values of a tile are fetched one tile ahead
         // (four loads per lane, issued together), so the global-memory latency is hidden behind the tile before.
         TileWalk tw(tpu, prm.H), twn(tpu, prm.H);
-        float nv[4];
+        float nv[4], nda[4];
         auto fetch = [&](const TileWalk& w) {
-            const float* row = prm.dt + ((int64_t)w.b * prm.S + w.i * T) * prm.H + w.h;
             const int left = prm.S - w.i * T;
+            if (kMode == 0) {
+                const float* row = prm.dt + ((int64_t)w.b * prm.S + w.i * T) * prm.H + w.h;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int t = lane * 4 + k;
-                nv[k] = t < left ? row[(int64_t)t * prm.H] : 0.f;
+                for (int k = 0; k < 4; ++k) {
+                    const int t = lane * 4 + k;
+                    nv[k] = t < left ? row[(int64_t)t * prm.H] : 0.f;
+                }
+            } else {
+                // fused row -> time step; the step's decay enters at its first rank, so that every rank of a
+                // step sees the cumulative decay including that step
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int rrow = w.i * T + lane * 4 + k;
+                    const int64_t o = ((int64_t)w.b * prm.St + (rrow >> prm.log2m)) * prm.H + w.h;
+                    const bool live = lane * 4 + k < left;
+                    nv[k] = live ? (prm.dt ? prm.dt[o] : 1.f) : 0.f;
+                    nda[k] = (live && (rrow & ((1 << prm.log2m) - 1)) == 0) ? prm.da[o] : 0.f;
+                }
             }
         };
         if (total > 0) fetch(twn);
@@ -427,8 +472,8 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const int cst = (it & (kCumStages - 1));
             float* cum2 = reinterpret_cast<float*>(smem + kOffCum + cst * kCumStageBytes);
             float *dtv = cum2 + kCumDt, *wv = cum2 + kCumW, *colf = cum2 + kCumColf;
-            const float ah = prm.a[h] * log2e;
-            const float bias = prm.dt_bias ? prm.dt_bias[h] : 0.f;
+            const float ah = kMode == 0 ? prm.a[h] * log2e : log2e;
+            const float bias = (kMode == 0 && prm.dt_bias) ? prm.dt_bias[h] : 0.f;
             const int left = prm.S - i * T;      // tokens of the sequence from the start of this tile on
             float d4[4], c4[4];
             float run = 0.f;
@@ -437,10 +482,14 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             for (int k = 0; k < 4; ++k) {
                 float v = nv[k];
                 const bool live = lane * 4 + k < left;
-                if (prm.dt_bias && live) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
-                zero |= live && !(v > 0.f);
+                if (kMode == 0) {
+                    if (prm.dt_bias && live) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
+                    zero |= live && !(v > 0.f);
+                    run = fmaf(v, ah, run);
+                } else {
+                    run = fmaf(nda[k], ah, run);
+                }
                 d4[k] = v;
-                run = fmaf(v, ah, run);
                 c4[k] = run;
             }
             twn.next();
@@ -467,7 +516,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 dtv[t] = d4[k];
                 wv[t] = w;
                 colf[t] = d4[k] * ex2(cend_blk - c);
-                weak |= (t < left) && !(w >= kFactoredMinRowWeight);
+                if (kMode == 0) weak |= (t < left) && !(w >= kFactoredMinRowWeight);
             }
             // the factored form divides by the row weight w_t (the D x term): a tile with a live row whose
             // weight is zero, denormal or merely tiny takes the exact form
@@ -500,6 +549,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const float ct = cum2[t];
             const bool factored = cum2[kCumFlag] != 0.f;
             const uint32_t cb = lane_addr + kColCB + st * 128;
+            float same = 1.f;   // Mamba-3: weight of the same-step block for this row
+            if (kMode == 1 && prm.gamma != nullptr) {
+                const int rrow = tw.i * T + t;
+                const float gam = rrow < prm.S ? prm.gamma[((int64_t)tw.b * prm.St + (rrow >> prm.log2m)) * prm.H + tw.h] : 0.f;
+                const float sc = dtv[t];
+                same = factored ? (sc > 0.f ? gam / sc : 0.f) : gam;
+            }
             // blocks 0..q carry data (block q holds the diagonal), blocks above are zero
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -508,7 +564,8 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     uint32_t r[32];
                     tmem_ld32(cb + c * 32, r);
                     tmem_wait_ld();
-                    mask_block(r, out, factored, c == q, c, ct, cum2, dtv, colf, causal);
+                    if (kMode == 1 && c == q) mask_block_m3(r, out, factored, c, lane, prm.log2m, ct, same, cum2, dtv);
+                    else mask_block(r, out, factored, kMode == 0 && c == q, c, ct, cum2, dtv, colf, causal);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) out[j] = 0u;
@@ -848,13 +905,154 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     // that a bounded wait runs out and the error path can be exercised
     prm.stall_loads = (a->reserved == BM_DEBUG_STALL_LOADS) ? 1 : 0;
     {
-        cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd2_tc_kernel)");
     }
     if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, 256, stream), "cudaMemsetAsync(status)")) return e;
     const int grid = prm.num_units < num_sms() ? prm.num_units : num_sms();
-    ssd2_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(prm);
+    ssd2_tc_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(prm);
     return check_launch("ssd2_tc_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Mamba-3 cores on the same kernel
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// Data-dependent rotation of B and C (src/mamba3/rotation/mod.rs:653-679, src/modules/misc/rope.rs:50-170) as a
+// pre-pass of the tensor-core path: raw bf16 B / C [b, s, m, h, r] + cumulative angles [b, s, h, a] -> rotated
+// bf16 copies.  One thread per (b, s, h, group of 8 pairs): 16-byte loads and stores, cos / sin of the wrapped
+// angles shared by B, C and all ranks.  Pairs are (2j, 2j+1) when `pairwise`, else (j, j + r/2); only the first
+// rope_dim / 2 pairs rotate.
+__device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float (&cs)[8], const float (&sn)[8], bool pairwise) {
+    uint32_t* l = &lo.x;
+    uint32_t* h = &hi.x;
+    if (pairwise) {   // lo, hi hold 16 consecutive elements: pair j is the two halves of word j
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t& w = j < 4 ? l[j] : h[j - 4];
+            const float2 f = unpack_bf16x2(w);
+            w = pack_bf16x2(cs[j] * f.x - sn[j] * f.y, sn[j] * f.x + cs[j] * f.y);
+        }
+    } else {          // lo holds elements j0 .. j0+7 of the first half, hi the same positions of the second half
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2) {
+            const float2 a = unpack_bf16x2(l[j2]), b = unpack_bf16x2(h[j2]);
+            l[j2] = pack_bf16x2(cs[2 * j2] * a.x - sn[2 * j2] * b.x, cs[2 * j2 + 1] * a.y - sn[2 * j2 + 1] * b.y);
+            h[j2] = pack_bf16x2(sn[2 * j2] * a.x + cs[2 * j2] * b.x, sn[2 * j2 + 1] * a.y + cs[2 * j2 + 1] * b.y);
+        }
+    }
+}
+
+__global__ void rotate_bc_kernel(const __nv_bfloat16* __restrict__ bsrc, const __nv_bfloat16* __restrict__ csrc,
+                                 const float* __restrict__ angles, __nv_bfloat16* __restrict__ bdst,
+                                 __nv_bfloat16* __restrict__ cdst, int64_t rows, int M, int H, int Rk, int rope_dim, int pairwise) {
+    const int half = Rk / 2, na = rope_dim / 2, ngrp = half / 8;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // (b s, h, group of 8 pairs), groups fastest
+    if (idx >= rows * H * ngrp) return;
+    const int j0 = (idx % ngrp) * 8, h = (idx / ngrp) % H;
+    const int64_t bs = idx / ((int64_t)ngrp * H);
+    float cs[8], sn[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        cs[j] = 1.f, sn[j] = 0.f;
+        if (j0 + j < na) __sincosf(wrap_angle(angles[(bs * H + h) * na + j0 + j]), &sn[j], &cs[j]);
+    }
+    const int o_lo = pairwise ? 2 * j0 : j0, o_hi = pairwise ? 2 * j0 + 8 : j0 + half;
+    for (int m = 0; m < M; ++m) {
+        const int64_t o = ((bs * M + m) * H + h) * Rk;
+        uint4 bl = *reinterpret_cast<const uint4*>(bsrc + o + o_lo), bh = *reinterpret_cast<const uint4*>(bsrc + o + o_hi);
+        uint4 cl = *reinterpret_cast<const uint4*>(csrc + o + o_lo), ch = *reinterpret_cast<const uint4*>(csrc + o + o_hi);
+        rotate8(bl, bh, cs, sn, pairwise != 0);
+        rotate8(cl, ch, cs, sn, pairwise != 0);
+        *reinterpret_cast<uint4*>(bdst + o + o_lo) = bl;
+        *reinterpret_cast<uint4*>(bdst + o + o_hi) = bh;
+        *reinterpret_cast<uint4*>(cdst + o + o_lo) = cl;
+        *reinterpret_cast<uint4*>(cdst + o + o_hi) = ch;
+    }
+}
+
+int log2_exact(int v) {
+    int l = 0;
+    while ((1 << l) < v) ++l;
+    return (1 << l) == v ? l : -1;
+}
+
+}  // namespace
+
+const char* ssd3_why_not(const bm_ssd3_fwd_args* a) {
+    if (a->dtype != BM_DTYPE_BF16) return "activations must be bf16";
+    if (a->headdim != P) return "headdim must be 64";
+    if (a->state_rank != R) return "state_rank must be 128";
+    if (log2_exact(a->mimo_rank) < 0 || a->mimo_rank > 4) return "mimo_rank must be 1, 2 or 4";
+    return nullptr;
+}
+
+bool ssd3_supported(const bm_ssd3_fwd_args* a) { return ssd3_why_not(a) == nullptr; }
+
+size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a) {
+    size_t n = 256 + 7 * 64 * 4 * 8;
+    if (a->angles != nullptr)   // rotated copies of B and C
+        n = align_up(n, 256) + 2 * align_up((size_t)a->batch * a->seqlen * a->mimo_rank * a->nheads * a->state_rank * 2, 256);
+    return n;
+}
+
+int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (workspace == nullptr || workspace_bytes < ssd3_workspace_bytes(a))
+        return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes,
+                    ssd3_workspace_bytes(a));
+    const void* bsrc = a->b;
+    const void* csrc = a->c;
+    if (a->angles != nullptr) {
+        const size_t each = align_up((size_t)a->batch * a->seqlen * a->mimo_rank * a->nheads * a->state_rank * 2, 256);
+        char* base = static_cast<char*>(workspace) + align_up(256 + 7 * 64 * 4 * 8, 256);
+        const int64_t rows = (int64_t)a->batch * a->seqlen;
+        const int64_t total = rows * a->nheads * (a->state_rank / 16);
+        rotate_bc_kernel<<<(unsigned)cdiv(total, 256), 256, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(a->b), static_cast<const __nv_bfloat16*>(a->c), a->angles,
+            reinterpret_cast<__nv_bfloat16*>(base), reinterpret_cast<__nv_bfloat16*>(base + each), rows, a->mimo_rank,
+            a->nheads, a->state_rank, a->rope_dim, a->mimo_rank == 1 ? 1 : 0);
+        if (int32_t e = check_launch("rotate_bc_kernel")) return e;
+        bsrc = base;
+        csrc = base + each;
+    }
+    Params prm{};
+    const char* err = nullptr;
+    const uint64_t S = (uint64_t)a->seqlen * a->mimo_rank, H = a->nheads, B = a->batch;
+    const uint32_t box[4] = {64, 1, (uint32_t)T, 1};
+    {
+        const uint64_t dims[4] = {(uint64_t)P, H, S, B};
+        const uint64_t strides[3] = {(uint64_t)P * 2, H * P * 2, S * H * P * 2};
+        const uint32_t box_y[4] = {32, 1, 32, 1};
+        if (!make_tensor_map_bf16(&prm.tm_x, a->v, 4, dims, strides, box, 128, &err) ||
+            !make_tensor_map_bf16(&prm.tm_y, a->y, 4, dims, strides, box_y, 64, &err))
+            return fail(BM_ERR_CUDA, "tensor map (v/y): %s", err);
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)R, H, S, B};   // B / C are per head: one group per head
+        const uint64_t strides[3] = {(uint64_t)R * 2, H * R * 2, S * H * R * 2};
+        if (!make_tensor_map_bf16(&prm.tm_b, bsrc, 4, dims, strides, box, 128, &err) ||
+            !make_tensor_map_bf16(&prm.tm_c, csrc, 4, dims, strides, box, 128, &err))
+            return fail(BM_ERR_CUDA, "tensor map (b/c): %s", err);
+    }
+    prm.dt = single ? a->scale : nullptr, prm.da = a->da, prm.gamma = single ? a->gamma : nullptr;
+    prm.a = nullptr, prm.d = nullptr, prm.h0 = a->h0, prm.dt_bias = nullptr;
+    prm.h_final = a->h_final, prm.chunk_states = nullptr;
+    prm.status = static_cast<int*>(workspace);
+    prm.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256);
+    prm.B = a->batch, prm.S = (int)S, prm.St = a->seqlen, prm.log2m = log2_exact(a->mimo_rank);
+    prm.H = a->nheads, prm.G = a->nheads, prm.Q = T, prm.NC = 1;
+    prm.tiles_per_unit = (int)cdiv((int64_t)S, T);
+    prm.num_units = a->batch * a->nheads;
+    prm.stall_loads = 0;
+    {
+        cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+        if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd3 tensor kernel)");
+    }
+    if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, 256, stream), "cudaMemsetAsync(status)")) return e;
+    const int grid = prm.num_units < num_sms() ? prm.num_units : num_sms();
+    ssd2_tc_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(prm);
+    return check_launch("ssd3 tensor kernel");
 }
 
 }  // namespace tc

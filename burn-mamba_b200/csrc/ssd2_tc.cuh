@@ -20,5 +20,14 @@ bool ssd2_pair_preferred(const bm_ssd2_fwd_args* a);
 size_t ssd2_pair_workspace_bytes(const bm_ssd2_fwd_args* a);
 int32_t ssd2_pair_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+
+// The Mamba-3 cores (single-pass with gamma / scale, or the generic core) on the one-head-per-CTA kernel, over the
+// fused (time x rank) axis.  bf16, headdim 64, state_rank 128, MIMO rank 1, 2 or 4.  When `angles` is given, B and C
+// are rotated by a pre-pass into the workspace.
+bool ssd3_supported(const bm_ssd3_fwd_args* a);
+const char* ssd3_why_not(const bm_ssd3_fwd_args* a);
+size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a);
+int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 }  // namespace tc
 }  // namespace bm

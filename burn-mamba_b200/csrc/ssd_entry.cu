@@ -118,7 +118,10 @@ static int32_t validate_ssd3(const bm_ssd3_fwd_args* a, bool single) {
                    "rope_dim must be even and <= state_rank");
         BM_REQUIRE(a->state_rank % 2 == 0, BM_ERR_BAD_SHAPE, "state_rank must be even when rotating");
     }
-    BM_REQUIRE(a->path < BM_PATH_TENSOR, BM_ERR_UNSUPPORTED, "no tensor-core path for the Mamba-3 SSD yet");
+    BM_REQUIRE(a->path >= BM_PATH_AUTO && a->path <= BM_PATH_TENSOR_SINGLE, BM_ERR_UNSUPPORTED,
+               "path must be auto, exact or tensor (the Mamba-3 cores have no paired kernel: B and C are per head)");
+    if (a->path >= BM_PATH_TENSOR && !tc::ssd3_supported(a))
+        return fail(BM_ERR_UNSUPPORTED, "tensor-core SSD path does not cover this shape/dtype: %s", tc::ssd3_why_not(a));
     return BM_OK;
 }
 
@@ -138,21 +141,28 @@ static exact::Params ssd3_exact_params(const bm_ssd3_fwd_args* a, bool single) {
     return p;
 }
 
+static bool ssd3_use_tensor(const bm_ssd3_fwd_args* a) { return a->path != BM_PATH_EXACT && tc::ssd3_supported(a); }
+
 extern "C" size_t bm_ssd3_fwd_workspace_bytes(const bm_ssd3_fwd_args* a) {
     if (a == nullptr || a->batch <= 0 || a->seqlen <= 0 || a->nheads <= 0 || a->chunk_len <= 0) return 0;
+    if (ssd3_use_tensor(a)) return tc::ssd3_workspace_bytes(a);
     return exact::workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, true);
 }
 
-extern "C" int32_t bm_ssd3_single_fwd(const bm_ssd3_fwd_args* a, void* ws, size_t ws_bytes, void* stream) {
+static int32_t ssd3_fwd(const bm_ssd3_fwd_args* a, bool single, void* ws, size_t ws_bytes, void* stream) {
     clear_error();
-    if (int32_t e = validate_ssd3(a, true)) return e;
-    return exact::run(ssd3_exact_params(a, true), ws, ws_bytes, static_cast<cudaStream_t>(stream));
+    if (int32_t e = validate_ssd3(a, single)) return e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (ssd3_use_tensor(a)) return tc::ssd3_run(a, single, ws, ws_bytes, st);
+    return exact::run(ssd3_exact_params(a, single), ws, ws_bytes, st);
+}
+
+extern "C" int32_t bm_ssd3_single_fwd(const bm_ssd3_fwd_args* a, void* ws, size_t ws_bytes, void* stream) {
+    return ssd3_fwd(a, true, ws, ws_bytes, stream);
 }
 
 extern "C" int32_t bm_ssd3_double_fwd(const bm_ssd3_fwd_args* a, void* ws, size_t ws_bytes, void* stream) {
-    clear_error();
-    if (int32_t e = validate_ssd3(a, false)) return e;
-    return exact::run(ssd3_exact_params(a, false), ws, ws_bytes, static_cast<cudaStream_t>(stream));
+    return ssd3_fwd(a, false, ws, ws_bytes, stream);
 }
 
 extern "C" int32_t bm_workspace_status(const void* workspace, void* stream) {

@@ -134,9 +134,11 @@ __global__ void conv_step_kernel(bm_conv_step_args a) {
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)a.batch * a.channels) return;
     const int v = idx % a.channels, K = a.kernel;
+    const int64_t b = idx / a.channels;
     float* win = a.window + idx * K;
     const float* w = a.weight + (int64_t)v * K;
-    const float xn = to_f32(static_cast<const T*>(a.xin)[idx]);
+    const int64_t xs = a.xin_stride > 0 ? a.xin_stride : a.channels;
+    const float xn = to_f32(static_cast<const T*>(a.xin)[b * xs + v]);
     float acc = a.bias ? a.bias[v] : 0.f;
     if (K == 4) {
         float4 wv = ld4(win), ww = ld4(w);
@@ -150,7 +152,16 @@ __global__ void conv_step_kernel(bm_conv_step_args a) {
             acc = fmaf(val, w[k], acc);
         }
     }
-    static_cast<T*>(a.out)[idx] = from_f32<T>(silu_f32(acc));
+    const T o = from_f32<T>(silu_f32(acc));
+    if (a.out_b == nullptr) {
+        static_cast<T*>(a.out)[idx] = o;
+    } else if (v < a.split_x) {   // the three tensors the state step reads: x [b, split_x], B / C [b, split_bc]
+        static_cast<T*>(a.out)[b * a.split_x + v] = o;
+    } else if (v < a.split_x + a.split_bc) {
+        static_cast<T*>(a.out_b)[b * a.split_bc + (v - a.split_x)] = o;
+    } else {
+        static_cast<T*>(a.out_c)[b * a.split_bc + (v - a.split_x - a.split_bc)] = o;
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -394,6 +405,13 @@ extern "C" int32_t bm_conv_step(const bm_conv_step_args* a, void* stream) {
     BM_REQUIRE_PTR(a->weight);
     BM_REQUIRE_PTR(a->out);
     BM_OPTIONAL_PTR(a->bias);
+    BM_REQUIRE(a->xin_stride == 0 || a->xin_stride >= a->channels, BM_ERR_BAD_SHAPE, "xin_stride must be 0 (dense) or >= channels");
+    if (a->out_b != nullptr || a->out_c != nullptr) {
+        BM_REQUIRE_PTR(a->out_b);
+        BM_REQUIRE_PTR(a->out_c);
+        BM_REQUIRE(a->split_x > 0 && a->split_bc > 0 && a->split_x + 2 * a->split_bc == a->channels, BM_ERR_BAD_SHAPE,
+                   "split_x + 2 split_bc must equal channels");
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int64_t total = (int64_t)a->batch * a->channels;
     if (a->dtype == BM_DTYPE_F32) conv_step_kernel<float><<<(unsigned)cdiv(total, 256), 256, 0, st>>>(*a);

@@ -105,6 +105,8 @@ class Mamba2:
         self.per_head_dim = self.d_inner // nheads
         self.conv_dim, self.conv_kernel = conv_w.shape
         self.dt_limit, self.norm_before_gate = dt_limit, norm_before_gate
+        self._conv_w32, self._conv_b32 = conv_w.float().contiguous(), conv_b.float().contiguous()
+        self._a = -torch.exp(self.a_log)
         assert self.conv_dim == self.d_inner + 2 * ngroups * state_rank
         assert nheads % ngroups == 0
 
@@ -131,12 +133,12 @@ class Mamba2:
         # window slide + causal depthwise conv + bias + SiLU in one kernel, reading xbc in place from the
         # projection's columns and writing x, B, C as the three dense tensors the SSD takes
         gr = self.ngroups * self.state_rank
-        (x, bm, cm), new_conv = ops.conv1d_silu_fwd(xbc, self.conv_w.float(), self.conv_b.float(), cache.conv_bvk,
+        (x, bm, cm), new_conv = ops.conv1d_silu_fwd(xbc, self._conv_w32, self._conv_b32, cache.conv_bvk,
                                                     splits=(self.d_inner, gr, gr))
         x = x.view(bsz, s, self.nheads, self.per_head_dim)
         bm = bm.view(bsz, s, self.ngroups, self.state_rank)
         cm = cm.view(bsz, s, self.ngroups, self.state_rank)
-        a = -torch.exp(self.a_log)
+        a = self._a
         chunk_len = ssd_path.chunk_len_or_optimal(self.state_rank, self.per_head_dim)
         # softplus(dt_raw + dt_bias) and the clamp are fused into the SSD's decay scan; the tail chunk is
         # handled inside the kernel (dt = 0 padding semantics), so no explicit pad / unpad here
@@ -145,37 +147,38 @@ class Mamba2:
         out = self._gated_norm(y.reshape(bsz, s, self.d_inner), z) @ self.w_out
         return out, Mamba2Cache(new_conv, hf)
 
-    def step(self, input_bm, cache: Optional[Mamba2Cache] = None):
+    def step(self, input_bm, cache: Optional[Mamba2Cache] = None, residual=None):
         """Mamba2::step (src/mamba2/mamba2.rs:820-1004) -> (out_bm, cache).  The cache tensors are updated
-        in place by the kernels and returned."""
+        in place by the kernels and returned.  `residual` (the layer's skip connection) is added to the output
+        inside the out-projection GEMM when given."""
         bsz = input_bm.shape[0]
         cache = cache or self.zero_cache(bsz)
         proj = input_bm @ self.w_in
         z, xbc, dt_raw = torch.split(proj, [self.d_inner, self.conv_dim, self.nheads], dim=1)
-        xbc_act = ops.conv_step(cache.conv_bvk, xbc.contiguous(), self.conv_w.float(), self.conv_b.float())
+        # window slide + conv + SiLU, reading xbc in place and writing x / B / C as the step's three dense inputs
         gr = self.ngroups * self.state_rank
-        x, bm, cm = torch.split(xbc_act, [self.d_inner, gr, gr], dim=1)
-        x = x.reshape(bsz, self.nheads, self.per_head_dim).contiguous()
-        bm = bm.reshape(bsz, self.ngroups, self.state_rank).contiguous()
-        cm = cm.reshape(bsz, self.ngroups, self.state_rank).contiguous()
-        y = ops.step2(cache.ssm_bhpr, x, dt_raw.float().contiguous(), -torch.exp(self.a_log), bm, cm, self.d,
+        x, bm, cm = ops.conv_step(cache.conv_bvk, xbc, self._conv_w32, self._conv_b32, splits=(self.d_inner, gr, gr))
+        y = ops.step2(cache.ssm_bhpr, x.view(bsz, self.nheads, self.per_head_dim), dt_raw.float().contiguous(), self._a,
+                      bm.view(bsz, self.ngroups, self.state_rank), cm.view(bsz, self.ngroups, self.state_rank), self.d,
                       dt_bias=self.dt_bias, dt_limit=self.dt_limit)
-        out = self._gated_norm(y.reshape(bsz, self.d_inner), z) @ self.w_out
+        g = self._gated_norm(y.reshape(bsz, self.d_inner), z)
+        out = g @ self.w_out if residual is None else torch.addmm(residual, g, self.w_out)
         return out, cache
 
 
 def rms_norm(x, gamma):
-    """RmsNorm (src/modules/norm/rms_norm.rs:53-98): x / sqrt(mean(x^2) + eps) * gamma."""
-    eps = DIV_EPS.get(x.dtype, DIV_EPS[torch.float32])
-    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * gamma
+    """RmsNorm (src/modules/norm/rms_norm.rs:53-98): x / sqrt(mean(x^2) + eps) * gamma, one kernel."""
+    return ops.rmsnorm_gated(x, None, gamma.to(x.dtype))
 
 
 def stack_step(blocks, norm_gammas, caches, x_bm):
     """One decode step through a stack of pre-norm residual layers, the default (no class latents, plain
     residual) path of Layers::step / Layer::step_one (src/modules/layers.rs:427-497,
     src/modules/layer.rs:224-229): x <- x + block.step(norm(x)).  `caches` is one Mamba2Cache per layer,
-    updated in place.  Returns the output of the last layer [b, d_model]."""
+    updated in place.  Returns the output of the last layer [b, d_model].  Per layer this is seven launches
+    (norm, in-projection, conv step, state step, gated norm, out-projection with the residual folded in as the
+    GEMM's addend, plus the dt cast); none of them depends on the host, so the whole step can be replayed from a
+    CUDA graph."""
     for blk, gamma, cache in zip(blocks, norm_gammas, caches):
-        h1, _ = blk.step(rms_norm(x_bm, gamma), cache)
-        x_bm = x_bm + h1
+        x_bm = blk.step(rms_norm(x_bm, gamma), cache, residual=x_bm)[0]
     return x_bm

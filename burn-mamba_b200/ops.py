@@ -109,16 +109,28 @@ def step2(state, x, dt, a, b, c, d=None, dt_bias=None, dt_limit=(0.0, 65504.0), 
     return y
 
 
-def conv_step(window, xin, weight, bias=None):
-    """Causal depthwise conv, one token: slides `window` [b,v,k] f32 in place, returns silu(conv) [b,v]."""
+def conv_step(window, xin, weight, bias=None, splits=None):
+    """Causal depthwise conv, one token: slides `window` [b,v,k] f32 in place, returns silu(conv) [b,v] -- or, with
+    splits = (split_x, split_bc, split_bc), the three tensors (x [b,split_x], B, C [b,split_bc]).  `xin` [b,v] may be
+    a column slice of a wider row."""
     bsz, v, k = window.shape
-    _chk(window, "window", torch.float32); _chk(xin, "xin", None, (bsz, v))
+    _chk(window, "window", torch.float32)
+    if not xin.is_cuda or tuple(xin.shape) != (bsz, v) or xin.stride(1) != 1:
+        raise ValueError("xin must be a CUDA tensor [b, v] with a contiguous last axis")
     _chk(weight, "weight", torch.float32, (v, k)); _chk(bias, "bias", torch.float32, (v,), optional=True)
-    out = torch.empty_like(xin)
-    args = _ffi.ConvStepArgs(batch=bsz, channels=v, kernel=k, dtype=_DT[xin.dtype], window=_ptr(window),
-                             xin=_ptr(xin), weight=_ptr(weight), bias=_ptr(bias), out=_ptr(out))
+    act = xin.dtype
+    if splits is None:
+        outs, sx, sbc = (torch.empty((bsz, v), dtype=act, device=xin.device), None, None), 0, 0
+    else:
+        sx, sbc, sbc2 = splits
+        if sbc != sbc2 or sx + 2 * sbc != v:
+            raise ValueError("splits must be (split_x, split_bc, split_bc) summing to the channel count")
+        outs = tuple(torch.empty((bsz, n), dtype=act, device=xin.device) for n in (sx, sbc, sbc))
+    args = _ffi.ConvStepArgs(batch=bsz, channels=v, kernel=k, dtype=_DT[act], window=_ptr(window), xin=xin.data_ptr(),
+                             weight=_ptr(weight), bias=_ptr(bias), out=_ptr(outs[0]), out_b=_ptr(outs[1]),
+                             out_c=_ptr(outs[2]), xin_stride=xin.stride(0), split_x=sx, split_bc=sbc, reserved=0)
     check(lib.bm_conv_step(C.byref(args), _stream()), "bm_conv_step")
-    return out
+    return outs[0] if splits is None else outs
 
 
 DIV_EPS = {torch.float32: 8.1584695e-8, torch.bfloat16: 2.0885676e-5}   # src/utils/mod.rs:50-95
@@ -231,7 +243,10 @@ def step1(state, u, delta, a, b, c, d=None, z=None, delta_bias=None, delta_softp
     return y
 
 
-def _ssd3(fn_name, v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, path):
+SSD3_TENSOR_PATH = True   # bm_ssd3_*_fwd have a tensor-core path (bf16, P 64, N 128, MIMO rank 1 / 2 / 4)
+
+
+def _ssd3(fn_name, v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, path, check_status=False):
     bsz, s, m, h, p = v.shape
     r = b.shape[-1]
     act = v.dtype
@@ -250,17 +265,19 @@ def _ssd3(fn_name, v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, p
     nbytes = lib.bm_ssd3_fwd_workspace_bytes(C.byref(args))
     ws = _workspace(nbytes, v.device)
     check(getattr(lib, fn_name)(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), fn_name)
+    if check_status:
+        check(lib.bm_workspace_status(ws.data_ptr(), _stream()), fn_name + " (device status)")
     return y, h_final
 
 
-def ssd3_single_fwd(v, da, b, c, gamma, scale, h0=None, chunk_len=64, angles=None, rope_dim=0, path="auto"):
+def ssd3_single_fwd(v, da, b, c, gamma, scale, h0=None, chunk_len=64, angles=None, rope_dim=0, path="auto", check_status=False):
     """Mamba-3 single-pass SSD.  v [b,s,m,h,p], da/gamma/scale [b,s,h] f32, b/c [b,s,m,h,r]."""
-    return _ssd3("bm_ssd3_single_fwd", v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, path)
+    return _ssd3("bm_ssd3_single_fwd", v, da, b, c, gamma, scale, h0, chunk_len, angles, rope_dim, path, check_status)
 
 
-def ssd3_double_fwd(v, da, b, c, h0=None, chunk_len=64, angles=None, rope_dim=0, path="auto"):
+def ssd3_double_fwd(v, da, b, c, h0=None, chunk_len=64, angles=None, rope_dim=0, path="auto", check_status=False):
     """Generic MIMO SSD on pre-scaled v (one pass of Mamba-3's double-SSD pathway)."""
-    return _ssd3("bm_ssd3_double_fwd", v, da, b, c, None, None, h0, chunk_len, angles, rope_dim, path)
+    return _ssd3("bm_ssd3_double_fwd", v, da, b, c, None, None, h0, chunk_len, angles, rope_dim, path, check_status)
 
 
 def angle_cumsum(rot, dt, prev=None, rng=2.0):

@@ -203,7 +203,12 @@ typedef struct {
     const void* xin;          /* [b, v] new pre-conv column */
     const float* weight;      /* [v, k] */
     const float* bias;        /* [v] or NULL */
-    void* out;                /* [b, v] = silu(sum_k window * weight + bias) */
+    void* out;                /* [b, v] = silu(sum_k window * weight + bias); [b, split_x] when out_b is given */
+    void* out_b;              /* optional [b, split_bc]: with out_c, the output leaves split along channels as the */
+    void* out_c;              /*   x / B / C tensors bm_step2 reads (split_x + 2 split_bc = v); NULL = one tensor */
+    int32_t xin_stride;       /* elements between batch rows of xin (a column slice of the projection); 0 = dense */
+    int32_t split_x, split_bc;
+    int32_t reserved;
 } bm_conv_step_args;
 
 int32_t bm_conv_step(const bm_conv_step_args* args, void* stream);

@@ -154,13 +154,14 @@ def _c5(seed, batch, seqlen, nheads):
     return cfg
 
 
-def test_ssd3_single_forward_at_the_configured_head_shape_bf16(bm):
-    """H 32, P 64, N 128, m 4, Q 64, L 2048, bf16, rotation fused at load; every head runs on the GPU,
-    four of them are checked against the oracle (heads are independent)."""
+@pytest.mark.parametrize("path", ["tensor", "exact"])
+def test_ssd3_single_forward_at_the_configured_head_shape_bf16(bm, path):
+    """H 32, P 64, N 128, m 4, Q 64, L 2048, bf16, rotation of B / C from the angles; every head runs on the GPU
+    (tensor-core kernel and float32 exact path), three of them are checked against the oracle (heads are independent)."""
     cfg = _c5(4, 1, 2048, 32)
     y, hf = bm.ops.ssd3_single_fwd(dev(cfg["v"], BF), dev(cfg["da"]), dev(cfg["b"], BF), dev(cfg["c"], BF),
                                    dev(cfg["gamma"]), dev(cfg["scale"]), None, chunk_len=64,
-                                   angles=dev(cfg["angles"]), rope_dim=128)
+                                   angles=dev(cfg["angles"]), rope_dim=128, path=path)
     y, hf = host(y), host(hf)
     for h in (0, 13, 31):
         sl = slice(h, h + 1)

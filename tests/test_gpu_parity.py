@@ -458,3 +458,53 @@ def test_ssd2_pair_kernel_refuses_odd_heads_per_group(bm):
     with pytest.raises(bm.BmError) as e:
         bm.ops.ssd2_fwd(t["x"], t["dt"], t["a"], t["b"], t["c"], t["d"], None, chunk_len=128, path="tensor_pair")
     assert e.value.code == bm._ffi.BM_ERR_UNSUPPORTED
+
+
+# ------------------------------------------------------------------ Mamba-3 cores, tensor-core path
+@pytest.mark.parametrize("b,s,h,m,double,fused,strong", [
+    (1, 32, 2, 4, False, True, False),      # one tile of the fused (time x rank) axis
+    (1, 100, 2, 4, False, True, False),     # ragged
+    (1, 100, 2, 4, False, False, False),    # pre-rotated B / C, no angles
+    (2, 300, 2, 1, False, True, False),     # SISO: pairwise rotation, the same-step block is the diagonal
+    (1, 130, 3, 2, False, True, False),
+    (1, 100, 2, 4, True, True, False),      # generic core (one pass of the double-SSD pathway)
+    (1, 200, 2, 1, True, True, False),
+    (1, 128, 2, 4, False, True, True),      # decay beyond the factored form's range: exact mask form
+    (1, 256, 2, 1, False, True, True),
+])
+def test_ssd3_tensor_path_matches_oracle(bm, b, s, h, m, double, fused, strong):
+    """bm_ssd3_single_fwd / bm_ssd3_double_fwd on the tcgen05 kernel (strict-in-time mask over the fused axis, column
+    scale, same-step gamma block; src/mamba3/single_ssd/ssd/serial.rs:156-268, double_ssd/ssd/serial.rs:118-409)."""
+    BF = torch.bfloat16
+    cfg = inputs.ssd3_single(seed=70 + s, batch=b, seqlen=s, nheads=h, headdim=64, state_rank=128, mimo_rank=m, h0_std=0.1)
+    if strong:
+        cfg["da"] = (cfg["da"] * 40).astype(np.float32)
+    v, bb, cc = (bf16_round(cfg[k]) for k in ("v", "b", "c"))
+    ang = cfg["angles"][:, :, None]
+    b_rot = mamba3.apply_rope_partial(bb, ang, 128, m == 1)
+    c_rot = mamba3.apply_rope_partial(cc, ang, 128, m == 1)
+    if double:
+        want_y, want_h = mamba3.double_ssd_serial(v, cfg["da"], b_rot, c_rot, cfg["h0"], 64)
+    else:
+        want_y, want_h = mamba3.single_ssd_serial(v, cfg["da"], b_rot, c_rot, cfg["gamma"], cfg["scale"], cfg["h0"], 64)
+    if fused:
+        a = (dev(v, BF), dev(cfg["da"]), dev(bb, BF), dev(cc, BF))
+        kw = dict(angles=dev(cfg["angles"]), rope_dim=128)
+    else:
+        a = (dev(v, BF), dev(cfg["da"]), dev(bf16_round(b_rot), BF), dev(bf16_round(c_rot), BF))
+        kw = {}
+    if double:
+        y, hf = bm.ops.ssd3_double_fwd(*a, dev(cfg["h0"]), chunk_len=64, path="tensor", check_status=True, **kw)
+    else:
+        y, hf = bm.ops.ssd3_single_fwd(*a, dev(cfg["gamma"]), dev(cfg["scale"]), dev(cfg["h0"]), chunk_len=64, path="tensor",
+                                       check_status=True, **kw)
+    assert torch.isfinite(y.float()).all()
+    assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
+
+
+def test_ssd3_tensor_path_refuses_what_it_does_not_cover(bm):
+    cfg = inputs.ssd3_single(seed=71, batch=1, seqlen=16, nheads=2, headdim=16, state_rank=32, mimo_rank=3)
+    t = {k: dev(cfg[k]) for k in ("v", "da", "b", "c", "gamma", "scale")}
+    with pytest.raises(bm.BmError) as e:
+        bm.ops.ssd3_single_fwd(t["v"], t["da"], t["b"], t["c"], t["gamma"], t["scale"], None, chunk_len=16, path="tensor")
+    assert e.value.code == bm._ffi.BM_ERR_UNSUPPORTED
