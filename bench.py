@@ -448,6 +448,22 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_leg(args):
+    """One leg alone, for profiler captures (rank 0, one GPU): prints that leg's JSON."""
+    import torch
+    import __graft_entry__ as ge
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    bm = ge.load_package()
+    if args.leg == "kernels":
+        out = kernel_legs(torch, bm, dev, iters=3 if args.small else 10, small=args.small)
+    else:
+        out = decode_step_leg(torch, bm, dev, layers=2 if args.small else 64, steps=2 if args.small else 8)
+    print(json.dumps({"leg": args.leg, "small": bool(args.small), "result": out}), flush=True)
+
+
 def replicated_leg(torch, dist, bm, dev, c, params, timed, world):
     """Every rank runs the whole batch-8 problem (independent replicas): the weak-scaling figure."""
     s = Slice(torch, dev, c, (0, c["batch"], 0, c["nheads"]), params)
@@ -516,9 +532,11 @@ def _time_flushed(torch, fn, iters, flush):
     return total / iters
 
 
-def kernel_legs(torch, bm, dev, iters=10):
+def kernel_legs(torch, bm, dev, iters=10, small=False):
     """The other kernels of the path at their configured shapes: device time (CUDA events, L2 flushed between
-    launches), algorithmic bytes or flops, and the fraction of the measured peak that bounds each."""
+    launches), algorithmic bytes or flops, and the fraction of the measured peak that bounds each.  `small` cuts
+    the batch-like axes (profiler captures only; the figures are then not the configured shapes')."""
+    sb = (lambda n, m=1: max(m, n // 8)) if small else (lambda n, m=1: n)
     peak, peak_tf, src = measured_peaks()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     g = torch.Generator(device=dev).manual_seed(3)
@@ -537,24 +555,24 @@ def kernel_legs(torch, bm, dev, iters=10):
                     "frac": tf / peak_tf, "peak": peak_tf, "note": note})
 
     # Mamba-1 selective scan at its configuration (b4 L2048 i1536 N16, bf16, gate through SiLU)
-    b1, L, I, N = 4, 2048, 1536, 16
+    b1, L, I, N = sb(4), 2048, 1536, 16
     u, z = rn(b1, L, I, dt=bf), rn(b1, L, I, dt=bf)
     delta = torch.exp(torch.rand(b1, L, I, device=dev) * 4.6 - 6.9).to(bf)
     a1 = -torch.arange(1, N + 1, device=dev, dtype=torch.float32).repeat(I, 1).contiguous()
     b_, c_, d1 = rn(b1, L, N, dt=bf), rn(b1, L, N, dt=bf), torch.ones(I, device=dev)
     ms = _time_flushed(torch, lambda: bm.ops.selscan1_fwd(u, delta, a1, b_, c_, d1, z=z), iters, flush)
-    hbm("selscan1_fwd (Mamba-1 scan, b4 L2048 i1536 N16, bf16)", ms,
+    hbm(f"selscan1_fwd (Mamba-1 scan, b{b1} L2048 i1536 N16, bf16)", ms,
         4 * u.numel() * 2 + 2 * b_.numel() * 2 + a1.numel() * 4 + 2 * b1 * I * N * 4)
 
     # Mamba-3 decode step (b256 H32 P64 N128 m4)
-    B3, H3, M3, P, R = 256, 32, 4, 64, 128
+    B3, H3, M3, P, R = sb(256), 32, 4, 64, 128
     st3, ks, vs_, ang = 0.1 * rn(B3, H3, P, R), rn(B3, M3, H3, R), rn(B3, H3, P), rn(B3, H3, R // 2)
     x3, b3, c3, rot = rn(B3, H3, P), rn(B3, M3, H3, R), rn(B3, M3, H3, R), rn(B3, R // 2)
     sc = lambda: torch.rand(B3, H3, device=dev) * 0.1
     dt3, al, be, ga = sc(), 1 - sc(), sc(), sc()
     mx = torch.full((H3, M3, P), 0.25, device=dev)
     ms = _time_flushed(torch, lambda: bm.ops.step3(st3, ks, vs_, ang, x3, b3, c3, rot, dt3, al, be, ga, mx), iters, flush)
-    hbm("step3 (Mamba-3 decode, b256 H32 P64 N128 m4)", ms,
+    hbm(f"step3 (Mamba-3 decode, b{B3} H32 P64 N128 m4)", ms,
         2 * st3.numel() * 4 + 4 * ks.numel() * 4 + 3 * vs_.numel() * 4 + M3 * vs_.numel() * 4)
     del st3
 
@@ -572,33 +590,33 @@ def kernel_legs(torch, bm, dev, iters=10):
 
     for extra in (_prefill_glue_legs, _ssd3_legs, _ssd2_bwd_leg):
         try:
-            extra(torch, bm, dev, rn, flush, hbm, tensor)
+            extra(torch, bm, dev, rn, flush, hbm, tensor, sb)
         except torch.cuda.OutOfMemoryError:
             out.append({"kernel": extra.__name__, "skipped": "out of device memory"})
         torch.cuda.empty_cache()
     return out
 
 
-def _prefill_glue_legs(torch, bm, dev, rn, flush, hbm, tensor):
+def _prefill_glue_legs(torch, bm, dev, rn, flush, hbm, tensor, sb):
     """Pre-/post-SSD kernels of the Mamba-2 block at the prefill configuration (when the library has them)."""
     bf = torch.bfloat16
     if hasattr(bm.ops, "conv1d_silu_fwd"):
-        b, s, v, k = 8, 4096, 5376, 4
+        b, s, v, k = sb(8), 4096, 5376, 4
         xbc, w, bias, prev = rn(b, s, v, dt=bf), rn(v, k), rn(v), rn(b, v, k)
         ms = _time_flushed(torch, lambda: bm.ops.conv1d_silu_fwd(xbc, w, bias, prev, splits=(5120, 128, 128)), 5, flush)
-        hbm("conv1d_silu_fwd (prefill conv k4 + bias + SiLU, b8 L4096 v5376, bf16)", ms, 2 * xbc.numel() * 2)
+        hbm(f"conv1d_silu_fwd (prefill conv k4 + bias + SiLU, b{b} L4096 v5376, bf16)", ms, 2 * xbc.numel() * 2)
     if hasattr(bm.ops, "rmsnorm_gated"):
-        b, s, i = 8, 4096, 5120
+        b, s, i = sb(8), 4096, 5120
         y, z, gamma = rn(b * s, i, dt=bf), rn(b * s, i, dt=bf), rn(i, dt=bf)
         ms = _time_flushed(torch, lambda: bm.ops.rmsnorm_gated(y, z, gamma), 5, flush)
-        hbm("rmsnorm_gated (b8 L4096 d_inner 5120, bf16)", ms, 3 * y.numel() * 2)
+        hbm(f"rmsnorm_gated (b{b} L4096 d_inner 5120, bf16)", ms, 3 * y.numel() * 2)
 
 
-def _ssd3_legs(torch, bm, dev, rn, flush, hbm, tensor):
+def _ssd3_legs(torch, bm, dev, rn, flush, hbm, tensor, sb):
     """Mamba-3 single SSD forward and recompute backward at the configured shape
     (b16 L2048 H32 P64 N128 m4 Q64, bf16 / float32 state)."""
     bf = torch.bfloat16
-    b, s, m, h, p, r, q = 16, 2048, 4, 32, 64, 128, 64
+    b, s, m, h, p, r, q = sb(16, 2), 2048, 4, 32, 64, 128, 64
     v = rn(b, s, 1, h, p, dt=bf).expand(b, s, m, h, p).contiguous() / m
     bb, cc = rn(b, s, m, h, r, dt=bf) / r ** 0.5, rn(b, s, m, h, r, dt=bf) / r ** 0.5
     dt = torch.rand(b, s, h, device=dev) * 0.05 + 1e-3
@@ -614,7 +632,7 @@ def _ssd3_legs(torch, bm, dev, rn, flush, hbm, tensor):
     path = "tensor" if getattr(bm.ops, "SSD3_TENSOR_PATH", False) else "exact"
     fwd = lambda: bm.ops.ssd3_single_fwd(v, da, bb, cc, gamma, scale, None, chunk_len=q, angles=angles, rope_dim=r, path=path)
     ms = _time_flushed(torch, fwd, 3, flush)
-    tensor(f"ssd3_single_fwd (b16 L2048 H32 P64 N128 m4 Q64, bf16, rotation fused, {path} path)", ms, flops,
+    tensor(f"ssd3_single_fwd (b{b} L2048 H32 P64 N128 m4 Q64, bf16, rotation from angles, {path} path)", ms, flops,
            "dense GEMM count of the fused (time x rank) axis")
     del angles
     dy = rn(b, s, m, h, p, dt=bf)
@@ -623,17 +641,17 @@ def _ssd3_legs(torch, bm, dev, rn, flush, hbm, tensor):
     tensor("ssd3_single_bwd (same shape, recompute backward, pre-rotated B/C)", ms, 2.5 * flops, "2.5 x the forward count")
 
 
-def _ssd2_bwd_leg(torch, bm, dev, rn, flush, hbm, tensor):
+def _ssd2_bwd_leg(torch, bm, dev, rn, flush, hbm, tensor, sb):
     """Mamba-2 recompute backward at the prefill head shape (b2 L4096 H80 P64 N128 G1 Q256, bf16)."""
     bf = torch.bfloat16
-    c = dict(CFG, batch=2)
+    c = dict(CFG, batch=sb(2))
     b, s, h, p, r, q = c["batch"], c["seqlen"], c["nheads"], c["headdim"], c["state_rank"], c["chunk_len"]
     x, dy = rn(b, s, h, p, dt=bf), rn(b, s, h, p, dt=bf)
     dt = torch.rand(b, s, h, device=dev) * 0.05 + 1e-3
     a, d = -(torch.rand(h, device=dev) * 15 + 1), torch.rand(h, device=dev)
     bb, cc = rn(b, s, 1, r, dt=bf) / r ** 0.5, rn(b, s, 1, r, dt=bf) / r ** 0.5
     ms = _time_flushed(torch, lambda: bm.ops.ssd2_bwd(x, dt, a, bb, cc, d, None, dy, None, chunk_len=q), 2, flush)
-    tensor("ssd2_bwd (b2 L4096 H80 P64 N128 G1 Q256, bf16, recompute backward)", ms, 2.5 * algorithmic_flops(c),
+    tensor(f"ssd2_bwd (b{b} L4096 H80 P64 N128 G1 Q256, bf16, recompute backward)", ms, 2.5 * algorithmic_flops(c),
            "2.5 x the forward count")
 
 
@@ -721,9 +739,10 @@ def decode_step_leg(torch, bm, dev, layers=64, batch=256, steps=8):
     return res
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per (batch x head) unit of one ssd2 tensor-core launch, from an
-# ncu capture of the benchmark launch itself (two metrics, one pass); null until such a capture exists
-TRAFFIC_BYTES_PER_UNIT = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one tensor-core launch of the whole benchmark problem (640 units),
+# from an ncu capture of that launch itself: 373.9 MB read + 313.3 MB written (part of y is still dirty in L2 when
+# the kernel ends), per unit
+TRAFFIC_BYTES_PER_UNIT = (373.9e6 + 313.3e6) / 640
 
 
 def traffic_bytes_per_launch(units):
@@ -815,9 +834,14 @@ def main():
     ap.add_argument("--batch", type=int, default=CFG["batch"],
                     help="batch rows of the problem (default: the benchmark configuration; smaller only for profiler captures)")
     ap.add_argument("--profile", action="store_true", help="kernel-only run for ncu: skips every other leg")
+    ap.add_argument("--leg", default="all", choices=["all", "kernels", "decode"],
+                    help="profiler captures: run only the other-kernels leg or only the decode leg (no prefill timing)")
+    ap.add_argument("--small", action="store_true", help="with --leg: cut batch-like axes so that a full-metric ncu capture stays small")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.leg != "all":
+        run_leg(args)
     else:
         run_ours(args)
 

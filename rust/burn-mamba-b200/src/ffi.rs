@@ -6,6 +6,10 @@ pub const BM_OK: i32 = 0;
 pub const BM_DTYPE_F32: i32 = 0;
 pub const BM_DTYPE_BF16: i32 = 1;
 pub const BM_PATH_AUTO: i32 = 0;
+pub const BM_PATH_EXACT: i32 = 1;
+pub const BM_PATH_TENSOR: i32 = 2;
+pub const BM_PATH_TENSOR_SINGLE: i32 = 3;
+pub const BM_PATH_TENSOR_PAIR: i32 = 4;
 
 #[repr(C)]
 pub struct BmSsd2FwdArgs {
@@ -57,6 +61,23 @@ pub struct BmStep2Args {
 pub struct BmConvStepArgs {
     pub batch: i32, pub channels: i32, pub kernel: i32, pub dtype: i32,
     pub window: *mut f32, pub xin: *const c_void, pub weight: *const f32, pub bias: *const f32, pub out: *mut c_void,
+    pub out_b: *mut c_void, pub out_c: *mut c_void,
+    pub xin_stride: i32, pub split_x: i32, pub split_bc: i32, pub reserved: i32,
+}
+
+#[repr(C)]
+pub struct BmConv1dSiluArgs {
+    pub batch: i32, pub seqlen: i32, pub channels: i32, pub kernel: i32, pub dtype: i32, pub xin_stride: i32,
+    pub split_x: i32, pub split_bc: i32,
+    pub xin: *const c_void, pub weight: *const f32, pub bias: *const f32, pub window: *const f32,
+    pub new_window: *mut f32, pub out_x: *mut c_void, pub out_b: *mut c_void, pub out_c: *mut c_void,
+}
+
+#[repr(C)]
+pub struct BmRmsnormGatedArgs {
+    pub rows: i32, pub width: i32, pub dtype: i32, pub norm_before_gate: i32, pub x_stride: i32, pub z_stride: i32,
+    pub eps: f32,
+    pub x: *const c_void, pub z: *const c_void, pub gamma: *const c_void, pub out: *mut c_void,
 }
 
 #[repr(C)]
@@ -106,7 +127,11 @@ extern "C" {
     pub fn bm_ssd3_double_bwd(args: *const BmSsd3BwdArgs, ws: *mut c_void, ws_bytes: usize, stream: *mut c_void) -> i32;
     pub fn bm_step2(args: *const BmStep2Args, stream: *mut c_void) -> i32;
     pub fn bm_conv_step(args: *const BmConvStepArgs, stream: *mut c_void) -> i32;
+    pub fn bm_conv1d_silu_fwd(args: *const BmConv1dSiluArgs, stream: *mut c_void) -> i32;
+    pub fn bm_rmsnorm_gated(args: *const BmRmsnormGatedArgs, stream: *mut c_void) -> i32;
     pub fn bm_selscan1_fwd(args: *const BmSelscan1Args, stream: *mut c_void) -> i32;
+    pub fn bm_selscan1_fwd_workspace_bytes(args: *const BmSelscan1Args) -> usize;
+    pub fn bm_selscan1_fwd_ws(args: *const BmSelscan1Args, ws: *mut c_void, ws_bytes: usize, stream: *mut c_void) -> i32;
     pub fn bm_step1(args: *const BmStep1Args, stream: *mut c_void) -> i32;
     pub fn bm_angle_cumsum(args: *const BmAngleCumsumArgs, stream: *mut c_void) -> i32;
     pub fn bm_step3(args: *const BmStep3Args, stream: *mut c_void) -> i32;
