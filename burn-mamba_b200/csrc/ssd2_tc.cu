@@ -3,7 +3,11 @@
 //
 // One persistent CTA per SM walks (batch, head) units; inside a unit it walks the sequence in tiles of
 // T = 128 tokens, keeping the head's state [r = 128, p = 64] in registers (float32) for the whole
-// sequence, so no per-chunk state ever goes to HBM.  Per tile (reference formulas:
+// sequence, so no per-chunk state ever goes to HBM.  The tiles of all units, laid end to end, are cut
+// into one contiguous range per CTA, so every CTA gets the same number of tiles (+-1) whatever the
+// number of units; a unit that straddles two ranges is walked by two CTAs, the first handing the state
+// it reached to the second through the workspace (a CTA walks its range's last piece first and its
+// first piece last, so the piece it depends on has long been finished).  Per tile (reference formulas:
 // src/mamba2/ssd/serial.rs:138-506, restated with the tile as the chunk):
 //     CB   = C B^T                                          tcgen05 SS   (K1/K2)
 //     P    = bf16(CB * exp(cum_t - cum_s)[s<=t] dt_s + D [s==t])  in TMEM (mask + skip of K5)
@@ -79,6 +83,7 @@ struct Barriers {
     uint32_t tmem_base;
     uint32_t abort_flag;
     int x_issued, cb_issued;                // TMA producer: tiles whose X / C+B loads have been issued
+    int w_total, w_items, w_unit0, w_first, w_last_end;   // this CTA's tile range, as items (see item_of)
 };
 
 struct alignas(64) Params {
@@ -92,8 +97,11 @@ struct alignas(64) Params {
     float* h_final;
     float* chunk_states;
     int* status;
+    int* handoff_flags;   // [grid] warps of CTA c that have stored the state their last piece ends with
+    float* handoff;       // [grid][P][R] that state
     long long* trace;
     int B, S, H, G, Q, NC, tiles_per_unit, num_units;
+    int share_q, share_r;   // (num_units * tiles_per_unit) / grid and the remainder
     int stall_loads;
     // Mamba-3 cores (kMode 1): S counts fused (time x rank) rows, St time steps, rows per step = 1 << log2m;
     // `dt` holds the column scale (NULL = 1, the generic core), `da` the per-step log decay, `gamma` the same-step
@@ -232,27 +240,26 @@ __device__ __forceinline__ void mask_block_m3(const uint32_t (&r)[32], uint32_t 
 // clamp(softplus(x)) of the fused dt path (src/mamba2/mamba2.rs:692-697); out of line: rarely used
 __device__ __noinline__ float dt_activation(float x, float lo, float hi) { return fminf(fmaxf(softplus_f32(x), lo), hi); }
 
-// Walks this CTA's tiles in order: units blockIdx.x, blockIdx.x + gridDim.x, ... and the tiles of each unit.
-// Divisions happen only at unit boundaries.
+// This CTA's tile range [lo, hi) of the global (unit-major) tile sequence, as items: an item is the part of
+// one unit inside the range, tiles [i0, iend) of that unit.  Natural item j covers unit w_unit0 + j; the first
+// may start inside its unit (it continues what the CTA before this one began), the last may end inside its
+// unit (the next CTA continues it).  Walk order: the last item first, the first item last, the rest in
+// between -- so the piece another CTA waits for is produced at once, and the piece that waits comes last.
+// -> {i0, iend, batch row, head}
+__device__ __noinline__ int4 item_of(const Barriers* bars, int tpu, int H, int pos) {
+    const int n = bars->w_items;
+    const int j = pos == 0 ? n - 1 : (pos == n - 1 ? 0 : pos);
+    const int unit = bars->w_unit0 + j;
+    int4 v;
+    v.x = j == 0 ? bars->w_first : 0;
+    v.y = j == n - 1 ? bars->w_last_end : tpu;
+    v.z = unit / H;
+    v.w = unit - v.z * H;
+    return v;
+}
+
 struct TileWalk {
-    int i, b, h, tpu, H, db, dh;
-    __device__ __forceinline__ TileWalk(int tpu_, int H_) : i(0), tpu(tpu_), H(H_) {
-        b = (int)blockIdx.x / H;
-        h = (int)blockIdx.x % H;
-        db = (int)gridDim.x / H;     // a step of gridDim.x units moves (b, h) by (db, dh) with one carry
-        dh = (int)gridDim.x % H;
-    }
-    __device__ __forceinline__ void next() {
-        if (++i == tpu) {
-            i = 0;
-            b += db;
-            h += dh;
-            if (h >= H) {
-                h -= H;
-                ++b;
-            }
-        }
-    }
+    int i, iend, b, h, pos, i0;
 };
 
 // Timeout path only (kept out of line, away from the hot code).  A wait gave up somewhere in this CTA and
@@ -314,6 +321,17 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         for (int i = 0; i < 3; ++i) mbar_init(&bars->drain[i], 1);
         bars->abort_flag = 0;
         bars->x_issued = bars->cb_issued = 0;
+        {
+            // tiles [lo, hi) of the global tile sequence: share_q tiles per CTA, one more for the first share_r
+            const int c = blockIdx.x, extra = c < prm.share_r ? c : prm.share_r;
+            const int lo = c * prm.share_q + extra, hi = lo + prm.share_q + (c < prm.share_r ? 1 : 0);
+            const int u0 = lo / prm.tiles_per_unit, u1 = (hi - 1) / prm.tiles_per_unit;
+            bars->w_total = hi - lo;
+            bars->w_items = u1 - u0 + 1;
+            bars->w_unit0 = u0;
+            bars->w_first = lo - u0 * prm.tiles_per_unit;
+            bars->w_last_end = hi - u1 * prm.tiles_per_unit;
+        }
         fence_mbar_init();
     }
     if (warp == 2) {
@@ -326,9 +344,15 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
     const uint32_t tmem = bars->tmem_base;
 
     const int tpu = prm.tiles_per_unit;
-    int my_units = 0;
-    for (int u = blockIdx.x; u < prm.num_units; u += gridDim.x) ++my_units;
-    const int total = my_units * tpu;
+    const int total = bars->w_total;
+    // a walker starts before its first tile: the first walk_next() loads item 0
+    auto walk_next = [&](TileWalk& w) {
+        if (++w.i == w.iend) {
+            const int4 v = item_of(bars, tpu, prm.H, ++w.pos);
+            w.i = w.i0 = v.x, w.iend = v.y, w.b = v.z, w.h = v.w;
+        }
+    };
+#define BM_WALK(w) TileWalk w; w.pos = -1, w.i = 0, w.iend = 1, w.b = w.h = w.i0 = 0
     const int hpg = prm.H / prm.G;
     const uint32_t c_base = smem_u32(smem + kOffC), b_base = smem_u32(smem + kOffB);
     const uint32_t x_base = smem_u32(smem + kOffX), xw_base = smem_u32(smem + kOffXw), h_base = smem_u32(smem + kOffH);
@@ -340,8 +364,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             tma_prefetch_desc(&prm.tm_b);
             tma_prefetch_desc(&prm.tm_c);
             tma_prefetch_desc(&prm.tm_y);
-            TileWalk tw(tpu, prm.H);
-            for (int it = 0; it < (prm.stall_loads ? 0 : total); ++it, tw.next()) {
+            BM_WALK(tw);
+            for (int it = 0; it < (prm.stall_loads ? 0 : total); ++it) {
+                walk_next(tw);
                 const int b = tw.b, h = tw.h, g = h / hpg;
                 const int st = it & 1, s0 = tw.i * T;
                 // X stage first: it is released early (by the scaling pass of the tile two back; on exact
@@ -442,7 +467,8 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // A lane owns four consecutive tokens: a serial sum over its four steps, one warp scan over the lane
         // totals, and the per-token factors follow.  The dt values of a tile are fetched one tile ahead
         // (four loads per lane, issued together), so the global-memory latency is hidden behind the tile before.
-        TileWalk tw(tpu, prm.H), twn(tpu, prm.H);
+        BM_WALK(twn);
+        TileWalk tw;
         float nv[4], nda[4];
         auto fetch = [&](const TileWalk& w) {
             const int left = prm.S - w.i * T;
@@ -466,34 +492,39 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 }
             }
         };
-        if (total > 0) fetch(twn);
-        for (int it = 0; it < total; ++it, tw.next()) {
-            const int h = tw.h, i = tw.i;
+        for (int it = -1; it < total; ++it) {
+            // the pass before the first tile (it = -1) only fetches that tile's steps
+            tw = twn;
             const int cst = (it & (kCumStages - 1));
             float* cum2 = reinterpret_cast<float*>(smem + kOffCum + cst * kCumStageBytes);
             float *dtv = cum2 + kCumDt, *wv = cum2 + kCumW, *colf = cum2 + kCumColf;
-            const float ah = kMode == 0 ? prm.a[h] * log2e : log2e;
-            const float bias = (kMode == 0 && prm.dt_bias) ? prm.dt_bias[h] : 0.f;
-            const int left = prm.S - i * T;      // tokens of the sequence from the start of this tile on
+            const int left = prm.S - tw.i * T;      // tokens of the sequence from the start of this tile on
             float d4[4], c4[4];
             float run = 0.f;
             bool zero = false;
+            if (it >= 0) {
+                const float ah = kMode == 0 ? prm.a[tw.h] * log2e : log2e;
+                const float bias = (kMode == 0 && prm.dt_bias) ? prm.dt_bias[tw.h] : 0.f;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                float v = nv[k];
-                const bool live = lane * 4 + k < left;
-                if (kMode == 0) {
-                    if (prm.dt_bias && live) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
-                    zero |= live && !(v > 0.f);
-                    run = fmaf(v, ah, run);
-                } else {
-                    run = fmaf(nda[k], ah, run);
+                for (int k = 0; k < 4; ++k) {
+                    float v = nv[k];
+                    const bool live = lane * 4 + k < left;
+                    if (kMode == 0) {
+                        if (prm.dt_bias && live) v = dt_activation(v + bias, prm.dt_min, prm.dt_max);
+                        zero |= live && !(v > 0.f);
+                        run = fmaf(v, ah, run);
+                    } else {
+                        run = fmaf(nda[k], ah, run);
+                    }
+                    d4[k] = v;
+                    c4[k] = run;
                 }
-                d4[k] = v;
-                c4[k] = run;
             }
-            twn.next();
-            if (it + 1 < total) fetch(twn);
+            if (it + 1 < total) {
+                walk_next(twn);
+                fetch(twn);
+            }
+            if (it < 0) continue;
             float incl = run;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -537,8 +568,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             causal[j] = (2 * j <= lane ? 0x0000ffffu : 0u) | (2 * j + 1 <= lane ? 0xffff0000u : 0u);
             asm volatile("" : "+r"(causal[j]));   // keep the masks in registers instead of recomputing them per tile
         }
-        TileWalk tw(tpu, prm.H);
-        for (int it = 0; it < total; ++it, tw.next()) {
+        BM_WALK(tw);
+        for (int it = 0; it < total; ++it) {
+            if (kMode == 1) walk_next(tw);
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + kCumDt, *colf = cum2 + kCumColf;
@@ -663,20 +695,36 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // still busy with tile it), folds S(it) into the state and publishes the result as the readout
         // operand of tile it+1.
         // At the first tile of a unit the initial state is loaded and published instead.
-        TileWalk tw(tpu, prm.H);
+        BM_WALK(tw);
         for (int it = -1; it < total; ++it) {
-            if (it > 0) tw.next();
+            if (it != 0) walk_next(tw);
             const int itc = it < 0 ? 0 : it;
             const int i = tw.i, b = tw.b, h = tw.h;
             const int cst = (itc & (kCumStages - 1));
             const float* cumv = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
             if (it >= 0) {
-                if (__builtin_expect(i == 0, 0)) {
-                    // unit start: initial state -> registers, published as the operand of this tile's
-                    // readout (the operand tile is free once Y2(it-1) has completed)
+                if (__builtin_expect(i == tw.i0, 0)) {
+                    // item start: the state entering it -> registers, published as the operand of this tile's
+                    // readout (the operand tile is free once Y2(it-1) has completed).  At the start of a unit
+                    // that is the caller's initial state; inside a unit, what the CTA before this one stored
+                    // when its piece of the unit ended.
+                    const float* src = prm.h0 ? prm.h0 + state_base : nullptr;
+                    if (i != 0) {
+                        const int* flag = prm.handoff_flags + (blockIdx.x - 1);
+                        uint32_t n_ = 0;
+                        bool ok_ = true;
+#pragma unroll 1
+                        while (ld_acquire_gpu(flag) < 4)
+                            if (++n_ >= kWaitBudget) {
+                                ok_ = false;
+                                break;
+                            }
+                        if (!__all_sync(0xffffffffu, ok_)) goto timed_out;
+                        src = prm.handoff + (int64_t)(blockIdx.x - 1) * P * R;
+                    }
 #pragma unroll
-                    for (int p = 0; p < P; ++p) hst[p] = prm.h0 ? prm.h0[state_base + (int64_t)p * R + t] : 0.f;
+                    for (int p = 0; p < P; ++p) hst[p] = src ? src[(int64_t)p * R + t] : 0.f;
                     if (it > 0) BM_WAIT_WARP(&bars->h_free, (it - 1) & 1);
                     publish_state();
                     BM_TRACE(5, it, 3);
@@ -723,16 +771,24 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     mbar_arrive(&bars->s_empty[it & 1]);
                     mbar_arrive(&bars->cum_empty[cst]);
                 }
-                // unless the unit ends here, the updated state is the readout operand of the next tile;
+                // unless the item ends here, the updated state is the readout operand of the next tile;
                 // the operand tile is free once Y2(it) has completed
-                if (__builtin_expect(i + 1 < tpu, 1)) {
+                if (__builtin_expect(i + 1 < tw.iend, 1)) {
                     BM_WAIT_WARP(&bars->h_free, it & 1);
                     publish_state();
                 }
                 BM_TRACE(5, it, 2);
-                if (__builtin_expect(i + 1 == tpu, 0)) {
+                if (__builtin_expect(i + 1 == tw.iend, 0)) {
+                    // end of the unit: the final state; end of this CTA's piece of it: the hand-over
+                    const bool whole = tw.iend == tpu;
+                    float* dst = whole ? prm.h_final + state_base : prm.handoff + (int64_t)blockIdx.x * P * R;
 #pragma unroll
-                    for (int p = 0; p < P; ++p) prm.h_final[state_base + (int64_t)p * R + t] = hst[p];
+                    for (int p = 0; p < P; ++p) dst[(int64_t)p * R + t] = hst[p];
+                    if (!whole) {
+                        __threadfence();
+                        __syncwarp();
+                        if (lane == 0) atomicAdd(prm.handoff_flags + blockIdx.x, 1);
+                    }
                 }
             }
         }
@@ -745,8 +801,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
         unsigned char* stage = smem + kOffStage + q * kStageWarpBytes;
         const uint32_t srow = lane * 64, sxor = (lane >> 1) & 3;   // 64-byte swizzle: chunk ^ ((row >> 1) & 3)
-        TileWalk tw(tpu, prm.H);
-        for (int it = 0; it < total; ++it, tw.next()) {
+        BM_WALK(tw);
+        for (int it = 0; it < total; ++it) {
+            walk_next(tw);
             const int i = tw.i, b = tw.b, h = tw.h;
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
@@ -867,7 +924,19 @@ const char* ssd2_why_not(const bm_ssd2_fwd_args* a) {
 
 bool ssd2_supported(const bm_ssd2_fwd_args* a) { return ssd2_why_not(a) == nullptr; }
 
-size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args*) { return 256 + 7 * 64 * 4 * 8; }  // status word (+ trace area of development builds)
+// Workspace head shared by both launchers: status word and the CTAs' hand-over flags in the first kWsFlagBytes
+// (reset before every launch), the trace area of development builds, then one state per CTA for hand-overs.
+constexpr size_t kWsFlagBytes = 2048, kWsTraceBytes = 7 * 64 * 4 * 8;
+static size_t ws_head_bytes() { return align_up(kWsFlagBytes + kWsTraceBytes, 256) + (size_t)num_sms() * P * R * sizeof(float); }
+static void ws_head_pointers(void* workspace, Params& prm) {
+    char* w = static_cast<char*>(workspace);
+    prm.status = reinterpret_cast<int*>(w);
+    prm.handoff_flags = reinterpret_cast<int*>(w + 64);
+    prm.trace = reinterpret_cast<long long*>(w + kWsFlagBytes);
+    prm.handoff = reinterpret_cast<float*>(w + align_up(kWsFlagBytes + kWsTraceBytes, 256));
+}
+
+size_t ssd2_workspace_bytes(const bm_ssd2_fwd_args*) { return ws_head_bytes(); }
 
 int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     if (workspace == nullptr || workspace_bytes < ssd2_workspace_bytes(a))
@@ -895,8 +964,7 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
     prm.dt = a->dt, prm.a = a->a, prm.d = a->d, prm.h0 = a->h0, prm.dt_bias = a->dt_bias;
     prm.dt_min = a->dt_min, prm.dt_max = a->dt_max;
     prm.h_final = a->h_final, prm.chunk_states = a->chunk_states;
-    prm.status = static_cast<int*>(workspace);
-    prm.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256);
+    ws_head_pointers(workspace, prm);
     prm.B = a->batch, prm.S = a->seqlen, prm.H = a->nheads, prm.G = a->ngroups, prm.Q = a->chunk_len;
     prm.NC = (int)cdiv(a->seqlen, a->chunk_len);
     prm.tiles_per_unit = (int)cdiv(a->seqlen, T);
@@ -908,8 +976,11 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
         cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd2_tc_kernel)");
     }
-    if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, 256, stream), "cudaMemsetAsync(status)")) return e;
+    if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, kWsFlagBytes, stream), "cudaMemsetAsync(status)")) return e;
     const int grid = prm.num_units < num_sms() ? prm.num_units : num_sms();
+    if ((int64_t)prm.num_units * prm.tiles_per_unit > INT32_MAX) return fail(BM_ERR_UNSUPPORTED, "more than 2^31 tiles");
+    prm.share_q = (int)((int64_t)prm.num_units * prm.tiles_per_unit / grid);
+    prm.share_r = (int)((int64_t)prm.num_units * prm.tiles_per_unit % grid);
     ssd2_tc_kernel<0><<<grid, kThreads, kSmemBytes, stream>>>(prm);
     return check_launch("ssd2_tc_kernel");
 }
@@ -991,7 +1062,7 @@ const char* ssd3_why_not(const bm_ssd3_fwd_args* a) {
 bool ssd3_supported(const bm_ssd3_fwd_args* a) { return ssd3_why_not(a) == nullptr; }
 
 size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a) {
-    size_t n = 256 + 7 * 64 * 4 * 8;
+    size_t n = ws_head_bytes();
     if (a->angles != nullptr)   // rotated copies of B and C
         n = align_up(n, 256) + 2 * align_up((size_t)a->batch * a->seqlen * a->mimo_rank * a->nheads * a->state_rank * 2, 256);
     return n;
@@ -1005,7 +1076,7 @@ int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t
     const void* csrc = a->c;
     if (a->angles != nullptr) {
         const size_t each = align_up((size_t)a->batch * a->seqlen * a->mimo_rank * a->nheads * a->state_rank * 2, 256);
-        char* base = static_cast<char*>(workspace) + align_up(256 + 7 * 64 * 4 * 8, 256);
+        char* base = static_cast<char*>(workspace) + align_up(ws_head_bytes(), 256);
         const int64_t rows = (int64_t)a->batch * a->seqlen;
         const int64_t total = rows * a->nheads * (a->state_rank / 16);
         rotate_bc_kernel<<<(unsigned)cdiv(total, 256), 256, 0, stream>>>(
@@ -1038,8 +1109,7 @@ int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t
     prm.dt = single ? a->scale : nullptr, prm.da = a->da, prm.gamma = single ? a->gamma : nullptr;
     prm.a = nullptr, prm.d = nullptr, prm.h0 = a->h0, prm.dt_bias = nullptr;
     prm.h_final = a->h_final, prm.chunk_states = nullptr;
-    prm.status = static_cast<int*>(workspace);
-    prm.trace = reinterpret_cast<long long*>(static_cast<char*>(workspace) + 256);
+    ws_head_pointers(workspace, prm);
     prm.B = a->batch, prm.S = (int)S, prm.St = a->seqlen, prm.log2m = log2_exact(a->mimo_rank);
     prm.H = a->nheads, prm.G = a->nheads, prm.Q = T, prm.NC = 1;
     prm.tiles_per_unit = (int)cdiv((int64_t)S, T);
@@ -1049,8 +1119,11 @@ int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t
         cudaError_t e = cudaFuncSetAttribute(ssd2_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
         if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd3 tensor kernel)");
     }
-    if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, 256, stream), "cudaMemsetAsync(status)")) return e;
+    if (int32_t e = check_cuda(cudaMemsetAsync(workspace, 0, kWsFlagBytes, stream), "cudaMemsetAsync(status)")) return e;
     const int grid = prm.num_units < num_sms() ? prm.num_units : num_sms();
+    if ((int64_t)prm.num_units * prm.tiles_per_unit > INT32_MAX) return fail(BM_ERR_UNSUPPORTED, "more than 2^31 tiles");
+    prm.share_q = (int)((int64_t)prm.num_units * prm.tiles_per_unit / grid);
+    prm.share_r = (int)((int64_t)prm.num_units * prm.tiles_per_unit % grid);
     ssd2_tc_kernel<1><<<grid, kThreads, kSmemBytes, stream>>>(prm);
     return check_launch("ssd3 tensor kernel");
 }

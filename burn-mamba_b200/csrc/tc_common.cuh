@@ -251,6 +251,13 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
 // never carries out of its field for addresses inside one CTA's shared memory).
 __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
 
+// Acquire load of a flag another CTA publishes (after its data stores and a __threadfence) with an atomic.
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
 #endif  // __CUDACC__
 
 }  // namespace tc

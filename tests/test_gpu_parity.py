@@ -349,6 +349,24 @@ def test_ssd2_tensor_path_mixed_decay_tiles(bm):
     assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
 
 
+def test_ssd2_tensor_path_units_cut_between_ctas_are_bitwise_equal_to_whole_units(bm):
+    """More units than SMs: the tiles of all units are dealt out as one contiguous range per CTA, so units
+    straddle CTAs and their state crosses through the workspace.  The same rows launched one at a time (fewer
+    units than SMs: nothing is cut) must give the same bits, chunk states included."""
+    cfg = inputs.ssd2_prefill(seed=35, batch=3, seqlen=640, nheads=100, headdim=64, state_rank=128, h0_std=0.1)
+    dt = torch.bfloat16
+    args = [dev(cfg["x"], dt), dev(cfg["dt"]), dev(cfg["a"]), dev(cfg["b"], dt), dev(cfg["c"], dt), dev(cfg["d"]),
+            dev(cfg["h0"])]
+    y, hf, st = bm.ops.ssd2_fwd(*args, chunk_len=128, path="tensor", return_chunk_states=True, check_status=True)
+    for row in range(3):
+        sl = lambda t, batched: t[row:row + 1].contiguous() if batched else t
+        part = [sl(a, i in (0, 1, 3, 4, 6)) for i, a in enumerate(args)]
+        y1, h1, s1 = bm.ops.ssd2_fwd(*part, chunk_len=128, path="tensor", return_chunk_states=True, check_status=True)
+        assert torch.equal(y[row:row + 1], y1) and torch.equal(hf[row:row + 1], h1) and torch.equal(st[row:row + 1], s1)
+    ye, he = bm.ops.ssd2_fwd(*args, chunk_len=128, path="exact")
+    assert rel_l2(host(y), host(ye)) <= 2e-2 and rel_l2(host(hf), host(he)) <= 2e-2
+
+
 # ------------------------------------------------------------------ backward (recompute) vs autodiff oracle
 def _grad_close(got, want, tol=1e-3):
     """The reference's gradient tolerance is max-abs 1e-3 at its tiny shapes; relative-L2 here."""
