@@ -74,7 +74,7 @@ class Ssd2BwdArgs(C.Structure):
     _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "headdim", "state_rank", "ngroups", "chunk_len",
                                     "dtype")] + [
         (n, _vp) for n in ("x", "dt", "a", "b", "c", "d", "h0", "dy", "dh_final", "dx", "ddt", "da", "db", "dc", "dd",
-                           "dh0")]
+                           "dh0")] + [("path", _i32), ("reserved", _i32)]
 
 
 class Ssd3BwdArgs(C.Structure):

@@ -20,6 +20,12 @@ bool ssd2_pair_preferred(const bm_ssd2_fwd_args* a);
 size_t ssd2_pair_workspace_bytes(const bm_ssd2_fwd_args* a);
 int32_t ssd2_pair_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+// Mamba-2 SSD backward on the tensor cores (bf16, headdim 64, state_rank 128): a forward pass of the kernel
+// above for the state entering every 128-token tile, then one reverse walk per (batch, head) unit.
+bool ssd2_bwd_supported(const bm_ssd2_bwd_args* a);
+const char* ssd2_bwd_why_not(const bm_ssd2_bwd_args* a);
+size_t ssd2_bwd_workspace_bytes(const bm_ssd2_bwd_args* a);
+int32_t ssd2_bwd_run(const bm_ssd2_bwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 // The Mamba-3 cores (single-pass with gamma / scale, or the generic core) on the one-head-per-CTA kernel, over the
 // fused (time x rank) axis.  bf16, headdim 64, state_rank 128, MIMO rank 1, 2 or 4.  When `angles` is given, B and C

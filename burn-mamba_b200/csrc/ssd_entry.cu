@@ -1,5 +1,6 @@
 // C-ABI entry points of the chunked SSD forward (Mamba-2, Mamba-3 single / double): argument
 // validation and dispatch between the exact path and the tensor-core path.
+#include <algorithm>
 #include "common.cuh"
 #include "ssd2_tc.cuh"
 #include "ssd_exact.cuh"
@@ -182,7 +183,9 @@ extern "C" int32_t bm_workspace_status(const void* workspace, void* stream) {
 // ---------------------------------------------------------------------------------------------
 extern "C" size_t bm_ssd2_bwd_workspace_bytes(const bm_ssd2_bwd_args* a) {
     if (a == nullptr || a->batch <= 0 || a->seqlen <= 0 || a->nheads <= 0 || a->chunk_len <= 0) return 0;
-    return exact::bwd_workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, true);
+    size_t n = exact::bwd_workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, true);
+    if (a->path != BM_PATH_EXACT && tc::ssd2_bwd_supported(a)) n = std::max(n, tc::ssd2_bwd_workspace_bytes(a));
+    return n;
 }
 
 extern "C" int32_t bm_ssd2_bwd(const bm_ssd2_bwd_args* a, void* ws, size_t ws_bytes, void* stream) {
@@ -198,6 +201,12 @@ extern "C" int32_t bm_ssd2_bwd(const bm_ssd2_bwd_args* a, void* ws, size_t ws_by
     BM_REQUIRE_PTR(a->dc); BM_REQUIRE_PTR(a->dh0);
     BM_OPTIONAL_PTR(a->d); BM_OPTIONAL_PTR(a->h0); BM_OPTIONAL_PTR(a->dh_final); BM_OPTIONAL_PTR(a->dd);
     BM_REQUIRE((a->d == nullptr) == (a->dd == nullptr), BM_ERR_NULL_POINTER, "d and dd must be given together");
+    BM_REQUIRE(a->path == BM_PATH_AUTO || a->path == BM_PATH_EXACT || a->path == BM_PATH_TENSOR, BM_ERR_UNSUPPORTED,
+               "path must be auto, exact or tensor");
+    if (a->path != BM_PATH_EXACT) {
+        if (tc::ssd2_bwd_supported(a)) return tc::ssd2_bwd_run(a, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+        if (a->path == BM_PATH_TENSOR) return fail(BM_ERR_UNSUPPORTED, "tensor-core backward: %s", tc::ssd2_bwd_why_not(a));
+    }
     exact::BwdParams bp{};
     exact::Params& p = bp.fwd;
     p.B = a->batch, p.S = a->seqlen, p.H = a->nheads, p.P = a->headdim, p.R = a->state_rank;

@@ -342,9 +342,9 @@ def ssd2_fwd_noalloc(x, dt, a, b, c, d=None, h0=None, chunk_len=256, dt_bias=Non
     return y, h_final
 
 
-def ssd2_bwd(x, dt, a, b, c, d, h0, dy, dh_final=None, chunk_len=256):
+def ssd2_bwd(x, dt, a, b, c, d, h0, dy, dh_final=None, chunk_len=256, path="auto", check_status=False):
     """Mamba-2 SSD backward (recompute).  Returns dict(dx, ddt, da, db, dc, dd, dh0), all float32;
-    db / dc are per group."""
+    db / dc are per group.  path: "auto" (tensor-core kernel for bf16, headdim 64, state_rank 128), "exact", "tensor"."""
     bsz, s, h, p = x.shape
     g, r = b.shape[2], b.shape[3]
     act = x.dtype
@@ -360,9 +360,11 @@ def ssd2_bwd(x, dt, a, b, c, d, h0, dy, dh_final=None, chunk_len=256):
                             dtype=_DT[act], x=_ptr(x), dt=_ptr(dt), a=_ptr(a), b=_ptr(b), c=_ptr(c), d=_ptr(d),
                             h0=_ptr(h0), dy=_ptr(dy), dh_final=_ptr(dh_final), dx=_ptr(out["dx"]), ddt=_ptr(out["ddt"]),
                             da=_ptr(out["da"]), db=_ptr(out["db"]), dc=_ptr(out["dc"]), dd=_ptr(out["dd"]),
-                            dh0=_ptr(out["dh0"]))
+                            dh0=_ptr(out["dh0"]), path=PATHS[path])
     ws = _workspace(lib.bm_ssd2_bwd_workspace_bytes(C.byref(args)), x.device)
     check(lib.bm_ssd2_bwd(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_ssd2_bwd")
+    if check_status:
+        check(lib.bm_workspace_status(ws.data_ptr(), _stream()), "bm_workspace_status")
     return out
 
 

@@ -165,6 +165,9 @@ typedef struct {
     float* dc;                /* [b, s, g, r] */
     float* dd;                /* [h] or NULL */
     float* dh0;               /* [b, h, p, r] */
+    int32_t path;             /* bm_path: AUTO = tensor-core kernel when dtype / shape allow it (bf16, headdim 64,
+                                 state_rank 128), else the exact path; EXACT and TENSOR force one */
+    int32_t reserved;         /* 0 */
 } bm_ssd2_bwd_args;
 
 size_t bm_ssd2_bwd_workspace_bytes(const bm_ssd2_bwd_args* args);

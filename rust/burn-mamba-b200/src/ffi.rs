@@ -28,6 +28,7 @@ pub struct BmSsd2BwdArgs {
     pub d: *const f32, pub h0: *const f32, pub dy: *const c_void, pub dh_final: *const f32,
     pub dx: *mut f32, pub ddt: *mut f32, pub da: *mut f32, pub db: *mut f32, pub dc: *mut f32, pub dd: *mut f32,
     pub dh0: *mut f32,
+    pub path: i32, pub reserved: i32,
 }
 
 #[repr(C)]

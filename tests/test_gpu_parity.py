@@ -391,6 +391,60 @@ def test_ssd2_backward_matches_autodiff_oracle(bm, b, s, h, p, r, g, Q):
         assert _grad_close(got[k], want[k]), (k, rel_l2(host(got[k]), want[k]))
 
 
+def _bwd_inputs(cfg, seed):
+    dt = torch.bfloat16
+    x, b, c = (q(cfg[k], dt) for k in ("x", "b", "c"))
+    rng = np.random.default_rng(seed)
+    dy = q(rng.standard_normal(x.shape).astype(np.float32), dt)
+    dhf = rng.standard_normal(cfg["h0"].shape).astype(np.float32)
+    args = (dev(x, dt), dev(cfg["dt"]), dev(cfg["a"]), dev(b, dt), dev(c, dt), dev(cfg["d"]), dev(cfg["h0"]), dev(dy, dt),
+            dev(dhf))
+    return (x, b, c, dy, dhf), args
+
+
+@pytest.mark.parametrize("b,s,h,g", [(1, 128, 1, 1), (1, 256, 2, 1), (2, 1024, 4, 2), (1, 300, 3, 3), (1, 100, 2, 1)])
+def test_ssd2_backward_tensor_path_matches_autodiff_oracle(bm, b, s, h, g):
+    """The tcgen05 backward (bf16 operands, float32 accumulation) against autodiff of the serial forward on the
+    same bf16-rounded inputs: all seven gradients, ragged lengths, groups, initial state and dh_final."""
+    from oracle import backward
+    cfg = inputs.ssd2_prefill(seed=310 + s, batch=b, seqlen=s, nheads=h, headdim=64, state_rank=128, ngroups=g, h0_std=0.2)
+    (x, bb, cc, dy, dhf), args = _bwd_inputs(cfg, 11)
+    want = backward.ssd2_grads(x, cfg["dt"], cfg["a"], bb, cc, cfg["d"], cfg["h0"], dy, dhf, 128)
+    got = bm.ops.ssd2_bwd(*args, chunk_len=128, path="tensor", check_status=True)
+    for k in ("dx", "ddt", "da", "db", "dc", "dd", "dh0"):
+        assert rel_l2(host(got[k]), want[k]) <= 2e-2, (k, rel_l2(host(got[k]), want[k]))
+
+
+def test_ssd2_backward_tensor_path_cut_units_strong_decay_and_zero_steps(bm):
+    """More units than SMs (units straddle CTAs and dh crosses through the workspace), heads whose state is
+    forgotten within a few tokens, and steps of exactly zero: the tensor-core backward against the float32
+    backward on device, and without dh_final / initial state / skip."""
+    cfg = inputs.ssd2_prefill(seed=36, batch=3, seqlen=640, nheads=100, headdim=64, state_rank=128, h0_std=0.1)
+    cfg["a"][::7] = -16.0
+    cfg["dt"][:, :, ::7] = 3.0
+    cfg["dt"][:, 5::9, 1::3] = 0.0
+    _, args = _bwd_inputs(cfg, 12)
+    got = bm.ops.ssd2_bwd(*args, chunk_len=128, path="tensor", check_status=True)
+    want = bm.ops.ssd2_bwd(*args, chunk_len=128, path="exact")
+    for k in ("dx", "ddt", "da", "db", "dc", "dd", "dh0"):
+        assert torch.isfinite(got[k]).all(), k
+        assert rel_l2(host(got[k]), host(want[k])) <= 2e-2, (k, rel_l2(host(got[k]), host(want[k])))
+    bare = list(args)
+    bare[5] = bare[6] = bare[8] = None
+    got = bm.ops.ssd2_bwd(*bare, chunk_len=128, path="tensor", check_status=True)
+    want = bm.ops.ssd2_bwd(*bare, chunk_len=128, path="exact")
+    for k in ("dx", "ddt", "da", "db", "dc", "dh0"):
+        assert rel_l2(host(got[k]), host(want[k])) <= 2e-2, (k, rel_l2(host(got[k]), host(want[k])))
+
+
+def test_ssd2_backward_tensor_path_refuses_what_it_does_not_cover(bm):
+    cfg = inputs.ssd2_prefill(seed=37, batch=1, seqlen=64, nheads=2, headdim=32, state_rank=64, h0_std=0.1)
+    _, args = _bwd_inputs(cfg, 13)
+    with pytest.raises(RuntimeError):
+        bm.ops.ssd2_bwd(*args, chunk_len=64, path="tensor")
+    bm.ops.ssd2_bwd(*args, chunk_len=64, path="auto")   # falls back to the exact path
+
+
 @pytest.mark.parametrize("b,s,h,p,r,m,Q", [(2, 12, 2, 8, 8, 1, 4), (2, 10, 2, 8, 8, 2, 4), (1, 40, 2, 16, 32, 3, 16),
                                            (1, 64, 2, 64, 128, 4, 32)])
 def test_ssd3_backward_matches_autodiff_oracle(bm, b, s, h, p, r, m, Q):
