@@ -631,27 +631,27 @@ def _ssd3_legs(torch, bm, dev, rn, flush, hbm, tensor, sb):
     flops = (2 * lm * lm * r + 2 * lm * lm * p + 4 * lm * r * p) * b * (s // q) * h
     path = "tensor" if getattr(bm.ops, "SSD3_TENSOR_PATH", False) else "exact"
     fwd = lambda: bm.ops.ssd3_single_fwd(v, da, bb, cc, gamma, scale, None, chunk_len=q, angles=angles, rope_dim=r, path=path)
-    ms = _time_flushed(torch, fwd, 3, flush)
+    ms = _time_flushed(torch, fwd, 5, flush)
     tensor(f"ssd3_single_fwd (b{b} L2048 H32 P64 N128 m4 Q64, bf16, rotation from angles, {path} path)", ms, flops,
            "dense GEMM count of the fused (time x rank) axis")
     del angles
     dy = rn(b, s, m, h, p, dt=bf)
     bwd = lambda: bm.ops.ssd3_bwd(v, da, bb, cc, gamma, scale, None, dy, None, chunk_len=q, single=True)
-    ms = _time_flushed(torch, bwd, 2, flush)
-    tensor("ssd3_single_bwd (same shape, recompute backward, pre-rotated B/C)", ms, 2.5 * flops, "2.5 x the forward count")
+    ms = _time_flushed(torch, bwd, 5, flush)
+    tensor("ssd3_single_bwd (same shape, recompute backward on the tensor cores, pre-rotated B/C)", ms, 2.5 * flops, "2.5 x the forward count")
 
 
 def _ssd2_bwd_leg(torch, bm, dev, rn, flush, hbm, tensor, sb):
-    """Mamba-2 recompute backward at the prefill head shape (b2 L4096 H80 P64 N128 G1 Q256, bf16)."""
+    """Mamba-2 recompute backward at the prefill configuration (b8 L4096 H80 P64 N128 G1 Q256, bf16)."""
     bf = torch.bfloat16
-    c = dict(CFG, batch=sb(2))
+    c = dict(CFG, batch=sb(8))
     b, s, h, p, r, q = c["batch"], c["seqlen"], c["nheads"], c["headdim"], c["state_rank"], c["chunk_len"]
     x, dy = rn(b, s, h, p, dt=bf), rn(b, s, h, p, dt=bf)
     dt = torch.rand(b, s, h, device=dev) * 0.05 + 1e-3
     a, d = -(torch.rand(h, device=dev) * 15 + 1), torch.rand(h, device=dev)
     bb, cc = rn(b, s, 1, r, dt=bf) / r ** 0.5, rn(b, s, 1, r, dt=bf) / r ** 0.5
-    ms = _time_flushed(torch, lambda: bm.ops.ssd2_bwd(x, dt, a, bb, cc, d, None, dy, None, chunk_len=q), 2, flush)
-    tensor(f"ssd2_bwd (b{b} L4096 H80 P64 N128 G1 Q256, bf16, recompute backward)", ms, 2.5 * algorithmic_flops(c),
+    ms = _time_flushed(torch, lambda: bm.ops.ssd2_bwd(x, dt, a, bb, cc, d, None, dy, None, chunk_len=q), 5, flush)
+    tensor(f"ssd2_bwd (b{b} L4096 H80 P64 N128 G1 Q256, bf16, recompute backward on the tensor cores)", ms, 2.5 * algorithmic_flops(c),
            "2.5 x the forward count")
 
 

@@ -81,7 +81,7 @@ class Ssd3BwdArgs(C.Structure):
     _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "headdim", "state_rank", "mimo_rank", "chunk_len",
                                     "dtype")] + [
         (n, _vp) for n in ("v", "da", "b", "c", "gamma", "scale", "h0", "dy", "dh_final", "dv", "dda", "db", "dc",
-                           "dgamma", "dscale", "dh0")]
+                           "dgamma", "dscale", "dh0")] + [("path", _i32), ("reserved", _i32)]
 
 
 class AngleCumsumArgs(C.Structure):

@@ -54,7 +54,7 @@ constexpr uint32_t kRowC = 528, kRowX = 272;  // padded row strides (bytes) of t
 constexpr uint32_t kOffStC = 0, kOffStB = 128 * kRowC, kOffStX = 2 * 128 * kRowC;
 static_assert(kOffStX + 128 * kRowX <= kOperandBytes, "staging does not fit the operand area");
 constexpr uint32_t kOffSc = kOperandBytes;    // per-tile scalars, float[128] each
-enum { kScCum = 0, kScDt, kScK, kScE, kScColk, kScColW, kScPa, kScPb = kScPa + 4, kScPd = kScPb + 4, kScCount = kScPd + 4 };
+enum { kScCum = 0, kScSc, kScSame, kScK, kScE, kScColk, kScColZ, kScPgs, kScPa, kScPgi = kScPa + 4, kScCount = kScPgi + 4 };
 constexpr uint32_t kOffRed = kOffSc + kScCount * 128 * 4;   // 8 floats of block reductions
 constexpr uint32_t kOffBar = kOffRed + 64;
 constexpr uint32_t kSmemBytes = kOffBar + 64 + 1024;
@@ -72,16 +72,19 @@ struct Bars {
 
 struct alignas(64) BwdParams {
     CUtensorMap tm_x, tm_dy, tm_b, tm_c;
-    const float* dt;
-    const float* a;
+    const float* sc;             // [b, s, h] column scale: dt (Mamba-2), scale (Mamba-3 single), NULL = 1
+    const float* a;              // [h] (Mamba-2: the step's log decay is dt a)
+    const float* da;             // [b, s, h] log decay per step (Mamba-3)
+    const float* gamma;          // [b, s, h] same-step weight (Mamba-3 single), NULL = 1
     const float* d;
     const float* chunk_states;   // [b, n, h, p, r] state entering every tile (from the forward pass)
     const float* dh_final;
-    const __nv_bfloat16* x;      // raw pointers for the row-local products
-    const __nv_bfloat16* dy;
-    float* dx;
-    float* ddt;
-    float* da;
+    float* dx;                   // [b, rows, h, p]
+    float* ddt;                  // Mamba-2: [b, s, h]
+    float* d_a;                  // Mamba-2: [h]
+    float* dda;                  // Mamba-3: [b, s, h]
+    float* dgamma;               // Mamba-3 single: [b, s, h]
+    float* dscale;               // Mamba-3 single: [b, s, h]
     float* db;
     float* dc;
     float* dd;
@@ -89,8 +92,9 @@ struct alignas(64) BwdParams {
     int* status;
     int* handoff_flags;          // [grid] warps of CTA c that have stored the dh its first piece ends with
     float* handoff;              // [grid][P][R]
-    int B, S, H, G, NT, num_units;
+    int B, S, St, H, G, NT, num_units, log2m;   // S counts fused (time x rank) rows, St time steps
     int share_q, share_r;        // (num_units * NT) / grid and the remainder
+    int plain_bc;                // one head per group: dB / dC rows are stored, not reduce-added
 };
 
 __device__ __forceinline__ void bulk_store_row(float* dst, const void* src, uint32_t bytes) {
@@ -115,7 +119,11 @@ __device__ __forceinline__ bool cta_wait_failed(uint64_t* bar, uint32_t parity) 
     return __syncthreads_or(!ok) != 0;
 }
 
-__global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_constant__ BwdParams prm) {
+// kMode 0: Mamba-2 (rows are tokens; column scale and same-step weight are both dt; skip term D).
+// kMode 1: the Mamba-3 cores on the fused (time x rank) axis, 1 << log2m rows per step: strict-in-time decay
+//          kernel with column scale `sc`, same-step block weighted by gamma (both 1 for the generic core).
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_constant__ BwdParams prm) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     Bars* bars = reinterpret_cast<Bars*>(smem + kOffBar);
@@ -123,6 +131,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
     float* red = reinterpret_cast<float*>(smem + kOffRed);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = tid & 127, pq = tid >> 7;   // the accumulator row and column quarter this thread owns
+    const int log2m = kMode == 0 ? 0 : prm.log2m;
 
     if (tid == 0) {
         mbar_init(&bars->ld_full, 1);
@@ -158,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
         const int i_lo = unit == u_first ? lo - u_first * prm.NT : 0;          // this CTA's tiles of the unit
         const int i_hi = unit == u_last ? hi - u_last * prm.NT : prm.NT;
         const int64_t state_base = ((int64_t)b * prm.H + h) * P * R;
-        const float ah = prm.a[h], dskip = prm.d ? prm.d[h] : 0.f;
+        const float ah = kMode == 0 ? prm.a[h] : 1.f, dskip = (kMode == 0 && prm.d) ? prm.d[h] : 0.f;
         // dh = gradient of the state leaving the current tile: the caller's at the end of the unit, else what
         // the next CTA stored when it finished the later tiles of this unit
         float dh[16];
@@ -180,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
 #pragma unroll
             for (int j = 0; j < 16; ++j) dh[j] = src ? src[(int64_t)(16 * pq + j) * R + row] : 0.f;
         }
-        float da_acc = 0.f, dd_acc = 0.f;   // meaningful in thread 0 (dA) and as per-thread partials (dD)
+        float da_acc = 0.f, dd_acc = 0.f;   // Mamba-2: dA (warp 0) and per-thread partials of dD
 
         for (int i = i_hi - 1; i >= i_lo; --i, phase ^= 1) {
             const int s0 = i * T, left = prm.S - s0;
@@ -194,14 +203,25 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                 tma_load_4d(smem + kOffC, &prm.tm_c, &bars->ld_full, 0, g, s0, b);
                 tma_load_4d(smem + kOffC + kPanel, &prm.tm_c, &bars->ld_full, 64, g, s0, b);
             }
-            // ---- per-token scalars (warp 1): log2-domain cumulative decay and the factors derived from it
+            // ---- per-row scalars (warp 1): log2-domain cumulative decay and the factors derived from it
             if (warp == 1) {
-                float d4[4], c4[4], run = 0.f;
+                float d4[4], g4[4], c4[4], run = 0.f;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int t = lane * 4 + k;
-                    d4[k] = t < left ? prm.dt[((int64_t)b * prm.S + s0 + t) * prm.H + h] : 0.f;
-                    run = fmaf(d4[k], ah * log2e, run);
+                    const bool live = t < left;
+                    if (kMode == 0) {
+                        d4[k] = live ? prm.sc[((int64_t)b * prm.S + s0 + t) * prm.H + h] : 0.f;
+                        g4[k] = d4[k];
+                        run = fmaf(d4[k], ah * log2e, run);
+                    } else {
+                        const int rrow = s0 + t;
+                        const int64_t o = ((int64_t)b * prm.St + (rrow >> log2m)) * prm.H + h;
+                        d4[k] = live ? (prm.sc ? prm.sc[o] : 1.f) : 0.f;
+                        g4[k] = live ? (prm.gamma ? prm.gamma[o] : 1.f) : 0.f;
+                        // the step's decay enters at its first rank, so every rank of a step sees it
+                        if (live && (rrow & ((1 << log2m) - 1)) == 0) run = fmaf(prm.da[o], log2e, run);
+                    }
                     c4[k] = run;
                 }
                 float incl = run;
@@ -212,17 +232,19 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                 }
                 const float excl = incl - run;
                 const float cend = __shfl_sync(0xffffffffu, incl, 31);
-                const float cblk = __shfl_sync(0xffffffffu, incl, (lane & ~7) | 7);   // end of the 32-token block
+                const float cblk = __shfl_sync(0xffffffffu, incl, (lane & ~7) | 7);   // end of the 32-row block
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const int t = lane * 4 + k;
                     const float c = excl + c4[k];
                     sc[kScCum * 128 + t] = c;
-                    sc[kScDt * 128 + t] = d4[k];
+                    sc[kScSc * 128 + t] = d4[k];
+                    sc[kScSame * 128 + t] = g4[k];
                     sc[kScK * 128 + t] = ex2(cend - c);
                     sc[kScE * 128 + t] = ex2(c);
                     sc[kScColk * 128 + t] = ex2(cblk - c);
-                    sc[kScColW * 128 + t] = 0.f;
+                    sc[kScColZ * 128 + t] = 0.f;
+                    sc[kScPgs * 128 + t] = 0.f;
                 }
             }
             // ---- the state entering the tile -> bf16 operand [r][p]; dh -> bf16 operand [r][p]; <dh, h_in> over
@@ -246,31 +268,28 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                 *reinterpret_cast<uint4*>(smem + kOffDh + sw128_offset(row, 2 * pq + 1)) = w1;
             }
             if (cta_wait_failed(&bars->ld_full, phase)) goto timed_out;   // also publishes the scalars
-            // ---- operand scaling: X -> dt X, e dY (this thread: 16 elements of row `row`)
-            uint4 xr[2], dyr[2];   // the unscaled x and dy of this thread's 16 elements, packed bf16
+            // ---- e dY (this thread: 16 elements of row `row`); x and dy of those elements stay in registers
+            uint4 xr[2], dyr[2];
             {
-                const float dts = sc[kScDt * 128 + row], et = sc[kScE * 128 + row];
+                const float et = sc[kScE * 128 + row];
 #pragma unroll
                 for (int c2 = 0; c2 < 2; ++c2) {
                     const uint32_t off = sw128_offset(row, 2 * pq + c2);
                     xr[c2] = *reinterpret_cast<const uint4*>(smem + kOffX + off);
                     dyr[c2] = *reinterpret_cast<const uint4*>(smem + kOffDy + off);
-                    const uint32_t* xs = &xr[c2].x;
                     const uint32_t* ys = &dyr[c2].x;
-                    uint32_t xo[4], yo[4];
+                    uint32_t yo[4];
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {
-                        const float2 xf = unpack_bf16x2(xs[m]), yf = unpack_bf16x2(ys[m]);
-                        xo[m] = pack_bf16x2(xf.x * dts, xf.y * dts);
+                        const float2 yf = unpack_bf16x2(ys[m]);
                         yo[m] = pack_bf16x2(yf.x * et, yf.y * et);
                     }
-                    *reinterpret_cast<uint4*>(smem + kOffX + off) = make_uint4(xo[0], xo[1], xo[2], xo[3]);
                     *reinterpret_cast<uint4*>(smem + kOffDye + off) = make_uint4(yo[0], yo[1], yo[2], yo[3]);
                 }
             }
             fence_proxy_async_smem();
             __syncthreads();
-            // ---- phase 1: CB = C B^T, dM = dY (dt X)^T
+            // ---- phase 1: CB = C B^T, dM = dY X^T
             if (tid == 0) {
                 tc_fence_after();
                 const uint32_t id128 = umma_idesc_bf16(128, 128, false, false);
@@ -287,7 +306,11 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
             }
             if (cta_wait_failed(&bars->mma1, phase)) goto timed_out;
             tc_fence_after();
-            // ---- mask pass: columns [32 pq, 32 pq + 32) of row `row`; X: dt X -> k dt X for the state terms
+            // ---- mask pass: columns [32 pq, 32 pq + 32) of row `row`.  Entry (t, s): an earlier step takes
+            // w = exp(c_t - c_s) sc_s, the same step takes the row's same-step weight, later steps 0.
+            //   M = CB w, dCB = dM w (bf16, to shared memory);  Z = CB dM exp(c_t - c_s) over earlier steps:
+            //   its row sums weighted by sc_s and its column sums feed the decay and scale gradients; the
+            //   same-step sum of CB dM is the gradient of the same-step weight.
             {
                 const int q = row >> 5;                       // 32-row block of this row
                 uint32_t om[16], od[16];
@@ -302,30 +325,50 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                         const float rf = ex2(ct - sc[kScCum * 128 + 32 * pq + 31]);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const float f0 = rf * sc[kScColk * 128 + 32 * pq + 2 * j], f1 = rf * sc[kScColk * 128 + 32 * pq + 2 * j + 1];
-                            const float m0 = __uint_as_float(cb[2 * j]) * f0, m1 = __uint_as_float(cb[2 * j + 1]) * f1;
-                            om[j] = pack_bf16x2(m0, m1);
-                            od[j] = pack_bf16x2(__uint_as_float(dm[2 * j]) * f0, __uint_as_float(dm[2 * j + 1]) * f1);
-                            cb[2 * j] = __float_as_uint(m0 * __uint_as_float(dm[2 * j]));          // W
-                            cb[2 * j + 1] = __float_as_uint(m1 * __uint_as_float(dm[2 * j + 1]));
+                            const int s_ = 32 * pq + 2 * j;
+                            const float f0 = rf * sc[kScColk * 128 + s_], f1 = rf * sc[kScColk * 128 + s_ + 1];
+                            const float w0 = f0 * sc[kScSc * 128 + s_], w1 = f1 * sc[kScSc * 128 + s_ + 1];
+                            const float c0 = __uint_as_float(cb[2 * j]), c1 = __uint_as_float(cb[2 * j + 1]);
+                            const float d0 = __uint_as_float(dm[2 * j]), d1 = __uint_as_float(dm[2 * j + 1]);
+                            om[j] = pack_bf16x2(c0 * w0, c1 * w1);
+                            od[j] = pack_bf16x2(d0 * w0, d1 * w1);
+                            const float z0 = c0 * d0 * f0, z1 = c1 * d1 * f1;
+                            wrow = fmaf(z0, sc[kScSc * 128 + s_], wrow);
+                            wrow = fmaf(z1, sc[kScSc * 128 + s_ + 1], wrow);
+                            cb[2 * j] = __float_as_uint(z0);
+                            cb[2 * j + 1] = __float_as_uint(z1);
                         }
                     } else {
+                        const float same = sc[kScSame * 128 + row];
+                        const int tstep = row >> log2m;
+                        float gs = 0.f;
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            const int s_ = 32 * pq + 2 * j;
-                            const float f0 = s_ <= row ? ex2(ct - sc[kScCum * 128 + s_]) : 0.f;
-                            const float f1 = s_ + 1 <= row ? ex2(ct - sc[kScCum * 128 + s_ + 1]) : 0.f;
-                            const float m0 = __uint_as_float(cb[2 * j]) * f0, m1 = __uint_as_float(cb[2 * j + 1]) * f1;
-                            om[j] = pack_bf16x2(m0, m1);
-                            od[j] = pack_bf16x2(__uint_as_float(dm[2 * j]) * f0, __uint_as_float(dm[2 * j + 1]) * f1);
-                            cb[2 * j] = __float_as_uint(m0 * __uint_as_float(dm[2 * j]));
-                            cb[2 * j + 1] = __float_as_uint(m1 * __uint_as_float(dm[2 * j + 1]));
-                        }
-                    }
-                    // W = M o dM: row sum (this thread's 32 columns) and, through a transposing butterfly over
-                    // the warp's 32 rows, the column sums of the same values
+                            float mv[2], dcv[2], zv[2];
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) wrow += __uint_as_float(cb[j]);
+                            for (int e = 0; e < 2; ++e) {
+                                const int s_ = 32 * pq + 2 * j + e, sstep = s_ >> log2m;
+                                const float cv = __uint_as_float(cb[2 * j + e]), dv = __uint_as_float(dm[2 * j + e]);
+                                float w = 0.f, z = 0.f;
+                                if (sstep < tstep) {
+                                    const float f = ex2(ct - sc[kScCum * 128 + s_]);
+                                    w = f * sc[kScSc * 128 + s_];
+                                    z = cv * dv * f;
+                                    wrow = fmaf(z, sc[kScSc * 128 + s_], wrow);
+                                } else if (sstep == tstep) {
+                                    w = same;
+                                    gs = fmaf(cv, dv, gs);
+                                }
+                                mv[e] = cv * w, dcv[e] = dv * w, zv[e] = z;
+                            }
+                            om[j] = pack_bf16x2(mv[0], mv[1]);
+                            od[j] = pack_bf16x2(dcv[0], dcv[1]);
+                            cb[2 * j] = __float_as_uint(zv[0]);
+                            cb[2 * j + 1] = __float_as_uint(zv[1]);
+                        }
+                        sc[kScPgs * 128 + row] = gs;
+                    }
+                    // column sums of Z over the warp's 32 rows through a transposing butterfly
 #pragma unroll
                     for (int o = 16; o >= 1; o >>= 1) {
 #pragma unroll
@@ -336,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                             cb[j] = __float_as_uint(keep + __shfl_xor_sync(0xffffffffu, send, o));
                         }
                     }
-                    atomicAdd(&sc[kScColW * 128 + 32 * pq + lane], __uint_as_float(cb[0]));
+                    atomicAdd(&sc[kScColZ * 128 + 32 * pq + lane], __uint_as_float(cb[0]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) om[j] = od[j] = 0u;
@@ -349,19 +392,18 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                     *reinterpret_cast<uint4*>(smem + kOffM + off) = make_uint4(om[4 * c4], om[4 * c4 + 1], om[4 * c4 + 2], om[4 * c4 + 3]);
                     *reinterpret_cast<uint4*>(smem + kOffDcb + off) = make_uint4(od[4 * c4], od[4 * c4 + 1], od[4 * c4 + 2], od[4 * c4 + 3]);
                 }
-                // the scaled input of the state terms: k_s dt_s x_s (dM has been formed from dt_s x_s already)
-                const float ks = sc[kScK * 128 + row];
+                // the scaled input of the state terms: k_s sc_s x_s (dM has been formed from x_s already)
+                const float ks = sc[kScK * 128 + row] * sc[kScSc * 128 + row];
 #pragma unroll
                 for (int c2 = 0; c2 < 2; ++c2) {
-                    const uint32_t off = sw128_offset(row, 2 * pq + c2);
-                    uint4 v = *reinterpret_cast<const uint4*>(smem + kOffX + off);
-                    uint32_t* w = &v.x;
+                    const uint32_t* xs = &xr[c2].x;
+                    uint32_t w[4];
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {
-                        const float2 f = unpack_bf16x2(w[m]);
+                        const float2 f = unpack_bf16x2(xs[m]);
                         w[m] = pack_bf16x2(f.x * ks, f.y * ks);
                     }
-                    *reinterpret_cast<uint4*>(smem + kOffX + off) = v;
+                    *reinterpret_cast<uint4*>(smem + kOffX + sw128_offset(row, 2 * pq + c2)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
             tc_fence_before();
@@ -386,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
 #pragma unroll 1
                     for (int k = 0; k < 4; ++k) umma_ss(tmem + kColDC, desc_advance(dy_, k * 32), desc_advance(dh_, k * 32), id_kk, true);
                 }
-                // dB = dCB^T C + (k dt X) dh^T
+                // dB = dCB^T C + (k sc X) dh^T
                 {
                     const uint64_t da_ = umma_desc_mnmajor(dcb_sm, kPanel), dc_ = umma_desc_mnmajor(c_sm, kPanel);
 #pragma unroll 1
@@ -395,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
 #pragma unroll 1
                     for (int k = 0; k < 4; ++k) umma_ss(tmem + kColDB, desc_advance(dx_, k * 32), desc_advance(dh_, k * 32), id_kk, true);
                 }
-                // G = M^T dY, Gi = B dh, dhC = C^T (e dY)
+                // G = M^T dY, Gi = B dh, dhC = C^T (e dY), Y2 = C h_in^T
                 {
                     const uint64_t dm_ = umma_desc_mnmajor(m_sm, kPanel), dy_ = umma_desc_mnmajor(dy_sm, kPanel);
 #pragma unroll 1
@@ -431,15 +473,15 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                 for (int c4 = 0; c4 < 8; ++c4)
                     *reinterpret_cast<uint4*>(smem + kOffStB + row * kRowC + pq * 128 + c4 * 16) =
                         make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
-                // dx and the direct part of ddt: 16 columns of row `row`
+                // dx: 16 columns of row `row`; dy . Y2 and x . Gi for the decay / scale gradients
                 uint32_t gg[16], gi[16], dc16[16], y2[16];
                 tmem_ld16(lane_addr + kColG + 16 * pq, gg);
                 tmem_ld16(lane_addr + kColGi + 16 * pq, gi);
                 tmem_ld16(lane_addr + kColDhC + 16 * pq, dc16);
                 tmem_ld16(lane_addr + kColY2 + 16 * pq, y2);
                 tmem_wait_ld();
-                const float dts = sc[kScDt * 128 + row], ks = sc[kScK * 128 + row];
-                float pd = 0.f, pin = 0.f, pgi = 0.f, dxo[16];   // direct ddt; dy . Y2; x . Gi
+                const float ks = sc[kScK * 128 + row] * sc[kScSc * 128 + row];
+                float pin = 0.f, pgi = 0.f, dxo[16];
 #pragma unroll
                 for (int c2 = 0; c2 < 2; ++c2) {
                     const uint32_t* xs = &xr[c2].x;
@@ -448,28 +490,27 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                     for (int m = 0; m < 4; ++m) {
                         const float2 xf = unpack_bf16x2(xs[m]), yf = unpack_bf16x2(ys[m]);
                         const int j = 8 * c2 + 2 * m;
-                        const float g0 = fmaf(ks, __uint_as_float(gi[j]), __uint_as_float(gg[j]));
-                        const float g1 = fmaf(ks, __uint_as_float(gi[j + 1]), __uint_as_float(gg[j + 1]));
-                        pd = fmaf(xf.x, g0, pd);
-                        pd = fmaf(xf.y, g1, pd);
                         pin = fmaf(yf.x, __uint_as_float(y2[j]), pin);
                         pin = fmaf(yf.y, __uint_as_float(y2[j + 1]), pin);
                         pgi = fmaf(xf.x, __uint_as_float(gi[j]), pgi);
                         pgi = fmaf(xf.y, __uint_as_float(gi[j + 1]), pgi);
-                        dxo[j] = fmaf(dts, g0, dskip * yf.x);
-                        dxo[j + 1] = fmaf(dts, g1, dskip * yf.y);
-                        dd_acc = fmaf(xf.x, yf.x, dd_acc);
-                        dd_acc = fmaf(xf.y, yf.y, dd_acc);
+                        dxo[j] = fmaf(ks, __uint_as_float(gi[j]), __uint_as_float(gg[j]));
+                        dxo[j + 1] = fmaf(ks, __uint_as_float(gi[j + 1]), __uint_as_float(gg[j + 1]));
+                        if (kMode == 0) {
+                            dxo[j] = fmaf(dskip, yf.x, dxo[j]);
+                            dxo[j + 1] = fmaf(dskip, yf.y, dxo[j + 1]);
+                            dd_acc = fmaf(xf.x, yf.x, dd_acc);
+                            dd_acc = fmaf(xf.y, yf.y, dd_acc);
+                        }
                     }
                 }
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4)
                     *reinterpret_cast<float4*>(smem + kOffStX + row * kRowX + pq * 64 + c4 * 16) =
                         make_float4(dxo[4 * c4], dxo[4 * c4 + 1], dxo[4 * c4 + 2], dxo[4 * c4 + 3]);
-                // the readout term joins the row sum of W this thread stored in the mask pass
+                // the readout term joins the weighted row sum of Z this thread stored in the mask pass
                 sc[(kScPa + pq) * 128 + row] += sc[kScE * 128 + row] * pin;
-                sc[(kScPb + pq) * 128 + row] = ks * dts * pgi;
-                sc[(kScPd + pq) * 128 + row] = pd;
+                sc[(kScPgi + pq) * 128 + row] = pgi;
                 // the state gradient entering the tile
                 const float decay = ex2(sc[kScCum * 128 + 127]);
 #pragma unroll
@@ -481,22 +522,31 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                 fence_proxy_async_smem();
                 __syncthreads();
                 if (lane == 0) atomicAdd(&red[0], dot * decay);
-                // gradient rows leave: dx by a bulk copy, dB / dC by a bulk reduce-add into the group's rows
+                // gradient rows leave: dx by a bulk copy, dB / dC by a bulk reduce-add into the group's rows (a
+                // plain copy when every head has its own)
                 if (tid < 128 && tid < left) {
                     const int64_t tok = (int64_t)b * prm.S + s0 + tid;
                     bulk_store_row(prm.dx + (tok * prm.H + h) * P, smem + kOffStX + tid * kRowX, P * 4);
-                    bulk_add_row(prm.dc + (tok * prm.G + g) * R, smem + kOffStC + tid * kRowC, R * 4);
-                    bulk_add_row(prm.db + (tok * prm.G + g) * R, smem + kOffStB + tid * kRowC, R * 4);
+                    if (prm.plain_bc) {
+                        bulk_store_row(prm.dc + (tok * prm.G + g) * R, smem + kOffStC + tid * kRowC, R * 4);
+                        bulk_store_row(prm.db + (tok * prm.G + g) * R, smem + kOffStB + tid * kRowC, R * 4);
+                    } else {
+                        bulk_add_row(prm.dc + (tok * prm.G + g) * R, smem + kOffStC + tid * kRowC, R * 4);
+                        bulk_add_row(prm.db + (tok * prm.G + g) * R, smem + kOffStB + tid * kRowC, R * 4);
+                    }
                     tma_store_commit();
                 }
                 __syncthreads();
-                // ---- suffix sum of dc over the tile -> d(dt A); ddt and dA (warp 0)
+                // ---- scalar gradients (warp 0, four consecutive rows per lane):
+                //   d(log decay)_row = sum_{t >= row} [rowsum_t - sc_t colZ_t] + sum_{s < row} k_s sc_s (x_s . Gi_s)
+                //                      + exp(c_end) <dh, h_in>
+                //   d(column scale)_row = colZ_row + k_row (x_row . Gi_row);  d(same-step weight)_row = Pgs_row
                 if (warp == 0) {
-                    float v[4], u[4], run = 0.f, prun = 0.f;
+                    float v[4], u[4], ds[4], run = 0.f, prun = 0.f;
 #pragma unroll
                     for (int k = 3; k >= 0; --k) {
                         const int t = lane * 4 + k;
-                        float dcv = -sc[kScColW * 128 + t];
+                        float dcv = -sc[kScSc * 128 + t] * sc[kScColZ * 128 + t];
 #pragma unroll
                         for (int w = 0; w < 4; ++w) dcv += sc[(kScPa + w) * 128 + t];
                         run += dcv;
@@ -505,9 +555,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {   // exclusive prefix of the state-input terms
                         const int t = lane * 4 + k;
-                        u[k] = prun;
+                        float pg = 0.f;
 #pragma unroll
-                        for (int w = 0; w < 4; ++w) prun += sc[(kScPb + w) * 128 + t];
+                        for (int w = 0; w < 4; ++w) pg += sc[(kScPgi + w) * 128 + t];
+                        pg *= sc[kScK * 128 + t];
+                        ds[k] = sc[kScColZ * 128 + t] + pg;
+                        u[k] = prun;
+                        prun = fmaf(sc[kScSc * 128 + t], pg, prun);
                     }
                     float incl = run, pincl = prun;   // suffix / prefix over lanes
 #pragma unroll
@@ -518,21 +572,40 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                         if (lane >= o) pincl += up;
                     }
                     const float after = incl - run + (pincl - prun) + red[0];   // lanes above, lanes below, exp(c_end) <dh, h_in>
-                    float dal = 0.f;
+                    if (kMode == 0) {
+                        float dal = 0.f;
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int t = lane * 4 + k;
-                        const float dda = v[k] + u[k] + after;
-                        const float dts2 = sc[kScDt * 128 + t];
-                        float pdv = 0.f;
+                        for (int k = 0; k < 4; ++k) {
+                            const int t = lane * 4 + k;
+                            const float dda = v[k] + u[k] + after;
+                            if (t < left)
+                                prm.ddt[((int64_t)b * prm.S + s0 + t) * prm.H + h] = fmaf(ah, dda, ds[k] + sc[kScPgs * 128 + t]);
+                            dal = fmaf(sc[kScSc * 128 + t], dda, dal);
+                        }
 #pragma unroll
-                        for (int w = 0; w < 4; ++w) pdv += sc[(kScPd + w) * 128 + t];
-                        if (t < left) prm.ddt[((int64_t)b * prm.S + s0 + t) * prm.H + h] = fmaf(ah, dda, pdv);
-                        dal = fmaf(dts2, dda, dal);
+                        for (int o = 16; o > 0; o >>= 1) dal += __shfl_xor_sync(0xffffffffu, dal, o);
+                        da_acc += dal;
+                    } else {
+                        // rows of a step are consecutive and never straddle lanes (1, 2 or 4 rows per step)
+                        const int m = 1 << log2m;
+#pragma unroll
+                        for (int k0 = 0; k0 < 4; ++k0) {
+                            if ((k0 & (m - 1)) != 0) continue;
+                            const int t = lane * 4 + k0;
+                            if (t >= left) continue;
+                            float dsc = 0.f, dg = 0.f;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k)
+                                if (k >= k0 && k < k0 + m) {
+                                    dsc += ds[k];
+                                    dg += sc[kScPgs * 128 + lane * 4 + k];
+                                }
+                            const int64_t o = ((int64_t)b * prm.St + ((s0 + t) >> log2m)) * prm.H + h;
+                            prm.dda[o] = v[k0] + u[k0] + after;
+                            if (prm.dscale) prm.dscale[o] = dsc;
+                            if (prm.dgamma) prm.dgamma[o] = dg;
+                        }
                     }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) dal += __shfl_xor_sync(0xffffffffu, dal, o);
-                    da_acc += dal;
                 }
                 // the staging tiles must have been read before the next tile's loads overwrite them
                 if (tid < 128) tma_store_wait_read<0>();
@@ -550,11 +623,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_bwd_tc_kernel(const __grid_c
                 if (lane == 0) atomicAdd(prm.handoff_flags + cta, 1);
             }
         }
-        if (tid == 0) atomicAdd(prm.da + h, da_acc);
-        if (prm.dd != nullptr) {
+        if (kMode == 0) {
+            if (tid == 0) atomicAdd(prm.d_a + h, da_acc);
+            if (prm.dd != nullptr) {
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) dd_acc += __shfl_xor_sync(0xffffffffu, dd_acc, o);
-            if (lane == 0) atomicAdd(prm.dd + h, dd_acc);
+                for (int o = 16; o > 0; o >>= 1) dd_acc += __shfl_xor_sync(0xffffffffu, dd_acc, o);
+                if (lane == 0) atomicAdd(prm.dd + h, dd_acc);
+            }
         }
     }
     goto done;
@@ -589,14 +664,15 @@ struct BwdLayout {
     size_t off_fwd, off_cs, off_y, off_hf, off_flags, off_slots, total;
 };
 
-BwdLayout bwd_layout(const bm_ssd2_bwd_args* a, const bm_ssd2_fwd_args* f) {
+// rows = sequence length of the kernel's row axis (tokens, or fused time x rank rows)
+BwdLayout bwd_layout(int batch, int64_t rows, int nheads, size_t fwd_bytes) {
     BwdLayout l{};
-    const size_t nt = (size_t)cdiv(a->seqlen, T);
+    const size_t nt = (size_t)cdiv(rows, T);
     l.off_fwd = 0;   // the forward kernel's status word doubles as this pass's
-    l.off_cs = align_up(l.off_fwd + ssd2_workspace_bytes(f), 256);
-    l.off_y = align_up(l.off_cs + (size_t)a->batch * nt * a->nheads * P * R * sizeof(float), 256);
-    l.off_hf = align_up(l.off_y + (size_t)a->batch * a->seqlen * a->nheads * P * 2, 256);
-    l.off_flags = align_up(l.off_hf + (size_t)a->batch * a->nheads * P * R * sizeof(float), 256);
+    l.off_cs = align_up(l.off_fwd + fwd_bytes, 256);
+    l.off_y = align_up(l.off_cs + (size_t)batch * nt * nheads * P * R * sizeof(float), 256);
+    l.off_hf = align_up(l.off_y + (size_t)batch * rows * nheads * P * 2, 256);
+    l.off_flags = align_up(l.off_hf + (size_t)batch * nheads * P * R * sizeof(float), 256);
     l.off_slots = l.off_flags + align_up((size_t)(sm_count() + 1) * sizeof(int), 256);
     l.total = l.off_slots + (size_t)(sm_count() + 1) * P * R * sizeof(float);
     return l;
@@ -608,6 +684,64 @@ bm_ssd2_fwd_args forward_args(const bm_ssd2_bwd_args* a) {
     f.ngroups = a->ngroups, f.chunk_len = T, f.dtype = a->dtype, f.path = BM_PATH_TENSOR_SINGLE;
     f.x = a->x, f.dt = a->dt, f.a = a->a, f.b = a->b, f.c = a->c, f.d = a->d, f.h0 = a->h0;
     return f;
+}
+
+bm_ssd3_fwd_args forward_args3(const bm_ssd3_bwd_args* a) {
+    bm_ssd3_fwd_args f{};
+    f.batch = a->batch, f.seqlen = a->seqlen, f.nheads = a->nheads, f.headdim = a->headdim, f.state_rank = a->state_rank;
+    f.mimo_rank = a->mimo_rank, f.chunk_len = a->chunk_len, f.dtype = a->dtype, f.path = BM_PATH_TENSOR;
+    f.v = a->v, f.da = a->da, f.b = a->b, f.c = a->c, f.gamma = a->gamma, f.scale = a->scale, f.h0 = a->h0;
+    return f;
+}
+
+int log2_of(int v) {
+    int l = 0;
+    while ((1 << l) < v) ++l;
+    return (1 << l) == v ? l : -1;
+}
+
+// Tensor maps, shares and the launch, common to both families.  `rows` = length of the row axis.
+template <int kMode>
+int32_t launch(BwdParams& prm, const void* x, const void* dy, const void* bmat, const void* cmat, int batch, int64_t rows,
+               int nheads, int ngroups, char* w, const BwdLayout& l, cudaStream_t stream) {
+    const char* err = nullptr;
+    const uint64_t S = rows, H = nheads, G = ngroups, B = batch;
+    const uint32_t box[4] = {64, 1, (uint32_t)T, 1};
+    {
+        const uint64_t dims[4] = {(uint64_t)P, H, S, B};
+        const uint64_t strides[3] = {(uint64_t)P * 2, H * P * 2, S * H * P * 2};
+        if (!make_tensor_map_bf16(&prm.tm_x, x, 4, dims, strides, box, 128, &err) ||
+            !make_tensor_map_bf16(&prm.tm_dy, dy, 4, dims, strides, box, 128, &err))
+            return fail(BM_ERR_CUDA, "tensor map (x/dy): %s", err);
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)R, G, S, B};
+        const uint64_t strides[3] = {(uint64_t)R * 2, G * R * 2, S * G * R * 2};
+        if (!make_tensor_map_bf16(&prm.tm_b, bmat, 4, dims, strides, box, 128, &err) ||
+            !make_tensor_map_bf16(&prm.tm_c, cmat, 4, dims, strides, box, 128, &err))
+            return fail(BM_ERR_CUDA, "tensor map (b/c): %s", err);
+    }
+    prm.status = reinterpret_cast<int*>(w);
+    prm.B = batch, prm.S = (int)rows, prm.H = nheads, prm.G = ngroups;
+    prm.NT = (int)cdiv(rows, T);
+    prm.num_units = batch * nheads;
+    prm.plain_bc = ngroups == nheads ? 1 : 0;
+    cudaError_t e = cudaFuncSetAttribute(ssd_bwd_tc_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd_bwd_tc_kernel)");
+    if (!prm.plain_bc) {
+        const size_t grp = (size_t)batch * rows * ngroups * R * sizeof(float);
+        if (int32_t r = check_cuda(cudaMemsetAsync(prm.db, 0, grp, stream), "cudaMemsetAsync(db)")) return r;
+        if (int32_t r = check_cuda(cudaMemsetAsync(prm.dc, 0, grp, stream), "cudaMemsetAsync(dc)")) return r;
+    }
+    const int grid = prm.num_units < sm_count() ? prm.num_units : sm_count();
+    if ((int64_t)prm.num_units * prm.NT > INT32_MAX) return fail(BM_ERR_UNSUPPORTED, "more than 2^31 tiles");
+    prm.share_q = (int)((int64_t)prm.num_units * prm.NT / grid);
+    prm.share_r = (int)((int64_t)prm.num_units * prm.NT % grid);
+    prm.handoff_flags = reinterpret_cast<int*>(w + l.off_flags);
+    prm.handoff = reinterpret_cast<float*>(w + l.off_slots);
+    if (int32_t r = check_cuda(cudaMemsetAsync(prm.handoff_flags, 0, l.off_slots - l.off_flags, stream), "cudaMemsetAsync(flags)")) return r;
+    ssd_bwd_tc_kernel<kMode><<<grid, kThreads, kSmemBytes, stream>>>(prm);
+    return check_launch("ssd_bwd_tc_kernel");
 }
 
 }  // namespace
@@ -623,64 +757,66 @@ bool ssd2_bwd_supported(const bm_ssd2_bwd_args* a) { return ssd2_bwd_why_not(a) 
 
 size_t ssd2_bwd_workspace_bytes(const bm_ssd2_bwd_args* a) {
     const bm_ssd2_fwd_args f = forward_args(a);
-    return bwd_layout(a, &f).total;
+    return bwd_layout(a->batch, a->seqlen, a->nheads, ssd2_workspace_bytes(&f)).total;
 }
 
 int32_t ssd2_bwd_run(const bm_ssd2_bwd_args* a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     bm_ssd2_fwd_args f = forward_args(a);
-    const BwdLayout l = bwd_layout(a, &f);
+    const BwdLayout l = bwd_layout(a->batch, a->seqlen, a->nheads, ssd2_workspace_bytes(&f));
     if (workspace == nullptr || workspace_bytes < l.total)
         return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, l.total);
     char* w = static_cast<char*>(workspace);
-    // forward pass for the state entering every tile (and the final state)
+    // forward pass for the state entering every tile
     f.y = w + l.off_y;
     f.h_final = reinterpret_cast<float*>(w + l.off_hf);
     f.chunk_states = reinterpret_cast<float*>(w + l.off_cs);
     if (int32_t e = ssd2_run(&f, w + l.off_fwd, l.off_cs - l.off_fwd, stream)) return e;
 
     BwdParams prm{};
-    const char* err = nullptr;
-    const uint64_t S = a->seqlen, H = a->nheads, G = a->ngroups, B = a->batch;
-    const uint32_t box[4] = {64, 1, (uint32_t)T, 1};
-    {
-        const uint64_t dims[4] = {(uint64_t)P, H, S, B};
-        const uint64_t strides[3] = {(uint64_t)P * 2, H * P * 2, S * H * P * 2};
-        if (!make_tensor_map_bf16(&prm.tm_x, a->x, 4, dims, strides, box, 128, &err) ||
-            !make_tensor_map_bf16(&prm.tm_dy, a->dy, 4, dims, strides, box, 128, &err))
-            return fail(BM_ERR_CUDA, "tensor map (x/dy): %s", err);
-    }
-    {
-        const uint64_t dims[4] = {(uint64_t)R, G, S, B};
-        const uint64_t strides[3] = {(uint64_t)R * 2, G * R * 2, S * G * R * 2};
-        if (!make_tensor_map_bf16(&prm.tm_b, a->b, 4, dims, strides, box, 128, &err) ||
-            !make_tensor_map_bf16(&prm.tm_c, a->c, 4, dims, strides, box, 128, &err))
-            return fail(BM_ERR_CUDA, "tensor map (b/c): %s", err);
-    }
-    prm.dt = a->dt, prm.a = a->a, prm.d = a->d;
+    prm.sc = a->dt, prm.a = a->a, prm.d = a->d;
     prm.chunk_states = f.chunk_states, prm.dh_final = a->dh_final;
-    prm.x = static_cast<const __nv_bfloat16*>(a->x), prm.dy = static_cast<const __nv_bfloat16*>(a->dy);
-    prm.dx = a->dx, prm.ddt = a->ddt, prm.da = a->da, prm.db = a->db, prm.dc = a->dc, prm.dd = a->dd, prm.dh0 = a->dh0;
-    prm.status = reinterpret_cast<int*>(w);
-    prm.B = a->batch, prm.S = a->seqlen, prm.H = a->nheads, prm.G = a->ngroups;
-    prm.NT = (int)cdiv(a->seqlen, T);
-    prm.num_units = a->batch * a->nheads;
-    cudaError_t e = cudaFuncSetAttribute(ssd2_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
-    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(ssd2_bwd_tc_kernel)");
-    const size_t grp = (size_t)a->batch * a->seqlen * a->ngroups * R * sizeof(float);
-    if (int32_t r = check_cuda(cudaMemsetAsync(a->db, 0, grp, stream), "cudaMemsetAsync(db)")) return r;
-    if (int32_t r = check_cuda(cudaMemsetAsync(a->dc, 0, grp, stream), "cudaMemsetAsync(dc)")) return r;
+    prm.dx = a->dx, prm.ddt = a->ddt, prm.d_a = a->da, prm.db = a->db, prm.dc = a->dc, prm.dd = a->dd, prm.dh0 = a->dh0;
+    prm.St = a->seqlen, prm.log2m = 0;
     if (int32_t r = check_cuda(cudaMemsetAsync(a->da, 0, (size_t)a->nheads * sizeof(float), stream), "cudaMemsetAsync(da)")) return r;
     if (a->dd != nullptr)
         if (int32_t r = check_cuda(cudaMemsetAsync(a->dd, 0, (size_t)a->nheads * sizeof(float), stream), "cudaMemsetAsync(dd)")) return r;
-    const int grid = prm.num_units < sm_count() ? prm.num_units : sm_count();
-    if ((int64_t)prm.num_units * prm.NT > INT32_MAX) return fail(BM_ERR_UNSUPPORTED, "more than 2^31 tiles");
-    prm.share_q = (int)((int64_t)prm.num_units * prm.NT / grid);
-    prm.share_r = (int)((int64_t)prm.num_units * prm.NT % grid);
-    prm.handoff_flags = reinterpret_cast<int*>(w + l.off_flags);
-    prm.handoff = reinterpret_cast<float*>(w + l.off_slots);
-    if (int32_t r = check_cuda(cudaMemsetAsync(prm.handoff_flags, 0, l.off_slots - l.off_flags, stream), "cudaMemsetAsync(flags)")) return r;
-    ssd2_bwd_tc_kernel<<<grid, kThreads, kSmemBytes, stream>>>(prm);
-    return check_launch("ssd2_bwd_tc_kernel");
+    return launch<0>(prm, a->x, a->dy, a->b, a->c, a->batch, a->seqlen, a->nheads, a->ngroups, w, l, stream);
+}
+
+const char* ssd3_bwd_why_not(const bm_ssd3_bwd_args* a) {
+    if (a->dtype != BM_DTYPE_BF16) return "activations must be bf16";
+    if (a->headdim != P) return "headdim must be 64";
+    if (a->state_rank != R) return "state_rank must be 128";
+    if (log2_of(a->mimo_rank) < 0 || a->mimo_rank > 4) return "mimo_rank must be 1, 2 or 4";
+    return nullptr;
+}
+
+bool ssd3_bwd_supported(const bm_ssd3_bwd_args* a) { return ssd3_bwd_why_not(a) == nullptr; }
+
+size_t ssd3_bwd_workspace_bytes(const bm_ssd3_bwd_args* a) {
+    const bm_ssd3_fwd_args f = forward_args3(a);
+    return bwd_layout(a->batch, (int64_t)a->seqlen * a->mimo_rank, a->nheads, ssd3_workspace_bytes(&f)).total;
+}
+
+int32_t ssd3_bwd_run(const bm_ssd3_bwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    bm_ssd3_fwd_args f = forward_args3(a);
+    const int64_t rows = (int64_t)a->seqlen * a->mimo_rank;
+    const BwdLayout l = bwd_layout(a->batch, rows, a->nheads, ssd3_workspace_bytes(&f));
+    if (workspace == nullptr || workspace_bytes < l.total)
+        return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, l.total);
+    char* w = static_cast<char*>(workspace);
+    f.y = w + l.off_y;
+    f.h_final = reinterpret_cast<float*>(w + l.off_hf);
+    float* cs = reinterpret_cast<float*>(w + l.off_cs);
+    if (int32_t e = ssd3_run(&f, single, w + l.off_fwd, l.off_cs - l.off_fwd, stream, cs)) return e;
+
+    BwdParams prm{};
+    prm.sc = single ? a->scale : nullptr, prm.gamma = single ? a->gamma : nullptr, prm.da = a->da;
+    prm.chunk_states = cs, prm.dh_final = a->dh_final;
+    prm.dx = a->dv, prm.dda = a->dda, prm.dgamma = single ? a->dgamma : nullptr, prm.dscale = single ? a->dscale : nullptr;
+    prm.db = a->db, prm.dc = a->dc, prm.dh0 = a->dh0;
+    prm.St = a->seqlen, prm.log2m = log2_of(a->mimo_rank);
+    return launch<1>(prm, a->v, a->dy, a->b, a->c, a->batch, rows, a->nheads, a->nheads, w, l, stream);
 }
 
 }  // namespace tc

@@ -1068,7 +1068,8 @@ size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a) {
     return n;
 }
 
-int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                 float* chunk_states) {
     if (workspace == nullptr || workspace_bytes < ssd3_workspace_bytes(a))
         return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes,
                     ssd3_workspace_bytes(a));
@@ -1108,10 +1109,10 @@ int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t
     }
     prm.dt = single ? a->scale : nullptr, prm.da = a->da, prm.gamma = single ? a->gamma : nullptr;
     prm.a = nullptr, prm.d = nullptr, prm.h0 = a->h0, prm.dt_bias = nullptr;
-    prm.h_final = a->h_final, prm.chunk_states = nullptr;
+    prm.h_final = a->h_final, prm.chunk_states = chunk_states;
     ws_head_pointers(workspace, prm);
     prm.B = a->batch, prm.S = (int)S, prm.St = a->seqlen, prm.log2m = log2_exact(a->mimo_rank);
-    prm.H = a->nheads, prm.G = a->nheads, prm.Q = T, prm.NC = 1;
+    prm.H = a->nheads, prm.G = a->nheads, prm.Q = T, prm.NC = (int)cdiv((int64_t)S, T);
     prm.tiles_per_unit = (int)cdiv((int64_t)S, T);
     prm.num_units = a->batch * a->nheads;
     prm.stall_loads = 0;

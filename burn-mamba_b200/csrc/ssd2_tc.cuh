@@ -33,7 +33,15 @@ int32_t ssd2_bwd_run(const bm_ssd2_bwd_args* a, void* workspace, size_t workspac
 bool ssd3_supported(const bm_ssd3_fwd_args* a);
 const char* ssd3_why_not(const bm_ssd3_fwd_args* a);
 size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a);
-int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+// chunk_states (optional, internal): [b, tiles, h, p, r] float32, the state entering every 128-row tile.
+int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream,
+                 float* chunk_states = nullptr);
+
+// Backward of the Mamba-3 cores on the tensor cores (same kernel as the Mamba-2 backward, on the fused axis).
+bool ssd3_bwd_supported(const bm_ssd3_bwd_args* a);
+const char* ssd3_bwd_why_not(const bm_ssd3_bwd_args* a);
+size_t ssd3_bwd_workspace_bytes(const bm_ssd3_bwd_args* a);
+int32_t ssd3_bwd_run(const bm_ssd3_bwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 }  // namespace tc
 }  // namespace bm

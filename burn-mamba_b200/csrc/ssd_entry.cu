@@ -219,7 +219,9 @@ extern "C" int32_t bm_ssd2_bwd(const bm_ssd2_bwd_args* a, void* ws, size_t ws_by
 
 extern "C" size_t bm_ssd3_bwd_workspace_bytes(const bm_ssd3_bwd_args* a) {
     if (a == nullptr || a->batch <= 0 || a->seqlen <= 0 || a->nheads <= 0 || a->chunk_len <= 0) return 0;
-    return exact::bwd_workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, false);
+    size_t n = exact::bwd_workspace_bytes(a->batch, a->seqlen, a->nheads, a->headdim, a->state_rank, a->chunk_len, false);
+    if (a->path != BM_PATH_EXACT && tc::ssd3_bwd_supported(a)) n = std::max(n, tc::ssd3_bwd_workspace_bytes(a));
+    return n;
 }
 
 static int32_t ssd3_bwd(const bm_ssd3_bwd_args* a, void* ws, size_t ws_bytes, void* stream, bool single) {
@@ -234,6 +236,12 @@ static int32_t ssd3_bwd(const bm_ssd3_bwd_args* a, void* ws, size_t ws_bytes, vo
     BM_OPTIONAL_PTR(a->h0); BM_OPTIONAL_PTR(a->dh_final);
     if (single) {
         BM_REQUIRE_PTR(a->gamma); BM_REQUIRE_PTR(a->scale); BM_REQUIRE_PTR(a->dgamma); BM_REQUIRE_PTR(a->dscale);
+    }
+    BM_REQUIRE(a->path == BM_PATH_AUTO || a->path == BM_PATH_EXACT || a->path == BM_PATH_TENSOR, BM_ERR_UNSUPPORTED,
+               "path must be auto, exact or tensor");
+    if (a->path != BM_PATH_EXACT) {
+        if (tc::ssd3_bwd_supported(a)) return tc::ssd3_bwd_run(a, single, ws, ws_bytes, static_cast<cudaStream_t>(stream));
+        if (a->path == BM_PATH_TENSOR) return fail(BM_ERR_UNSUPPORTED, "tensor-core backward: %s", tc::ssd3_bwd_why_not(a));
     }
     exact::BwdParams bp{};
     exact::Params& p = bp.fwd;

@@ -368,8 +368,9 @@ def ssd2_bwd(x, dt, a, b, c, d, h0, dy, dh_final=None, chunk_len=256, path="auto
     return out
 
 
-def ssd3_bwd(v, da, b, c, gamma, scale, h0, dy, dh_final=None, chunk_len=64, single=True):
-    """Mamba-3 SSD backward.  single: returns also dgamma / dscale.  All gradients float32."""
+def ssd3_bwd(v, da, b, c, gamma, scale, h0, dy, dh_final=None, chunk_len=64, single=True, path="auto", check_status=False):
+    """Mamba-3 SSD backward.  single: returns also dgamma / dscale.  All gradients float32.
+    path: "auto" (tensor-core kernel for bf16, headdim 64, state_rank 128, MIMO rank 1 / 2 / 4), "exact", "tensor"."""
     bsz, s, m, h, p = v.shape
     r = b.shape[-1]
     act = v.dtype
@@ -389,8 +390,10 @@ def ssd3_bwd(v, da, b, c, gamma, scale, h0, dy, dh_final=None, chunk_len=64, sin
                             gamma=_ptr(gamma) if single else None, scale=_ptr(scale) if single else None, h0=_ptr(h0),
                             dy=_ptr(dy), dh_final=_ptr(dh_final), dv=_ptr(out["dv"]), dda=_ptr(out["dda"]),
                             db=_ptr(out["db"]), dc=_ptr(out["dc"]), dgamma=_ptr(out.get("dgamma")),
-                            dscale=_ptr(out.get("dscale")), dh0=_ptr(out["dh0"]))
+                            dscale=_ptr(out.get("dscale")), dh0=_ptr(out["dh0"]), path=PATHS[path])
     ws = _workspace(lib.bm_ssd3_bwd_workspace_bytes(C.byref(args)), v.device)
     fn = lib.bm_ssd3_single_bwd if single else lib.bm_ssd3_double_bwd
     check(fn(C.byref(args), ws.data_ptr(), ws.numel(), _stream()), "bm_ssd3_bwd")
+    if check_status:
+        check(lib.bm_workspace_status(ws.data_ptr(), _stream()), "bm_workspace_status")
     return out

@@ -368,6 +368,9 @@ typedef struct {
     float* dgamma;            /* [b, s, h] (single) */
     float* dscale;            /* [b, s, h] (single) */
     float* dh0;               /* [b, h, p, r] */
+    int32_t path;             /* bm_path: AUTO = tensor-core kernel when dtype / shape allow it (bf16, headdim 64,
+                                 state_rank 128, mimo_rank 1, 2 or 4), else the exact path; EXACT and TENSOR force one */
+    int32_t reserved;         /* 0 */
 } bm_ssd3_bwd_args;
 
 size_t bm_ssd3_bwd_workspace_bytes(const bm_ssd3_bwd_args* args);

@@ -48,6 +48,7 @@ pub struct BmSsd3BwdArgs {
     pub gamma: *const f32, pub scale: *const f32, pub h0: *const f32, pub dy: *const c_void,
     pub dh_final: *const f32, pub dv: *mut f32, pub dda: *mut f32, pub db: *mut f32, pub dc: *mut f32,
     pub dgamma: *mut f32, pub dscale: *mut f32, pub dh0: *mut f32,
+    pub path: i32, pub reserved: i32,
 }
 
 #[repr(C)]

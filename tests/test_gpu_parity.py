@@ -465,6 +465,42 @@ def test_ssd3_backward_matches_autodiff_oracle(bm, b, s, h, p, r, m, Q):
         assert _grad_close(got[k], want[k]), ("double", k, rel_l2(host(got[k]), want[k]))
 
 
+@pytest.mark.parametrize("b,s,h,m", [(1, 128, 1, 1), (1, 64, 2, 2), (2, 160, 2, 4), (1, 75, 3, 4)])
+def test_ssd3_backward_tensor_path_matches_autodiff_oracle(bm, b, s, h, m):
+    """The tcgen05 backward of the Mamba-3 cores on the fused (time x rank) axis against autodiff of the serial
+    forward on the same bf16-rounded inputs: single (with d_gamma, d_scale) and the generic core, MIMO ranks
+    1 / 2 / 4, ragged lengths, initial state and dh_final."""
+    from oracle import backward
+    cfg = inputs.ssd3_single(seed=70 + s, batch=b, seqlen=s, nheads=h, headdim=64, state_rank=128, mimo_rank=m, h0_std=0.2)
+    dt = torch.bfloat16
+    v, bb, cc = (q(cfg[k], dt) for k in ("v", "b", "c"))
+    rng = np.random.default_rng(3)
+    dy = q(rng.standard_normal(v.shape).astype(np.float32), dt)
+    dhf = rng.standard_normal(cfg["h0"].shape).astype(np.float32)
+    args = (dev(v, dt), dev(cfg["da"]), dev(bb, dt), dev(cc, dt), dev(cfg["gamma"]), dev(cfg["scale"]), dev(cfg["h0"]),
+            dev(dy, dt), dev(dhf))
+    for single, keys in ((True, ("dv", "dda", "db", "dc", "dgamma", "dscale", "dh0")), (False, ("dv", "dda", "db", "dc", "dh0"))):
+        want = backward.ssd3_grads(v, cfg["da"], bb, cc, cfg["gamma"], cfg["scale"], cfg["h0"], dy, dhf, 32, single=single)
+        got = bm.ops.ssd3_bwd(*args, chunk_len=32, single=single, path="tensor", check_status=True)
+        for k in keys:
+            assert rel_l2(host(got[k]), want[k]) <= 2e-2, (single, k, rel_l2(host(got[k]), want[k]))
+
+
+def test_ssd3_backward_tensor_path_cut_units_against_the_float32_backward(bm):
+    """More units than SMs with MIMO rank 4: units straddle CTAs, dh crosses through the workspace; every
+    gradient against the float32 backward on device."""
+    cfg = inputs.ssd3_single(seed=71, batch=2, seqlen=320, nheads=160, headdim=64, state_rank=128, mimo_rank=4, h0_std=0.1)
+    dt = torch.bfloat16
+    rng = np.random.default_rng(4)
+    dy = rng.standard_normal(cfg["v"].shape).astype(np.float32)
+    args = (dev(cfg["v"], dt), dev(cfg["da"]), dev(cfg["b"], dt), dev(cfg["c"], dt), dev(cfg["gamma"]), dev(cfg["scale"]),
+            dev(cfg["h0"]), dev(dy, dt), None)
+    got = bm.ops.ssd3_bwd(*args, chunk_len=64, single=True, path="tensor", check_status=True)
+    want = bm.ops.ssd3_bwd(*args, chunk_len=64, single=True, path="exact")
+    for k in ("dv", "dda", "db", "dc", "dgamma", "dscale", "dh0"):
+        assert rel_l2(host(got[k]), host(want[k])) <= 2e-2, (k, rel_l2(host(got[k]), host(want[k])))
+
+
 # ------------------------------------------------------------------ Mamba-2 SSD, two heads per CTA (opt-in kernel)
 def _pair_case(bm, cfg, Q, oracle=True):
     dt = torch.bfloat16
