@@ -97,6 +97,13 @@ struct alignas(64) BwdParams {
     int plain_bc;                // one head per group: dB / dC rows are stored, not reduce-added
 };
 
+// L2 prefetch of one tile of a 4-D tensor map / of one 128-byte line.
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* m, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(m), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ void bulk_store_row(float* dst, const void* src, uint32_t bytes) {
     asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
 }
@@ -202,6 +209,19 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 tma_load_4d(smem + kOffB + kPanel, &prm.tm_b, &bars->ld_full, 64, g, s0, b);
                 tma_load_4d(smem + kOffC, &prm.tm_c, &bars->ld_full, 0, g, s0, b);
                 tma_load_4d(smem + kOffC + kPanel, &prm.tm_c, &bars->ld_full, 64, g, s0, b);
+                if (i > i_lo) {   // the tile this CTA walks next: into L2 while this one is worked on
+                    tma_prefetch_4d(&prm.tm_x, 0, h, s0 - T, b);
+                    tma_prefetch_4d(&prm.tm_dy, 0, h, s0 - T, b);
+                    tma_prefetch_4d(&prm.tm_b, 0, g, s0 - T, b);
+                    tma_prefetch_4d(&prm.tm_b, 64, g, s0 - T, b);
+                    tma_prefetch_4d(&prm.tm_c, 0, g, s0 - T, b);
+                    tma_prefetch_4d(&prm.tm_c, 64, g, s0 - T, b);
+                }
+            }
+            if (i > i_lo && lane < 4) {   // and the state entering it: 64 rows of 512 bytes, 4 lines per row
+                const float* nx = prm.chunk_states + (((int64_t)b * prm.NT + i - 1) * prm.H + h) * P * R;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) prefetch_l2(nx + (int64_t)(warp * 4 + j) * R + lane * 32);
             }
             // ---- per-row scalars (warp 1): log2-domain cumulative decay and the factors derived from it
             if (warp == 1) {
