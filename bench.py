@@ -634,6 +634,14 @@ def _ssd3_legs(torch, bm, dev, rn, flush, hbm, tensor, sb):
     ms = _time_flushed(torch, fwd, 5, flush)
     tensor(f"ssd3_single_fwd (b{b} L2048 H32 P64 N128 m4 Q64, bf16, rotation from angles, {path} path)", ms, flops,
            "dense GEMM count of the fused (time x rank) axis")
+    if hasattr(bm.ops, "mamba3_bc_prep"):
+        # B / C from the projection's raw group columns to the rotated per-head tensors the slot takes, one kernel
+        braw, craw = rn(b, s, m * r, dt=bf), rn(b, s, m * r, dt=bf)
+        gam, bias = torch.ones(r, device=dev), 0.1 * rn(h, m, r)
+        ms = _time_flushed(torch, lambda: bm.ops.mamba3_bc_prep(braw, craw, gam, gam, bias, bias, angles=angles, rope_dim=r,
+                                                              pairwise=False, ngroups=1), 5, flush)
+        hbm(f"mamba3_bc_prep (norm + expand + bias + rotation, b{b} L2048 m4 g1 H32 N128, bf16)", ms,
+            2 * braw.numel() * 2 + angles.numel() * 4 + 2 * bb.numel() * 2)
     del angles
     dy = rn(b, s, m, h, p, dt=bf)
     bwd = lambda: bm.ops.ssd3_bwd(v, da, bb, cc, gamma, scale, None, dy, None, chunk_len=q, single=True)

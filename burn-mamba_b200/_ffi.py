@@ -84,6 +84,12 @@ class Ssd3BwdArgs(C.Structure):
                            "dgamma", "dscale", "dh0")] + [("path", _i32), ("reserved", _i32)]
 
 
+class Mamba3BcPrepArgs(C.Structure):
+    _fields_ = [(n, _i32) for n in ("batch", "seqlen", "mimo_rank", "ngroups", "nheads", "state_rank", "dtype", "raw_stride",
+                                    "rope_dim", "pairwise")] + [("eps", _f32), ("reserved", _i32)] + [
+        (n, _vp) for n in ("b_raw", "c_raw", "b_gamma", "c_gamma", "b_bias", "c_bias", "angles", "b_out", "c_out")]
+
+
 class AngleCumsumArgs(C.Structure):
     _fields_ = [(n, _i32) for n in ("batch", "seqlen", "nheads", "nangles")] + [
         ("range", _f32), ("rot", _vp), ("dt", _vp), ("prev", _vp), ("theta", _vp), ("last", _vp)]
@@ -114,6 +120,7 @@ SYMBOLS = {
     "bm_conv_step": (_i32, [C.POINTER(ConvStepArgs), _vp]),
     "bm_conv1d_silu_fwd": (_i32, [C.POINTER(Conv1dSiluArgs), _vp]),
     "bm_rmsnorm_gated": (_i32, [C.POINTER(RmsnormGatedArgs), _vp]),
+    "bm_mamba3_bc_prep": (_i32, [C.POINTER(Mamba3BcPrepArgs), _vp]),
     "bm_selscan1_fwd": (_i32, [C.POINTER(Selscan1Args), _vp]),
     "bm_selscan1_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(Selscan1Args)]),
     "bm_selscan1_fwd_ws": (_i32, [C.POINTER(Selscan1Args), _vp, C.c_size_t, _vp]),

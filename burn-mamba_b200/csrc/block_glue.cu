@@ -196,6 +196,110 @@ __global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// Mamba-3: everything between the in-projection and the SSD slot for B and C, in one pass
+// (src/mamba3/helpers.rs:82-95 qk_norm_expand_bias: RMS norm over r, group -> head expansion, + bias[h, m, r];
+//  src/mamba3/rotation/mod.rs:653-679 + src/modules/misc/rope.rs:50-170: rotation of the leading rope_dim entries
+//  by the cumulative angles, pairs (2j, 2j+1) when `pairwise`, else (j, j + r/2)).
+// One CTA per token.  The raw rows [m, g, r] of B and C (a few KB) are normalised once into shared memory; then
+// one thread per (head, group of 8 pairs) forms cos / sin of its angles once and writes its 16 entries of every
+// rank of both tensors: 16-byte stores, consecutive threads on consecutive chunks.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void store8(T* dst, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* dst, const float (&v)[8]) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[8]) {
+    __nv_bfloat162 p[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(p);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256, 4) mamba3_bc_prep_kernel(bm_mamba3_bc_prep_args a) {
+    extern __shared__ float nrm[];   // [2][m * g][r]: normalised B rows, then C rows
+    const int M = a.mimo_rank, G = a.ngroups, H = a.nheads, Rk = a.state_rank;
+    const int rows = M * G, half = Rk / 2, na = a.rope_dim / 2, ngrp = half / 8;
+    const int64_t tok = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    // ---- RMS norm of the 2 m g raw rows, one warp per row
+    for (int rw = warp; rw < 2 * rows; rw += nwarps) {
+        const bool isc = rw >= rows;
+        const int r0 = isc ? rw - rows : rw;
+        const T* src = static_cast<const T*>(isc ? a.c_raw : a.b_raw) + tok * a.raw_stride + (int64_t)r0 * Rk;
+        const float* gam = isc ? a.c_gamma : a.b_gamma;
+        float ss = 0.f;
+        for (int e = lane; e < Rk; e += 32) {
+            const float v = to_f32(src[e]);
+            nrm[(int64_t)rw * Rk + e] = v;
+            ss = fmaf(v, v, ss);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = 1.f / sqrtf(ss / (float)Rk + a.eps);
+        for (int e = lane; e < Rk; e += 32) nrm[(int64_t)rw * Rk + e] *= inv * gam[e];
+    }
+    __syncthreads();
+    // ---- heads: bias, rotation, store
+    const int hpg = H / G;
+    for (int idx = threadIdx.x; idx < H * ngrp; idx += blockDim.x) {
+        const int h = idx / ngrp, j0 = (idx % ngrp) * 8, g = h / hpg;
+        float cs[8], sn[8], th[8];
+        if (a.angles != nullptr && j0 + 8 <= na && (na & 3) == 0) {
+            const float4* ap = reinterpret_cast<const float4*>(a.angles + (tok * H + h) * na + j0);
+            const float4 t0 = ap[0], t1 = ap[1];
+            th[0] = t0.x, th[1] = t0.y, th[2] = t0.z, th[3] = t0.w, th[4] = t1.x, th[5] = t1.y, th[6] = t1.z, th[7] = t1.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) th[j] = (a.angles != nullptr && j0 + j < na) ? a.angles[(tok * H + h) * na + j0 + j] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) __sincosf(wrap_angle(th[j]), &sn[j], &cs[j]);
+        const int o_lo = a.pairwise ? 2 * j0 : j0, o_hi = a.pairwise ? 2 * j0 + 8 : j0 + half;
+        for (int m = 0; m < M; ++m) {
+#pragma unroll
+            for (int isc = 0; isc < 2; ++isc) {
+                const float* nr = nrm + ((int64_t)isc * rows + m * G + g) * Rk;
+                const float* bias = (isc ? a.c_bias : a.b_bias) + ((int64_t)h * M + m) * Rk;
+                float lo[8], hi[8];
+#pragma unroll
+                for (int q4 = 0; q4 < 2; ++q4) {   // 16-byte loads: shared memory and the (cache-resident) bias
+                    const float4 nl = reinterpret_cast<const float4*>(nr + o_lo)[q4], nh = reinterpret_cast<const float4*>(nr + o_hi)[q4];
+                    const float4 bl = __ldg(reinterpret_cast<const float4*>(bias + o_lo) + q4);
+                    const float4 bh = __ldg(reinterpret_cast<const float4*>(bias + o_hi) + q4);
+                    lo[4 * q4] = nl.x + bl.x, lo[4 * q4 + 1] = nl.y + bl.y, lo[4 * q4 + 2] = nl.z + bl.z, lo[4 * q4 + 3] = nl.w + bl.w;
+                    hi[4 * q4] = nh.x + bh.x, hi[4 * q4 + 1] = nh.y + bh.y, hi[4 * q4 + 2] = nh.z + bh.z, hi[4 * q4 + 3] = nh.w + bh.w;
+                }
+                float olo[8], ohi[8];
+                if (a.pairwise) {   // lo, hi hold 16 consecutive entries: pair j = entries (2j, 2j + 1)
+                    float* both[2] = {lo, hi};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float x0 = both[j >> 2][2 * (j & 3)], x1 = both[j >> 2][2 * (j & 3) + 1];
+                        float* out = j < 4 ? olo : ohi;
+                        out[2 * (j & 3)] = cs[j] * x0 - sn[j] * x1;
+                        out[2 * (j & 3) + 1] = sn[j] * x0 + cs[j] * x1;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        olo[j] = cs[j] * lo[j] - sn[j] * hi[j];
+                        ohi[j] = sn[j] * lo[j] + cs[j] * hi[j];
+                    }
+                }
+                T* dst = static_cast<T*>(isc ? a.c_out : a.b_out) + ((tok * M + m) * H + h) * Rk;
+                store8<T>(dst + o_lo, olo);
+                store8<T>(dst + o_hi, ohi);
+            }
+        }
+    }
+}
+
 extern "C" int32_t bm_conv1d_silu_fwd(const bm_conv1d_silu_args* a, void* stream) {
     clear_error();
     if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
@@ -257,4 +361,30 @@ extern "C" int32_t bm_rmsnorm_gated(const bm_rmsnorm_gated_args* a, void* stream
     if (a->dtype == BM_DTYPE_F32) rmsnorm_gated_kernel<float><<<(unsigned)a->rows, NT, 0, st>>>(*a);
     else rmsnorm_gated_kernel<__nv_bfloat16><<<(unsigned)a->rows, NT, 0, st>>>(*a);
     return check_launch("rmsnorm_gated");
+}
+
+extern "C" int32_t bm_mamba3_bc_prep(const bm_mamba3_bc_prep_args* a, void* stream) {
+    clear_error();
+    if (a == nullptr) return fail(BM_ERR_NULL_POINTER, "args is NULL");
+    BM_REQUIRE(a->batch > 0 && a->seqlen > 0 && a->mimo_rank > 0 && a->ngroups > 0 && a->nheads > 0 && a->state_rank > 0,
+               BM_ERR_BAD_SHAPE, "batch, seqlen, mimo_rank, ngroups, nheads, state_rank must be positive");
+    BM_REQUIRE(a->nheads % a->ngroups == 0, BM_ERR_BAD_SHAPE, "nheads must be divisible by ngroups");
+    BM_REQUIRE(a->state_rank % 16 == 0, BM_ERR_UNSUPPORTED, "state_rank must be a multiple of 16");
+    BM_REQUIRE(a->rope_dim >= 0 && a->rope_dim <= a->state_rank && a->rope_dim % 2 == 0, BM_ERR_BAD_SHAPE,
+               "rope_dim must be even and at most state_rank");
+    BM_REQUIRE(a->dtype == BM_DTYPE_F32 || a->dtype == BM_DTYPE_BF16, BM_ERR_UNSUPPORTED, "dtype must be f32 or bf16");
+    const int esz = a->dtype == BM_DTYPE_F32 ? 4 : 2;
+    const int64_t row = (int64_t)a->mimo_rank * a->ngroups * a->state_rank;
+    BM_REQUIRE(a->raw_stride >= row && ((int64_t)a->raw_stride * esz) % 16 == 0, BM_ERR_BAD_SHAPE,
+               "raw_stride must cover m g r entries and keep rows 16-byte aligned");
+    BM_REQUIRE_PTR(a->b_raw); BM_REQUIRE_PTR(a->c_raw); BM_REQUIRE_PTR(a->b_gamma); BM_REQUIRE_PTR(a->c_gamma);
+    BM_REQUIRE_PTR(a->b_bias); BM_REQUIRE_PTR(a->c_bias); BM_REQUIRE_PTR(a->b_out); BM_REQUIRE_PTR(a->c_out);
+    BM_OPTIONAL_PTR(a->angles);
+    const size_t smem = 2 * (size_t)row * sizeof(float);
+    BM_REQUIRE(smem <= 48 * 1024, BM_ERR_UNSUPPORTED, "m g r too large for the staging buffer");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned grid = (unsigned)((int64_t)a->batch * a->seqlen);
+    if (a->dtype == BM_DTYPE_F32) mamba3_bc_prep_kernel<float><<<grid, 256, smem, st>>>(*a);
+    else mamba3_bc_prep_kernel<__nv_bfloat16><<<grid, 256, smem, st>>>(*a);
+    return check_launch("mamba3_bc_prep");
 }

@@ -98,7 +98,9 @@ class Mamba3:
         expanded = normed.repeat_interleave(self.nheads // self.ngroups, dim=-2)
         return expanded + bias_hmr.transpose(0, 1)
 
-    def _project(self, u):
+    def _project(self, u, qk=True):
+        """In-projection and its splits.  qk = True: B / C normed, expanded and biased by torch ops (the step
+        pathway, whose kernel rotates them itself); qk = False: the raw B / C columns, for `_bc_prep`."""
         proj = u @ self.w_in
         z, x, braw, craw, dd_dt, dd_a, lam_raw, rot = torch.split(proj, self.splits, dim=-1)
         # trapezoid coefficients (src/mamba3/helpers.rs:42-73)
@@ -110,9 +112,20 @@ class Mamba3:
         co = dict(dt=dt, da=da, lam=lam, alpha=alpha, beta=(1.0 - lam) * dt * alpha, gamma=lam * dt)
         lead = u.shape[:-1]
         shape = lead + (self.mimo_rank, self.ngroups, self.state_rank)
-        bm = self._qk(braw.reshape(shape), self.b_norm, self.b_bias)
-        cm = self._qk(craw.reshape(shape), self.c_norm, self.c_bias)
+        if qk:
+            bm = self._qk(braw.reshape(shape), self.b_norm, self.b_bias)
+            cm = self._qk(craw.reshape(shape), self.c_norm, self.c_bias)
+        else:
+            bm, cm = braw, craw
         return z, x.reshape(lead + (self.nheads, self.per_head_dim)), bm, cm, co, rot
+
+    def _bc_prep(self, braw, craw, theta):
+        """Raw B / C columns of the projection -> normed, expanded, biased and rotated [b, s, m, h, r] in one
+        kernel (helpers.rs:82-95 + rotation/mod.rs:653-679)."""
+        f = lambda t: t.float().contiguous()
+        return ops.mamba3_bc_prep(braw, craw, f(self.b_norm), f(self.c_norm), f(self.b_bias), f(self.c_bias),
+                                  angles=theta if self.rope_dim > 0 else None,
+                                  rope_dim=self.rope_dim, pairwise=self.mimo_rank == 1, ngroups=self.ngroups)
 
     def _mx(self):
         """mimo_x as a broadcastable [1, m, h, p] (ones when m = 1)."""
@@ -138,26 +151,24 @@ class Mamba3:
 
     # -- forward, single-SSD pathway -------------------------------------------------------------------
     def forward_single_ssd(self, u_bsm, cache=None, chunk_len=64):
-        """-> (out [b,s,d_model], cache).  One SSD pass with the trapezoid folded into gamma / scale; the
-        rotation of B / C is fused into the SSD's loads (the rotated tensors are never materialised, only
-        the last token's rotated B for the cache)."""
+        """-> (out [b,s,d_model], cache).  One SSD pass with the trapezoid folded into gamma / scale; B / C go
+        from the projection's raw columns to the rotated per-head tensors in one kernel."""
         bsz = u_bsm.shape[0]
         cache = cache or self.zero_cache(bsz)
-        z, x, bm, cm, co, rot = self._project(u_bsm)
+        z, x, braw, craw, co, rot = self._project(u_bsm, qk=False)
         dt, gamma, lam = co["dt"], co["gamma"], co["lam"]
         scale = gamma.clone()
         scale[:, :-1] += dt[:, 1:] * (1.0 - lam[:, 1:])             # single_ssd/mod.rs:134-149
         theta, last_angle = self._angles(rot, dt, cache)
+        bm, cm = self._bc_prep(braw, craw, theta)
         mxb = self._mx()
         seed = torch.einsum("bmhp,bmhr->bhpr", cache["v"][:, None] * mxb, cache["k"])
         h0 = cache["ssm"] + seed * (dt[:, 0] - gamma[:, 0])[:, :, None, None]
         v = (x[:, :, None] * mxb[:, None]).contiguous()
-        y, final = ops.ssd3_single_fwd(v, co["da"].contiguous(), bm.contiguous(), cm.contiguous(), gamma.contiguous(),
-                                       scale.contiguous(), h0.contiguous(), chunk_len=chunk_len, angles=theta,
-                                       rope_dim=self.rope_dim)
+        y, final = ops.ssd3_single_fwd(v, co["da"].contiguous(), bm, cm, gamma.contiguous(), scale.contiguous(),
+                                       h0.contiguous(), chunk_len=chunk_len)
         out = self._tail(y, v, z, m_axis=2)
-        k_last = apply_rope_partial(bm[:, -1], theta[:, -1, None], self.rope_dim, self.mimo_rank == 1)
-        return out, dict(ssm=final, k=k_last, v=x[:, -1].contiguous(), angle=last_angle)
+        return out, dict(ssm=final, k=bm[:, -1].contiguous(), v=x[:, -1].contiguous(), angle=last_angle)
 
     # -- forward, double-SSD pathway -------------------------------------------------------------------
     def forward_double_ssd(self, u_bsm, cache=None, chunk_len=64):
@@ -166,11 +177,9 @@ class Mamba3:
         both passes take the rotated tensors, which this pathway materialises once."""
         bsz = u_bsm.shape[0]
         cache = cache or self.zero_cache(bsz)
-        z, x, bm, cm, co, rot = self._project(u_bsm)
+        z, x, braw, craw, co, rot = self._project(u_bsm, qk=False)
         theta, last_angle = self._angles(rot, co["dt"], cache)
-        pairwise = self.mimo_rank == 1
-        bm = apply_rope_partial(bm, theta[:, :, None], self.rope_dim, pairwise).contiguous()
-        cm = apply_rope_partial(cm, theta[:, :, None], self.rope_dim, pairwise).contiguous()
+        bm, cm = self._bc_prep(braw, craw, theta)
         mxb = self._mx()
         x_prev = torch.cat([cache["v"][:, None], x[:, :-1]], dim=1)
         b_prev = torch.cat([cache["k"][:, None], bm[:, :-1]], dim=1).contiguous()

@@ -202,6 +202,40 @@ def rmsnorm_gated(x, z, gamma, norm_before_gate=False, eps=None):
     return out
 
 
+def mamba3_bc_prep(b_raw, c_raw, b_gamma, c_gamma, b_bias, c_bias, angles=None, rope_dim=None, pairwise=None, ngroups=1,
+                   eps=None):
+    """Mamba-3 B / C from the raw projection columns to what the SSD slot takes: RMS norm over r, group -> head
+    expansion, + bias[h, m, r], rotation by the cumulative angles.  b_raw / c_raw [b, s, m * g * r] (may be column
+    slices of the projection output), gammas [r] f32, biases [h, m, r] f32, angles [b, s, h, rope_dim / 2] f32 or
+    None -> (B, C) [b, s, m, h, r] in the activations' dtype."""
+    bsz, s, mgr = b_raw.shape
+    h, m, r = b_bias.shape
+    act = b_raw.dtype
+    if not b_raw.is_cuda:
+        raise ValueError("b_raw must be a CUDA tensor (this library has no CPU path)")
+    if mgr != m * ngroups * r or tuple(c_raw.shape) != (bsz, s, mgr):
+        raise ValueError("raw rows must hold m * g * r entries")
+    rope_dim = r if rope_dim is None else rope_dim
+    pairwise = (m == 1) if pairwise is None else pairwise
+    del _keepalive[:]
+    bp, bs = _rows(b_raw, "b_raw")
+    cp, cs = _rows(c_raw, "c_raw")
+    if bs != cs:
+        raise ValueError("b_raw and c_raw must have the same row stride")
+    for t, name in ((b_gamma, "b_gamma"), (c_gamma, "c_gamma")):
+        _chk(t, name, torch.float32, (r,))
+    _chk(b_bias, "b_bias", torch.float32, (h, m, r)); _chk(c_bias, "c_bias", torch.float32, (h, m, r))
+    _chk(angles, "angles", torch.float32, (bsz, s, h, max(rope_dim // 2, 0)), optional=True)
+    outs = [torch.empty((bsz, s, m, h, r), dtype=act, device=b_raw.device) for _ in range(2)]
+    args = _ffi.Mamba3BcPrepArgs(batch=bsz, seqlen=s, mimo_rank=m, ngroups=ngroups, nheads=h, state_rank=r, dtype=_DT[act],
+                                 raw_stride=bs, rope_dim=rope_dim, pairwise=int(pairwise),
+                                 eps=DIV_EPS[act] if eps is None else eps, b_raw=bp, c_raw=cp, b_gamma=_ptr(b_gamma),
+                                 c_gamma=_ptr(c_gamma), b_bias=_ptr(b_bias), c_bias=_ptr(c_bias), angles=_ptr(angles),
+                                 b_out=_ptr(outs[0]), c_out=_ptr(outs[1]))
+    check(lib.bm_mamba3_bc_prep(C.byref(args), _stream()), "bm_mamba3_bc_prep")
+    return outs[0], outs[1]
+
+
 def selscan1_fwd(u, delta, a, b, c, d=None, z=None, h0=None, delta_bias=None, delta_softplus=False, serial=False):
     """Mamba-1 selective scan.  u/delta/z [b,s,i], a [i,r] f32, b/c [b,s,r] -> (y [b,s,i], h_final [b,i,r] f32).
     The sequence-parallel kernels (bm_selscan1_fwd_ws) are used unless `serial` asks for the kernels that walk

@@ -259,6 +259,34 @@ typedef struct {
 
 int32_t bm_rmsnorm_gated(const bm_rmsnorm_gated_args* args, void* stream);
 
+/* Mamba-3: B and C from the in-projection's raw columns to what the SSD slot takes, in one pass:
+ * RMS norm over r (weights b_gamma / c_gamma), group -> head expansion, + bias[h, m, r]
+ * (qk_norm_expand_bias, src/mamba3/helpers.rs:82-95; call sites src/mamba3/single_ssd/single_ssd/mod.rs:156-169),
+ * then the data-dependent rotation of the leading rope_dim entries by the cumulative angles
+ * (rotate_bc_forward, src/mamba3/rotation/mod.rs:653-679; pairs (2j, 2j+1) when pairwise -- the reference's rule for
+ * MIMO rank 1 -- else (j, j + r/2), src/modules/misc/rope.rs:50-170).  angles = NULL skips the rotation.
+ * The raw rows may be column slices of the projection output (raw_stride elements between tokens). */
+typedef struct {
+    int32_t batch, seqlen, mimo_rank, ngroups, nheads, state_rank;   /* state_rank: multiple of 16 */
+    int32_t dtype;            /* bm_dtype of the raw rows and the outputs */
+    int32_t raw_stride;       /* elements between consecutive tokens of b_raw / c_raw (>= m g r) */
+    int32_t rope_dim;         /* even, <= state_rank */
+    int32_t pairwise;         /* 1: pairs (2j, 2j+1); 0: pairs (j, j + r/2) */
+    float eps;                /* the reference's per-dtype epsilon (src/utils/mod.rs:50-95) */
+    int32_t reserved;
+    const void* b_raw;        /* [b, s, m, g, r] */
+    const void* c_raw;
+    const float* b_gamma;     /* [r] */
+    const float* c_gamma;
+    const float* b_bias;      /* [h, m, r] */
+    const float* c_bias;
+    const float* angles;      /* [b, s, h, rope_dim / 2] cumulative angles (bm_angle_cumsum), or NULL */
+    void* b_out;              /* [b, s, m, h, r] */
+    void* c_out;
+} bm_mamba3_bc_prep_args;
+
+int32_t bm_mamba3_bc_prep(const bm_mamba3_bc_prep_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Mamba-1 selective scan (sequence) and single-token step.
  * Replace Mamba1::selective_scan (src/mamba1/mamba1.rs:422-523) and

@@ -83,6 +83,14 @@ pub struct BmRmsnormGatedArgs {
 }
 
 #[repr(C)]
+pub struct BmMamba3BcPrepArgs {
+    pub batch: i32, pub seqlen: i32, pub mimo_rank: i32, pub ngroups: i32, pub nheads: i32, pub state_rank: i32,
+    pub dtype: i32, pub raw_stride: i32, pub rope_dim: i32, pub pairwise: i32, pub eps: f32, pub reserved: i32,
+    pub b_raw: *const c_void, pub c_raw: *const c_void, pub b_gamma: *const f32, pub c_gamma: *const f32,
+    pub b_bias: *const f32, pub c_bias: *const f32, pub angles: *const f32, pub b_out: *mut c_void, pub c_out: *mut c_void,
+}
+
+#[repr(C)]
 pub struct BmSelscan1Args {
     pub batch: i32, pub seqlen: i32, pub d_inner: i32, pub state_rank: i32, pub dtype: i32, pub delta_softplus: i32,
     pub u: *const c_void, pub delta: *const c_void, pub a: *const f32, pub b: *const c_void, pub c: *const c_void,
@@ -131,6 +139,7 @@ extern "C" {
     pub fn bm_conv_step(args: *const BmConvStepArgs, stream: *mut c_void) -> i32;
     pub fn bm_conv1d_silu_fwd(args: *const BmConv1dSiluArgs, stream: *mut c_void) -> i32;
     pub fn bm_rmsnorm_gated(args: *const BmRmsnormGatedArgs, stream: *mut c_void) -> i32;
+    pub fn bm_mamba3_bc_prep(args: *const BmMamba3BcPrepArgs, stream: *mut c_void) -> i32;
     pub fn bm_selscan1_fwd(args: *const BmSelscan1Args, stream: *mut c_void) -> i32;
     pub fn bm_selscan1_fwd_workspace_bytes(args: *const BmSelscan1Args) -> usize;
     pub fn bm_selscan1_fwd_ws(args: *const BmSelscan1Args, ws: *mut c_void, ws_bytes: usize, stream: *mut c_void) -> i32;

@@ -249,3 +249,25 @@ def test_tensor_path_wait_that_runs_out_reports_timeout_and_the_context_stays_us
     want_y, want_h = mamba2.ssd_serial(x, cfg["dt"], cfg["a"], b, c, cfg["d"], cfg["h0"], 256)
     y, hf = bm.ops.ssd2_fwd(*args, chunk_len=256, path="tensor", check_status=True)
     assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
+
+
+# ------------------------------------------------------------------ (batch x head) sharding on the device
+@pytest.mark.parametrize("world,by_heads", [(2, False), (4, False), (5, True), (8, True)])
+def test_sharded_units_give_the_bits_of_the_unsharded_call(bm, world, by_heads):
+    """Every rank's share of one problem (shard.partition_units / partition_heads, run here one rank after the
+    other through the same library calls a rank makes) put back together equals the single call bit for bit:
+    whole rows merged into one call, head ranges cut at group boundaries, partial groups."""
+    shard = bm.shard
+    cfg = inputs.ssd2_prefill(seed=57, batch=3, seqlen=512, nheads=12, headdim=64, state_rank=128, ngroups=3, h0_std=0.1)
+    x, b, c = (dev(cfg[k], BF) for k in ("x", "b", "c"))
+    dt, a, d, h0 = dev(cfg["dt"]), dev(cfg["a"]), dev(cfg["d"]), dev(cfg["h0"])
+    fwd = lambda *args: bm.ops.ssd2_fwd(*args[:7], chunk_len=args[7], path="tensor", check_status=True)
+    want_y, want_h = fwd(x, dt, a, b, c, d, h0, 128)
+    parts_of_all = shard.partition_heads(3, 12, world) if by_heads else shard.partition_units(3, 12, 3, world)
+    assert sum(p.count for p in parts_of_all) == 36
+    got_y, got_h = torch.zeros_like(want_y), torch.zeros_like(want_h)
+    for mine in parts_of_all:
+        for b_lo, b_hi, h_lo, h_hi, y_p, h_p in shard.ssd2_fwd_local(fwd, x, dt, a, b, c, d, h0, 128, mine):
+            got_y[b_lo:b_hi, :, h_lo:h_hi] = y_p
+            got_h[b_lo:b_hi, h_lo:h_hi] = h_p
+    assert torch.equal(got_y, want_y) and torch.equal(got_h, want_h)

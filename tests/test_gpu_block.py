@@ -199,3 +199,38 @@ def test_rmsnorm_gated_matches_oracle(bm, dtype, norm_before_gate):
     assert rel_l2(got.float().cpu().numpy(), want) <= tol
     plain = bm.ops.rmsnorm_gated(xt.reshape(1, rows, d), None, gt)
     assert rel_l2(plain.float().cpu().numpy()[0], rms_norm(xq.astype(np.float64), gq.astype(np.float64), name)) <= tol
+
+
+# ------------------------------------------------------------------ Mamba-3 B / C preparation (norm, expand, bias, rotation)
+@pytest.mark.parametrize("dtype,m,g,h,r,rope", [
+    ("f32", 1, 1, 4, 32, 32),      # pairwise rotation (MIMO rank 1)
+    ("f32", 4, 2, 6, 64, 32),      # halves, partial rotation, two groups
+    ("bf16", 4, 1, 32, 128, 128),  # the configured head shape
+    ("bf16", 2, 1, 8, 128, 0),     # no rotation
+])
+def test_mamba3_bc_prep_matches_norm_expand_bias_and_rotation(bm, dtype, m, g, h, r, rope):
+    """One kernel against the oracle's chain qk_norm_expand_bias -> apply_rope_partial (src/mamba3/helpers.rs:82-95,
+    src/modules/misc/rope.rs:50-170), with the raw rows taken as column slices of a wider projection output."""
+    rng = np.random.default_rng(91)
+    b, s = 2, 37
+    tdt = torch.float32 if dtype == "f32" else torch.bfloat16
+    width = 2 * m * g * r + 24
+    proj = rng.standard_normal((b, s, width)).astype(np.float32)
+    if dtype == "bf16":
+        proj = bf16_round(proj)
+    braw, craw = proj[..., 8:8 + m * g * r], proj[..., 8 + m * g * r:8 + 2 * m * g * r]
+    gam = [1.0 + 0.1 * rng.standard_normal(r).astype(np.float32) for _ in range(2)]
+    bias = [0.3 * rng.standard_normal((h, m, r)).astype(np.float32) for _ in range(2)]
+    ang = (3.0 * rng.standard_normal((b, s, h, max(rope // 2, 1)))).astype(np.float32) if rope else None
+    want = []
+    for raw, gm, bi in ((braw, gam[0], bias[0]), (craw, gam[1], bias[1])):
+        t = o3.qk_norm_expand_bias(raw.reshape(b, s, m, g, r), gm, bi, h, dtype)
+        want.append(o3.apply_rope_partial(t, ang[:, :, None], rope, m == 1) if rope else t)
+    pd = torch.as_tensor(proj).cuda().to(tdt)
+    dev = lambda a: None if a is None else torch.as_tensor(a).cuda()
+    got = bm.ops.mamba3_bc_prep(pd[..., 8:8 + m * g * r], pd[..., 8 + m * g * r:8 + 2 * m * g * r], dev(gam[0]), dev(gam[1]),
+                                dev(bias[0]), dev(bias[1]), angles=dev(ang), rope_dim=rope, pairwise=m == 1, ngroups=g)
+    tol = 1e-5 if dtype == "f32" else 6e-3
+    for gt, wt in zip(got, want):
+        assert gt.shape == (b, s, m, h, r)
+        assert rel_l2(gt.float().cpu().numpy(), wt) <= tol, rel_l2(gt.float().cpu().numpy(), wt)
