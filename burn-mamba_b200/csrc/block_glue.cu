@@ -7,6 +7,9 @@
 // Both take a row stride for the tensors that are column slices of the in-projection's output, so that no
 // slice is materialised.
 #include "common.cuh"
+#include "tc_common.cuh"
+
+#include <algorithm>
 
 using namespace bm;
 
@@ -117,6 +120,135 @@ __global__ void __launch_bounds__(128, 6) conv1d_silu_kernel(bm_conv1d_silu_args
             }
             o.store(dst + (int64_t)(t0 + i) * dstride);
         }
+    }
+}
+
+// The same conv for bf16 with the input staged by TMA: a persistent CTA walks tiles of 64 tokens x 128 channels
+// (+ K - 1 halo rows, zero-filled by the copy where they lie before the sequence) and keeps the copies of its
+// next two tiles in flight, so the latency of the strided row reads is paid by the copy engine, not by registers.
+// A thread computes 8 tokens of one 8-channel vector from shared memory.  The first K - 1 tokens of a sequence
+// take their left context from the float32 cache window, as above.  A wait on a copy is bounded; if it ever ran
+// out, the tile's rows would be read straight from global memory instead.
+constexpr int kCtTok = 64, kCtCh = 128, kCtStages = 3, kCtThreads = 128;
+constexpr int kCtRowsMax = kCtTok + 3;
+constexpr int kCtStageBytes = kCtRowsMax * kCtCh * 2;   // 17152
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            tc::smem_u32(dst)),
+        "l"(m), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+template <int K>
+__global__ void __launch_bounds__(kCtThreads, 4) conv1d_silu_tma_kernel(bm_conv1d_silu_args a, const __grid_constant__ CUtensorMap tm,
+                                                                         int n_ctile, int n_ttile, int ntiles) {
+    using T = __nv_bfloat16;
+    extern __shared__ __align__(128) unsigned char ctraw[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ctraw + kCtStages * kCtStageBytes);
+    const int V = a.channels, S = a.seqlen, tid = threadIdx.x;
+    constexpr int ROWS = kCtTok + K - 1;
+    if (tid == 0) {
+        for (int i = 0; i < kCtStages; ++i) tc::mbar_init(&bars[i], 1);
+        tc::fence_mbar_init();
+        tc::tma_prefetch_desc(&tm);
+    }
+    __syncthreads();
+    auto coords = [&](int tile, int& ct, int& tt, int& b) {   // channel tile fastest
+        ct = tile % n_ctile;
+        tt = (tile / n_ctile) % n_ttile;
+        b = tile / (n_ctile * n_ttile);
+    };
+    auto issue = [&](int k) {
+        const int tile = blockIdx.x + k * gridDim.x;
+        if (tid == 0 && tile < ntiles) {
+            int ct, tt, b;
+            coords(tile, ct, tt, b);
+            const int sidx = k % kCtStages;
+            tc::mbar_expect_tx(&bars[sidx], ROWS * kCtCh * 2);
+            tma_load_3d(ctraw + sidx * kCtStageBytes, &tm, &bars[sidx], ct * kCtCh, tt * kCtTok - (K - 1), b);
+        }
+    };
+    issue(0);
+    issue(1);
+    const int cg = tid & 15, tg = tid >> 4;   // 8-channel vector inside the tile, group of 8 tokens
+    for (int k = 0;; ++k) {
+        const int tile = blockIdx.x + k * gridDim.x;
+        if (tile >= ntiles) break;
+        issue(k + 2);   // its stage was last read two tiles ago, before that tile's closing barrier
+        int ct, tt, b;
+        coords(tile, ct, tt, b);
+        const int c0 = ct * kCtCh + cg * VEC, t0 = tt * kCtTok;
+        const bool live = c0 < V;
+        const int cc = live ? c0 : 0;
+        float w[K][VEC], bias[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            bias[j] = a.bias ? a.bias[cc + j] : 0.f;
+#pragma unroll
+            for (int kk = 0; kk < K; ++kk) w[kk][j] = a.weight[(int64_t)(cc + j) * K + kk];
+        }
+        T* dst;
+        int64_t dstride;
+        if (a.out_b == nullptr) {
+            dst = static_cast<T*>(a.out_x) + (int64_t)b * S * V + cc, dstride = V;
+        } else if (cc < a.split_x) {
+            dst = static_cast<T*>(a.out_x) + (int64_t)b * S * a.split_x + cc, dstride = a.split_x;
+        } else if (cc < a.split_x + a.split_bc) {
+            dst = static_cast<T*>(a.out_b) + (int64_t)b * S * a.split_bc + (cc - a.split_x), dstride = a.split_bc;
+        } else {
+            dst = static_cast<T*>(a.out_c) + (int64_t)b * S * a.split_bc + (cc - a.split_x - a.split_bc), dstride = a.split_bc;
+        }
+        bool landed = true;
+        {
+            uint32_t n = 0;
+#pragma unroll 1
+            while (!tc::mbar_try_wait(&bars[k % kCtStages], (k / kCtStages) & 1))
+                if (++n >= tc::kWaitBudget) {
+                    landed = false;
+                    break;
+                }
+            landed = __all_sync(0xffffffffu, landed);
+        }
+        const unsigned char* stage = ctraw + (k % kCtStages) * kCtStageBytes;
+        const T* grow = static_cast<const T*>(a.xin) + (int64_t)b * S * a.xin_stride + cc;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r0 = tg * 8 + half * TL;            // first token of this pass inside the tile
+            Vec8<T> in[TL + K - 1];
+#pragma unroll
+            for (int r = 0; r < TL + K - 1; ++r) {
+                const int t = t0 + r0 - (K - 1) + r;      // token of the row
+                if (t < 0) {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j)
+                        in[r].v[j] = a.window ? a.window[((int64_t)b * V + cc + j) * K + (K + t)] : 0.f;
+                } else if (landed) {
+                    in[r].load(reinterpret_cast<const T*>(stage + (r0 + r) * (kCtCh * 2) + cg * 16));
+                } else if (t < S) {
+                    in[r].load(grow + (int64_t)t * a.xin_stride);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) in[r].v[j] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < TL; ++i) {
+                if (live && t0 + r0 + i < S) {
+                    Vec8<T> o;
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        float acc = bias[j];
+#pragma unroll
+                        for (int kk = 0; kk < K; ++kk) acc = fmaf(in[i + kk].v[j], w[kk][j], acc);
+                        o.v[j] = silu_fast(acc);
+                    }
+                    o.store(dst + (int64_t)(t0 + r0 + i) * dstride);
+                }
+            }
+        }
+        __syncthreads();   // the stage is free for the tile after next
     }
 }
 
@@ -323,10 +455,52 @@ extern "C" int32_t bm_conv1d_silu_fwd(const bm_conv1d_silu_args* a, void* stream
                    BM_ERR_BAD_SHAPE, "split_x + 2 split_bc must equal channels, both multiples of 8");
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    bool staged = false;
+    if (a->dtype == BM_DTYPE_BF16 && aligned16(a->xin)) {
+        // TMA-staged kernel: 3-D map over [b][s][channels] with the projection's row stride
+        CUtensorMap tm;
+        const char* err = nullptr;
+        const uint64_t dims[3] = {(uint64_t)a->channels, (uint64_t)a->seqlen, (uint64_t)a->batch};
+        const uint64_t strides[2] = {(uint64_t)a->xin_stride * 2, (uint64_t)a->seqlen * a->xin_stride * 2};
+        const uint32_t box[3] = {(uint32_t)kCtCh, (uint32_t)(kCtTok + a->kernel - 1), 1};
+        if (tc::make_tensor_map_bf16(&tm, a->xin, 3, dims, strides, box, 0, &err)) {
+            const int n_ctile = (int)cdiv(a->channels, kCtCh), n_ttile = (int)cdiv(a->seqlen, kCtTok);
+            const int64_t ntiles = (int64_t)a->batch * n_ctile * n_ttile;
+            if (ntiles <= INT32_MAX / 2) {
+                static int sms = 0;
+                if (sms == 0) {
+                    int dev = 0;
+                    cudaGetDevice(&dev);
+                    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+                    if (sms <= 0) sms = 148;
+                }
+                const int grid2 = (int)std::min<int64_t>(ntiles, 4 * (int64_t)sms);
+                const size_t smem = (size_t)kCtStages * kCtStageBytes + kCtStages * sizeof(uint64_t);
+                cudaError_t e = cudaSuccess;
+                switch (a->kernel) {
+                    case 2:
+                        e = cudaFuncSetAttribute(conv1d_silu_tma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                        if (e == cudaSuccess) conv1d_silu_tma_kernel<2><<<grid2, kCtThreads, smem, st>>>(*a, tm, n_ctile, n_ttile, (int)ntiles);
+                        break;
+                    case 3:
+                        e = cudaFuncSetAttribute(conv1d_silu_tma_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                        if (e == cudaSuccess) conv1d_silu_tma_kernel<3><<<grid2, kCtThreads, smem, st>>>(*a, tm, n_ctile, n_ttile, (int)ntiles);
+                        break;
+                    default:
+                        e = cudaFuncSetAttribute(conv1d_silu_tma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                        if (e == cudaSuccess) conv1d_silu_tma_kernel<4><<<grid2, kCtThreads, smem, st>>>(*a, tm, n_ctile, n_ttile, (int)ntiles);
+                        break;
+                }
+                if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(conv1d_silu_tma_kernel)");
+                if (int32_t e2 = check_launch("conv1d_silu_tma")) return e2;
+                staged = true;
+            }
+        }
+    }
     const int64_t threads = (int64_t)a->batch * cdiv(a->seqlen, TL) * (a->channels / VEC);
     const unsigned grid = (unsigned)cdiv(threads, 128);
     const bool f32 = a->dtype == BM_DTYPE_F32;
-    switch (a->kernel) {
+    if (!staged) switch (a->kernel) {
         case 2: f32 ? conv1d_silu_kernel<float, 2><<<grid, 128, 0, st>>>(*a) : conv1d_silu_kernel<__nv_bfloat16, 2><<<grid, 128, 0, st>>>(*a); break;
         case 3: f32 ? conv1d_silu_kernel<float, 3><<<grid, 128, 0, st>>>(*a) : conv1d_silu_kernel<__nv_bfloat16, 3><<<grid, 128, 0, st>>>(*a); break;
         default: f32 ? conv1d_silu_kernel<float, 4><<<grid, 128, 0, st>>>(*a) : conv1d_silu_kernel<__nv_bfloat16, 4><<<grid, 128, 0, st>>>(*a); break;
