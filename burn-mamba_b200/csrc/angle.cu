@@ -85,13 +85,69 @@ __global__ void angle_carry_kernel(bm_angle_cumsum_args a, int nchunks) {
     const int j = idx % A, h = (idx / A) % H, b = idx / ((int64_t)A * H);
     float* th = a.theta + ((int64_t)b * S * H + h) * A + j;
     float run = a.prev ? a.prev[idx] : 0.f;
-    for (int c = 0; c < nchunks; ++c) {
-        float* slot = th + (int64_t)chunk_last_row(c, S) * H * A;
-        const float total = *slot;
-        *slot = run;     // carry entering chunk c
-        run += total;
+    // the totals of up to 32 chunks are fetched together (independent loads), then scanned in registers
+    constexpr int G = 32;
+    for (int c0 = 0; c0 < nchunks; c0 += G) {
+        float tot[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) tot[g] = c0 + g < nchunks ? th[(int64_t)chunk_last_row(c0 + g, S) * H * A] : 0.f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (c0 + g < nchunks) {
+                th[(int64_t)chunk_last_row(c0 + g, S) * H * A] = run;   // carry entering chunk c0 + g
+                run += tot[g];
+            }
+        }
     }
     if (a.last) a.last[idx] = wrap_angle(run);
+}
+
+// Passes A and C with the chunk's inputs staged in shared memory: one CTA per (b, chunk) loads the chunk's
+// rot rows (tanh and the range factor applied once per entry) and dt rows with coalesced reads, then a thread
+// per (block of kHB heads, j) walks the tokens from shared memory, so the serial walk waits on no global load.
+constexpr int kStThreads = 256;
+
+template <bool kWrite>
+__global__ void __launch_bounds__(kStThreads) angle_chunk_staged_kernel(bm_angle_cumsum_args a, int nchunks, int nhb) {
+    extern __shared__ float ash[];
+    const int A = a.nangles, H = a.nheads, S = a.seqlen;
+    const int Hp = (H + 3) & ~3;                        // dt rows padded to 16 bytes
+    float* vs = ash;                                    // [kChunk][A]  range * pi * tanh(rot)
+    float* ds = ash + kChunk * A;                       // [kChunk][Hp] dt
+    const int c = blockIdx.x % nchunks, b = blockIdx.x / nchunks;
+    const int t0 = c * kChunk, nt = min(kChunk, S - t0);
+    const float scale = a.range * 3.14159265358979323846f;
+    const float* rot = a.rot + ((int64_t)b * S + t0) * A;
+    const float* dt = a.dt + ((int64_t)b * S + t0) * H;
+    for (int e = threadIdx.x; e < nt * A; e += kStThreads) vs[e] = tanhf(rot[e]) * scale;
+    for (int e = threadIdx.x; e < nt * H; e += kStThreads) ds[(e / H) * Hp + e % H] = dt[e];
+    __syncthreads();
+    const int j = threadIdx.x % A, ngrp = kStThreads / A;
+    if ((int)threadIdx.x >= ngrp * A) return;
+    const int64_t carry_row = (int64_t)chunk_last_row(c, S) * H * A;
+    for (int hb = threadIdx.x / A; hb < nhb; hb += ngrp) {
+        const int h0 = hb * kHB;
+        float* th = a.theta + (int64_t)b * S * H * A + (int64_t)h0 * A + j;
+        float run[kHB];
+#pragma unroll
+        for (int k = 0; k < kHB; ++k) run[k] = (kWrite && h0 + k < H) ? th[carry_row + (int64_t)k * A] : 0.f;
+        for (int t = 0; t < nt; ++t) {
+            const float v = vs[t * A + j];
+            float* tr = th + (int64_t)(t0 + t) * H * A;
+#pragma unroll
+            for (int k = 0; k < kHB; ++k) {
+                if (h0 + k < H) {
+                    run[k] = fmaf(ds[t * Hp + h0 + k], v, run[k]);
+                    if (kWrite) tr[(int64_t)k * A] = run[k];
+                }
+            }
+        }
+        if (!kWrite) {
+#pragma unroll
+            for (int k = 0; k < kHB; ++k)
+                if (h0 + k < H) th[carry_row + (int64_t)k * A] = run[k];
+        }
+    }
 }
 
 }  // namespace
@@ -111,10 +167,15 @@ extern "C" int32_t bm_angle_cumsum(const bm_angle_cumsum_args* a, void* stream) 
     const int nhb = (a->nheads + kHB - 1) / kHB;
     const int64_t per_chunk = (int64_t)a->batch * nchunks * nhb * a->nangles;
     const int64_t per_lane = (int64_t)a->batch * a->nheads * a->nangles;
-    angle_chunk_kernel<false><<<(unsigned)cdiv(per_chunk, 128), 128, 0, st>>>(*a, nchunks, nhb);
+    const size_t smem = (size_t)kChunk * (a->nangles + ((a->nheads + 3) & ~3)) * sizeof(float);
+    const bool staged = a->nangles <= kStThreads && smem <= 48 * 1024 && (int64_t)a->batch * nchunks <= INT32_MAX;
+    const unsigned sgrid = (unsigned)((int64_t)a->batch * nchunks);
+    if (staged) angle_chunk_staged_kernel<false><<<sgrid, kStThreads, smem, st>>>(*a, nchunks, nhb);
+    else angle_chunk_kernel<false><<<(unsigned)cdiv(per_chunk, 128), 128, 0, st>>>(*a, nchunks, nhb);
     if (int32_t e = check_launch("angle_cumsum (chunk totals)")) return e;
     angle_carry_kernel<<<(unsigned)cdiv(per_lane, 128), 128, 0, st>>>(*a, nchunks);
     if (int32_t e = check_launch("angle_cumsum (carries)")) return e;
-    angle_chunk_kernel<true><<<(unsigned)cdiv(per_chunk, 128), 128, 0, st>>>(*a, nchunks, nhb);
+    if (staged) angle_chunk_staged_kernel<true><<<sgrid, kStThreads, smem, st>>>(*a, nchunks, nhb);
+    else angle_chunk_kernel<true><<<(unsigned)cdiv(per_chunk, 128), 128, 0, st>>>(*a, nchunks, nhb);
     return check_launch("angle_cumsum (write)");
 }
