@@ -220,7 +220,19 @@ __device__ __forceinline__ void mask_block(const uint32_t (&r)[32], uint32_t (&o
 // later steps are cut.  Factored form: the column scale and the decay are in Xw and in the epilogue's row
 // factor, so the same-step entries carry rho = gamma / scale instead.
 __device__ __forceinline__ void mask_block_m3(const uint32_t (&r)[32], uint32_t (&out)[16], bool factored, int c, int lane,
-                                              int log2m, float ct, float same, const float* cum2, const float* dtv) {
+                                              int log2m, float ct, float same, const float* cum2, const float* dtv,
+                                              uint32_t same_cols, uint32_t lower_cols) {
+    if (factored) {
+        // the usual case, kept short (this code is fetched on every tile): bit `col` of same_cols / lower_cols says
+        // whether column `col` of the block lies in the row's own step / in an earlier step
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float f0 = (same_cols >> (2 * j)) & 1u ? same : ((lower_cols >> (2 * j)) & 1u ? 1.f : 0.f);
+            const float f1 = (same_cols >> (2 * j + 1)) & 1u ? same : ((lower_cols >> (2 * j + 1)) & 1u ? 1.f : 0.f);
+            out[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * f0, __uint_as_float(r[2 * j + 1]) * f1);
+        }
+        return;
+    }
     const int tr = lane >> log2m;
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -230,7 +242,7 @@ __device__ __forceinline__ void mask_block_m3(const uint32_t (&r)[32], uint32_t 
             const int col = 2 * j + e, tc_ = col >> log2m;
             float w = 0.f;
             if (tc_ == tr) w = same;
-            else if (tc_ < tr) w = factored ? 1.f : ex2(ct - cum2[c * 32 + col]) * dtv[c * 32 + col];
+            else if (tc_ < tr) w = ex2(ct - cum2[c * 32 + col]) * dtv[c * 32 + col];
             f[e] = w;
         }
         out[j] = pack_bf16x2(__uint_as_float(r[2 * j]) * f[0], __uint_as_float(r[2 * j + 1]) * f[1]);
@@ -569,8 +581,24 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             asm volatile("" : "+r"(causal[j]));   // keep the masks in registers instead of recomputing them per tile
         }
         BM_WALK(tw);
+        // Mamba-3, diagonal block: columns of the row's own step and of earlier steps, as bit masks (lane-constant)
+        uint32_t same_cols = 0u, lower_cols = 0u;
+        if (kMode == 1) {
+            const int m_ = 1 << prm.log2m, first = (lane >> prm.log2m) << prm.log2m;   // first column of the row's step
+            same_cols = (m_ >= 32 ? 0xffffffffu : ((1u << m_) - 1u)) << first;
+            lower_cols = first == 0 ? 0u : (0xffffffffu >> (32 - first));
+        }
+        // Mamba-3: the row's same-step weight gamma is fetched one tile ahead (at the end of the pass before), so
+        // that its global-memory latency is hidden behind the wait for the next C B^T
+        float gam_next = 0.f;
+        auto fetch_gamma = [&]() {
+            walk_next(tw);
+            const int rrow = tw.i * T + t;
+            gam_next = rrow < prm.S ? prm.gamma[((int64_t)tw.b * prm.St + (rrow >> prm.log2m)) * prm.H + tw.h] : 0.f;
+        };
+        if (kMode == 1 && prm.gamma != nullptr && total > 0) fetch_gamma();
         for (int it = 0; it < total; ++it) {
-            if (kMode == 1) walk_next(tw);
+            const float gam = gam_next;
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + kCumDt, *colf = cum2 + kCumColf;
@@ -583,8 +611,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const uint32_t cb = lane_addr + kColCB + st * 128;
             float same = 1.f;   // Mamba-3: weight of the same-step block for this row
             if (kMode == 1 && prm.gamma != nullptr) {
-                const int rrow = tw.i * T + t;
-                const float gam = rrow < prm.S ? prm.gamma[((int64_t)tw.b * prm.St + (rrow >> prm.log2m)) * prm.H + tw.h] : 0.f;
                 const float sc = dtv[t];
                 same = factored ? (sc > 0.f ? gam / sc : 0.f) : gam;
             }
@@ -596,7 +622,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     uint32_t r[32];
                     tmem_ld32(cb + c * 32, r);
                     tmem_wait_ld();
-                    if (kMode == 1 && c == q) mask_block_m3(r, out, factored, c, lane, prm.log2m, ct, same, cum2, dtv);
+                    if (kMode == 1 && c == q) mask_block_m3(r, out, factored, c, lane, prm.log2m, ct, same, cum2, dtv, same_cols, lower_cols);
                     else mask_block(r, out, factored, kMode == 0 && c == q, c, ct, cum2, dtv, colf, causal);
                 } else {
 #pragma unroll
@@ -612,6 +638,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 mbar_arrive(&bars->p_ready[st]);
                 mbar_arrive(&bars->cum_empty[cst]);
             }
+            if (kMode == 1 && prm.gamma != nullptr && it + 1 < total) fetch_gamma();
             if (q == 0) {
                 // The warp with the least mask work (one block) also issues Y1(it) = P X: it waits, as a
                 // whole, for the other three warps' parts of P, for the B operand and for the epilogue to
