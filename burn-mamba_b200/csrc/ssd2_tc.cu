@@ -60,7 +60,8 @@ constexpr int kCumDt = T, kCumW = 2 * T, kCumColf = 3 * T, kCumFlag = 4 * T;   /
 constexpr uint32_t kOffStage = 222208;           // y staging: 4 warps x [32 rows x 64 B], 64-byte swizzle (1024-aligned)
 constexpr uint32_t kStageWarpBytes = 2048;
 constexpr uint32_t kOffBar = kOffStage + 4 * kStageWarpBytes;
-constexpr uint32_t kSmemBytes = kOffBar + 384 + 1024;  // barriers + alignment slack
+constexpr uint32_t kSmemBytes = kOffBar + 512 + 1024;  // barriers + alignment slack
+static_assert(sizeof(uint64_t) * 43 + 64 <= 512, "barrier block outgrew its reserve");
 static_assert(kOffCum + kCumStages * kCumStageBytes <= kOffStage, "decay ring overlaps the staging tile");
 static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit of a CTA");
 constexpr uint32_t kLoadBytesCB = 4 * kPanel;
@@ -80,6 +81,7 @@ struct Barriers {
     uint64_t y1_full, y1_empty, y2_full, y2_empty;
     uint64_t h_ready, h_free, xw_ready[2], xw_free[2], xsrc_read[2], s_full[2], s_empty[2];
     uint64_t drain[3];                      // timeout path only: one per MMA-issuing thread
+    uint64_t rot_done[2];                   // Mamba-3 with angles: the C + B stage has been rotated in place
     uint32_t tmem_base;
     uint32_t abort_flag;
     int x_issued, cb_issued;                // TMA producer: tiles whose X / C+B loads have been issued
@@ -108,7 +110,11 @@ struct alignas(64) Params {
     // weight (NULL = 1)
     const float* da;
     const float* gamma;
-    int St, log2m;        // test hook: the TMA producer issues nothing, so the first wait runs out
+    int St, log2m;
+    // optional rotation of the B / C tiles inside the kernel: cumulative angles [b, St, H, rope_pairs]; pairs are
+    // (2j, 2j+1) when `pairwise`, else (j, j + R/2)
+    const float* angles;
+    int rope_pairs, pairwise;
 };
 
 // Optional timeline instrumentation (development builds only, -DBM_SSD2_TRACE): CTA 0 records
@@ -249,6 +255,93 @@ __device__ __forceinline__ void mask_block_m3(const uint32_t (&r)[32], uint32_t 
     }
 }
 
+// Rotation of 8 pairs held in two 16-byte chunks (src/modules/misc/rope.rs:50-170).
+__device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float (&cs)[8], const float (&sn)[8], bool pairwise) {
+    uint32_t* l = &lo.x;
+    uint32_t* h = &hi.x;
+    if (pairwise) {   // lo, hi hold 16 consecutive elements: pair j is the two halves of word j
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            uint32_t& w = j < 4 ? l[j] : h[j - 4];
+            const float2 f = unpack_bf16x2(w);
+            w = pack_bf16x2(cs[j] * f.x - sn[j] * f.y, sn[j] * f.x + cs[j] * f.y);
+        }
+    } else {          // lo holds elements j0 .. j0+7 of the first half, hi the same positions of the second half
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2) {
+            const float2 a = unpack_bf16x2(l[j2]), b = unpack_bf16x2(h[j2]);
+            l[j2] = pack_bf16x2(cs[2 * j2] * a.x - sn[2 * j2] * b.x, cs[2 * j2 + 1] * a.y - sn[2 * j2 + 1] * b.y);
+            h[j2] = pack_bf16x2(sn[2 * j2] * a.x + cs[2 * j2] * b.x, sn[2 * j2 + 1] * a.y + cs[2 * j2 + 1] * b.y);
+        }
+    }
+}
+
+
+// In-place rotation of one C + B stage (two 128-row x 128-column bf16 tiles, two 64-column panels each, 128-byte
+// swizzle) by the cumulative angles of its time steps: thread t of 128 takes (step, group of 8 pairs) items, forms
+// cos / sin of its 8 angles once and rotates that step's rows of both tensors.  Two warpgroups share a stage: thread
+// vt of 256 (warpgroup `part`, thread t) starts at item vt.  The angles of the thread's first item (its only one at
+// MIMO rank 4) arrive in `first`: the caller requests them a whole tile earlier (rotation_angles), so their latency
+// hides behind that tile's work.  Out of line: one copy of the code.  Returns false when the wait for the stage's
+// copy ran out of its budget.
+struct Ang8 {
+    float v[8];
+};
+__device__ __forceinline__ Ang8 rotation_angles(const float* angles, int b, int i, int h, int St, int H, int na, int log2m, int vt) {
+    const int nsteps = T >> log2m, sl = vt >> 3, gq = vt & 7, step = i * nsteps + sl;
+    Ang8 a;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        a.v[j] = (sl < nsteps && step < St && gq * 8 + j < na) ? angles[(((int64_t)b * St + step) * H + h) * na + gq * 8 + j] : 0.f;
+    return a;
+}
+__device__ __noinline__ bool rotate_tile(unsigned char* cstage, unsigned char* bstage, const float* angles, int b, int i, int h,
+                                         int St, int H, int na, int log2m, bool pairwise, int vt, uint64_t* full_bar,
+                                         uint32_t parity, Ang8 first) {
+    const int m = 1 << log2m, nsteps = T >> log2m;
+    auto angle_of = [&](int item, int j) {
+        const int sl = item >> 3, gq = item & 7, step = i * nsteps + sl;
+        return (step < St && gq * 8 + j < na) ? angles[(((int64_t)b * St + step) * H + h) * na + gq * 8 + j] : 0.f;
+    };
+    {
+        uint32_t n = 0;
+        bool ok = true;
+#pragma unroll 1
+        while (!mbar_try_wait(full_bar, parity))
+            if (++n >= kWaitBudget) {
+                ok = false;
+                break;
+            }
+        if (!__all_sync(0xffffffffu, ok)) return false;
+    }
+    for (int item = vt; item < nsteps * 8; item += 256) {
+        const int sl = item >> 3, gq = item & 7;
+        float cs[8], sn[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // MIMO ranks below 4 have more items than threads: the angles of the later ones are fetched here
+            const float a = item == vt ? first.v[j] : angle_of(item, j);
+            __sincosf(wrap_angle(a), &sn[j], &cs[j]);   // angle 0 (pairs past rope_dim, rows past the end) rotates nothing
+        }
+        // the two 16-byte chunks of a row that hold the 8 pairs: panel byte offset and chunk index inside the panel
+        const uint32_t pan_lo = pairwise ? (gq >> 2) * kPanel : 0u, pan_hi = pairwise ? pan_lo : kPanel;
+        const uint32_t ch_lo = pairwise ? (2 * gq) & 7 : gq, ch_hi = pairwise ? ch_lo + 1 : gq;
+        for (int r = 0; r < m; ++r) {
+            const uint32_t row = sl * m + r;
+            const uint32_t alo = pan_lo + sw128_offset(row, ch_lo), ahi = pan_hi + sw128_offset(row, ch_hi);
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                unsigned char* base = which ? bstage : cstage;
+                uint4 lo = *reinterpret_cast<uint4*>(base + alo), hi = *reinterpret_cast<uint4*>(base + ahi);
+                rotate8(lo, hi, cs, sn, pairwise);
+                *reinterpret_cast<uint4*>(base + alo) = lo;
+                *reinterpret_cast<uint4*>(base + ahi) = hi;
+            }
+        }
+    }
+    return true;
+}
+
 // clamp(softplus(x)) of the fused dt path (src/mamba2/mamba2.rs:692-697); out of line: rarely used
 __device__ __noinline__ float dt_activation(float x, float lo, float hi) { return fminf(fmaxf(softplus_f32(x), lo), hi); }
 
@@ -331,6 +424,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         mbar_init(&bars->y2_full, 1);
         mbar_init(&bars->y2_empty, 4);
         for (int i = 0; i < 3; ++i) mbar_init(&bars->drain[i], 1);
+        for (int i = 0; i < 2; ++i) mbar_init(&bars->rot_done[i], 8);   // four warps each of the mask and the epilogue warpgroup
         bars->abort_flag = 0;
         bars->x_issued = bars->cb_issued = 0;
         {
@@ -357,6 +451,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
 
     const int tpu = prm.tiles_per_unit;
     const int total = bars->w_total;
+    // Mamba-3 with angles: the mask and the epilogue warpgroups rotate every C + B stage in place once it has landed
+    // (half of its time steps each), and the MMA issuers wait for that instead of for the copy
+    const bool rotating = kMode == 1 && prm.angles != nullptr;
     // a walker starts before its first tile: the first walk_next() loads item 0
     auto walk_next = [&](TileWalk& w) {
         if (++w.i == w.iend) {
@@ -410,7 +507,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             const uint32_t id_cb = umma_idesc_bf16(128, 128, false, false);
             for (int it = 0; it < total; ++it) {
                 const int st = it & 1;
-                BM_WAIT(&bars->cbld_full[st], (it >> 1) & 1);
+                BM_WAIT(rotating ? &bars->rot_done[st] : &bars->cbld_full[st], (it >> 1) & 1);
                 BM_WAIT(&bars->p_free[st], ((it >> 1) & 1) ^ 1);
                 BM_TRACE(1, it, 0);
                 tc_fence_after();
@@ -458,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                     // of its two accumulators while the state update of tile it is still reading its own
                     const int nx = it + 1, st = nx & 1;
                     const uint32_t bs = b_base + st * 2 * kPanel, xw = xw_base + st * kPanel;
-                    BM_WAIT(&bars->cbld_full[st], (nx >> 1) & 1);
+                    BM_WAIT(rotating ? &bars->rot_done[st] : &bars->cbld_full[st], (nx >> 1) & 1);
                     BM_WAIT(&bars->xw_ready[st], (nx >> 1) & 1);
                     BM_WAIT(&bars->s_empty[st], ((nx >> 1) & 1) ^ 1);
                     BM_TRACE(2, nx, 1);
@@ -591,14 +688,36 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         // Mamba-3: the row's same-step weight gamma is fetched one tile ahead (at the end of the pass before), so
         // that its global-memory latency is hidden behind the wait for the next C B^T
         float gam_next = 0.f;
-        auto fetch_gamma = [&]() {
+        // moves the walker to the next tile, requests its gamma and (rotating) does this warpgroup's half of the
+        // rotation of its C + B stage
+        Ang8 ang_next;
+        auto prefetch_tile = [&]() {   // the walker moves to the next tile; its gamma and rotation angles are requested
             walk_next(tw);
-            const int rrow = tw.i * T + t;
-            gam_next = rrow < prm.S ? prm.gamma[((int64_t)tw.b * prm.St + (rrow >> prm.log2m)) * prm.H + tw.h] : 0.f;
+            if (prm.gamma != nullptr) {
+                const int rrow = tw.i * T + t;
+                gam_next = rrow < prm.S ? prm.gamma[((int64_t)tw.b * prm.St + (rrow >> prm.log2m)) * prm.H + tw.h] : 0.f;
+            }
+            if (rotating) ang_next = rotation_angles(prm.angles, tw.b, tw.i, tw.h, prm.St, prm.H, prm.rope_pairs, prm.log2m, t);
         };
-        if (kMode == 1 && prm.gamma != nullptr && total > 0) fetch_gamma();
+        auto rotate_next = [&](int n) {   // this warpgroup's half of the rotation of tile n's stage (the walker is on it)
+            if (!rotating) return true;
+            const int rst = n & 1;
+            const bool ok = rotate_tile(smem + kOffC + rst * 2 * kPanel, smem + kOffB + rst * 2 * kPanel, prm.angles, tw.b, tw.i, tw.h,
+                                        prm.St, prm.H, prm.rope_pairs, prm.log2m, prm.pairwise != 0, t, &bars->cbld_full[rst],
+                                        (n >> 1) & 1, ang_next);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&bars->rot_done[rst]);
+            return ok;
+        };
+        if (kMode == 1 && total > 0) {
+            prefetch_tile();
+            if (!rotate_next(0)) goto timed_out;
+        }
         for (int it = 0; it < total; ++it) {
             const float gam = gam_next;
+            // Mamba-3: what the next tile needs from global memory is requested now, a whole tile ahead of its use
+            if (kMode == 1 && it + 1 < total) prefetch_tile();
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
             const float *dtv = cum2 + kCumDt, *colf = cum2 + kCumColf;
@@ -638,7 +757,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 mbar_arrive(&bars->p_ready[st]);
                 mbar_arrive(&bars->cum_empty[cst]);
             }
-            if (kMode == 1 && prm.gamma != nullptr && it + 1 < total) fetch_gamma();
             if (q == 0) {
                 // The warp with the least mask work (one block) also issues Y1(it) = P X: it waits, as a
                 // whole, for the other three warps' parts of P, for the B operand and for the epilogue to
@@ -661,6 +779,8 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
                 }
                 __syncwarp();
             }
+            // Mamba-3: on to the next tile (its gamma, this warpgroup's half of its rotation) after Y1 has been issued
+            if (kMode == 1 && it + 1 < total && !rotate_next(it + 1)) goto timed_out;
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ X scaling and state update
@@ -829,8 +949,34 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
         unsigned char* stage = smem + kOffStage + q * kStageWarpBytes;
         const uint32_t srow = lane * 64, sxor = (lane >> 1) & 3;   // 64-byte swizzle: chunk ^ ((row >> 1) & 3)
         BM_WALK(tw);
+        TileWalk twn = tw;   // rotating: one tile ahead of tw
+        // waits for the copy of tile n's C + B stage, rotates it in place and releases it to the MMA issuers
+        Ang8 ang_next;
+        auto rotate_stage = [&](int n, const TileWalk& w) {
+            const int rst = n & 1;
+            const bool ok = rotate_tile(smem + kOffC + rst * 2 * kPanel, smem + kOffB + rst * 2 * kPanel, prm.angles, w.b, w.i, w.h,
+                                        prm.St, prm.H, prm.rope_pairs, prm.log2m, prm.pairwise != 0, 128 + t, &bars->cbld_full[rst],
+                                        (n >> 1) & 1, ang_next);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (ok && lane == 0) mbar_arrive(&bars->rot_done[rst]);
+            return ok;
+        };
+        if (rotating && total > 0) {
+            walk_next(twn);
+            ang_next = rotation_angles(prm.angles, twn.b, twn.i, twn.h, prm.St, prm.H, prm.rope_pairs, prm.log2m, 128 + t);
+            if (!rotate_stage(0, twn)) goto timed_out;
+        }
         for (int it = 0; it < total; ++it) {
-            walk_next(tw);
+            if (rotating) {
+                tw = twn;
+                if (it + 1 < total) {   // the next tile's angles, a whole tile ahead of their use
+                    walk_next(twn);
+                    ang_next = rotation_angles(prm.angles, twn.b, twn.i, twn.h, prm.St, prm.H, prm.rope_pairs, prm.log2m, 128 + t);
+                }
+            } else {
+                walk_next(tw);
+            }
             const int i = tw.i, b = tw.b, h = tw.h;
             const int st = it & 1, cst = (it & (kCumStages - 1));
             const float* cum2 = reinterpret_cast<const float*>(smem + kOffCum + cst * kCumStageBytes);
@@ -858,6 +1004,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd2_tc_kernel(const __grid_const
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->xsrc_read[st]);
+            if (rotating && it + 1 < total) {   // the next tile's stage, while this tile's MMAs are still running
+                if (!rotate_stage(it + 1, twn)) goto timed_out;
+            }
             BM_WAIT_WARP2(&bars->y2_full, it & 1, &bars->y1_full, it & 1);
             if (!factored && lane == 0) mbar_arrive(&bars->xld_empty[st]);   // exact tiles: Y1 and this warp are done with X
             BM_TRACE(6, it, 0);
@@ -1017,59 +1166,6 @@ int32_t ssd2_run(const bm_ssd2_fwd_args* a, void* workspace, size_t workspace_by
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-// Data-dependent rotation of B and C (src/mamba3/rotation/mod.rs:653-679, src/modules/misc/rope.rs:50-170) as a
-// pre-pass of the tensor-core path: raw bf16 B / C [b, s, m, h, r] + cumulative angles [b, s, h, a] -> rotated
-// bf16 copies.  One thread per (b, s, h, group of 8 pairs): 16-byte loads and stores, cos / sin of the wrapped
-// angles shared by B, C and all ranks.  Pairs are (2j, 2j+1) when `pairwise`, else (j, j + r/2); only the first
-// rope_dim / 2 pairs rotate.
-__device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float (&cs)[8], const float (&sn)[8], bool pairwise) {
-    uint32_t* l = &lo.x;
-    uint32_t* h = &hi.x;
-    if (pairwise) {   // lo, hi hold 16 consecutive elements: pair j is the two halves of word j
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            uint32_t& w = j < 4 ? l[j] : h[j - 4];
-            const float2 f = unpack_bf16x2(w);
-            w = pack_bf16x2(cs[j] * f.x - sn[j] * f.y, sn[j] * f.x + cs[j] * f.y);
-        }
-    } else {          // lo holds elements j0 .. j0+7 of the first half, hi the same positions of the second half
-#pragma unroll
-        for (int j2 = 0; j2 < 4; ++j2) {
-            const float2 a = unpack_bf16x2(l[j2]), b = unpack_bf16x2(h[j2]);
-            l[j2] = pack_bf16x2(cs[2 * j2] * a.x - sn[2 * j2] * b.x, cs[2 * j2 + 1] * a.y - sn[2 * j2 + 1] * b.y);
-            h[j2] = pack_bf16x2(sn[2 * j2] * a.x + cs[2 * j2] * b.x, sn[2 * j2 + 1] * a.y + cs[2 * j2 + 1] * b.y);
-        }
-    }
-}
-
-__global__ void rotate_bc_kernel(const __nv_bfloat16* __restrict__ bsrc, const __nv_bfloat16* __restrict__ csrc,
-                                 const float* __restrict__ angles, __nv_bfloat16* __restrict__ bdst,
-                                 __nv_bfloat16* __restrict__ cdst, int64_t rows, int M, int H, int Rk, int rope_dim, int pairwise) {
-    const int half = Rk / 2, na = rope_dim / 2, ngrp = half / 8;
-    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // (b s, h, group of 8 pairs), groups fastest
-    if (idx >= rows * H * ngrp) return;
-    const int j0 = (idx % ngrp) * 8, h = (idx / ngrp) % H;
-    const int64_t bs = idx / ((int64_t)ngrp * H);
-    float cs[8], sn[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        cs[j] = 1.f, sn[j] = 0.f;
-        if (j0 + j < na) __sincosf(wrap_angle(angles[(bs * H + h) * na + j0 + j]), &sn[j], &cs[j]);
-    }
-    const int o_lo = pairwise ? 2 * j0 : j0, o_hi = pairwise ? 2 * j0 + 8 : j0 + half;
-    for (int m = 0; m < M; ++m) {
-        const int64_t o = ((bs * M + m) * H + h) * Rk;
-        uint4 bl = *reinterpret_cast<const uint4*>(bsrc + o + o_lo), bh = *reinterpret_cast<const uint4*>(bsrc + o + o_hi);
-        uint4 cl = *reinterpret_cast<const uint4*>(csrc + o + o_lo), ch = *reinterpret_cast<const uint4*>(csrc + o + o_hi);
-        rotate8(bl, bh, cs, sn, pairwise != 0);
-        rotate8(cl, ch, cs, sn, pairwise != 0);
-        *reinterpret_cast<uint4*>(bdst + o + o_lo) = bl;
-        *reinterpret_cast<uint4*>(bdst + o + o_hi) = bh;
-        *reinterpret_cast<uint4*>(cdst + o + o_lo) = cl;
-        *reinterpret_cast<uint4*>(cdst + o + o_hi) = ch;
-    }
-}
-
 int log2_exact(int v) {
     int l = 0;
     while ((1 << l) < v) ++l;
@@ -1089,10 +1185,8 @@ const char* ssd3_why_not(const bm_ssd3_fwd_args* a) {
 bool ssd3_supported(const bm_ssd3_fwd_args* a) { return ssd3_why_not(a) == nullptr; }
 
 size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a) {
-    size_t n = ws_head_bytes();
-    if (a->angles != nullptr)   // rotated copies of B and C
-        n = align_up(n, 256) + 2 * align_up((size_t)a->batch * a->seqlen * a->mimo_rank * a->nheads * a->state_rank * 2, 256);
-    return n;
+    (void)a;
+    return ws_head_bytes();
 }
 
 int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t workspace_bytes, cudaStream_t stream,
@@ -1102,19 +1196,6 @@ int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t
                     ssd3_workspace_bytes(a));
     const void* bsrc = a->b;
     const void* csrc = a->c;
-    if (a->angles != nullptr) {
-        const size_t each = align_up((size_t)a->batch * a->seqlen * a->mimo_rank * a->nheads * a->state_rank * 2, 256);
-        char* base = static_cast<char*>(workspace) + align_up(ws_head_bytes(), 256);
-        const int64_t rows = (int64_t)a->batch * a->seqlen;
-        const int64_t total = rows * a->nheads * (a->state_rank / 16);
-        rotate_bc_kernel<<<(unsigned)cdiv(total, 256), 256, 0, stream>>>(
-            static_cast<const __nv_bfloat16*>(a->b), static_cast<const __nv_bfloat16*>(a->c), a->angles,
-            reinterpret_cast<__nv_bfloat16*>(base), reinterpret_cast<__nv_bfloat16*>(base + each), rows, a->mimo_rank,
-            a->nheads, a->state_rank, a->rope_dim, a->mimo_rank == 1 ? 1 : 0);
-        if (int32_t e = check_launch("rotate_bc_kernel")) return e;
-        bsrc = base;
-        csrc = base + each;
-    }
     Params prm{};
     const char* err = nullptr;
     const uint64_t S = (uint64_t)a->seqlen * a->mimo_rank, H = a->nheads, B = a->batch;
@@ -1139,6 +1220,9 @@ int32_t ssd3_run(const bm_ssd3_fwd_args* a, bool single, void* workspace, size_t
     prm.h_final = a->h_final, prm.chunk_states = chunk_states;
     ws_head_pointers(workspace, prm);
     prm.B = a->batch, prm.S = (int)S, prm.St = a->seqlen, prm.log2m = log2_exact(a->mimo_rank);
+    // the rotation of B / C (angles given) happens inside the kernel, on the tiles in shared memory
+    prm.angles = (a->angles != nullptr && a->rope_dim > 0) ? a->angles : nullptr;
+    prm.rope_pairs = a->rope_dim / 2, prm.pairwise = a->mimo_rank == 1 ? 1 : 0;
     prm.H = a->nheads, prm.G = a->nheads, prm.Q = T, prm.NC = (int)cdiv((int64_t)S, T);
     prm.tiles_per_unit = (int)cdiv((int64_t)S, T);
     prm.num_units = a->batch * a->nheads;

@@ -29,7 +29,7 @@ int32_t ssd2_bwd_run(const bm_ssd2_bwd_args* a, void* workspace, size_t workspac
 
 // The Mamba-3 cores (single-pass with gamma / scale, or the generic core) on the one-head-per-CTA kernel, over the
 // fused (time x rank) axis.  bf16, headdim 64, state_rank 128, MIMO rank 1, 2 or 4.  When `angles` is given, B and C
-// are rotated by a pre-pass into the workspace.
+// are rotated inside the kernel, on the tiles in shared memory.
 bool ssd3_supported(const bm_ssd3_fwd_args* a);
 const char* ssd3_why_not(const bm_ssd3_fwd_args* a);
 size_t ssd3_workspace_bytes(const bm_ssd3_fwd_args* a);
