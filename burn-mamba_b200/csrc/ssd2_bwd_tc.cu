@@ -49,10 +49,12 @@ constexpr uint32_t kOffDcb = 9 * kPanel;      // masked dM, 2 panels [t][s]
 constexpr uint32_t kOffH = 11 * kPanel;       // h_in bf16 [r][p]
 constexpr uint32_t kOffDh = 12 * kPanel;      // dh bf16 [r][p]
 constexpr uint32_t kOperandBytes = 13 * kPanel;   // 208 KB
-// output staging aliases the operand area once the MMAs of phase 2 have completed
-constexpr uint32_t kRowC = 528, kRowX = 272;  // padded row strides (bytes) of the float32 staging tiles
-constexpr uint32_t kOffStC = 0, kOffStB = 128 * kRowC, kOffStX = 2 * 128 * kRowC;
-static_assert(kOffStX + 128 * kRowX <= kOperandBytes, "staging does not fit the operand area");
+// output staging aliases the operand area once the MMAs of phase 2 have completed: float32 tiles as TMA boxes of
+// [128 rows x 32 floats] with 128-byte swizzle (one panel each): 4 for dC, 4 for dB, 2 for dx
+constexpr uint32_t kOffStC = 0, kOffStB = 4 * kPanel, kOffStX = 8 * kPanel;
+static_assert(kOffStX + 2 * kPanel <= kOperandBytes, "staging does not fit the operand area");
+// the float32 state entering the tile is bulk-copied into the (not yet written) M area and read from there
+constexpr uint32_t kOffHin = kOffM;
 constexpr uint32_t kOffSc = kOperandBytes;    // per-tile scalars, float[128] each
 enum { kScCum = 0, kScSc, kScSame, kScK, kScE, kScColk, kScColZ, kScPgs, kScPa, kScPgi = kScPa + 4, kScCount = kScPgi + 4 };
 constexpr uint32_t kOffRed = kOffSc + kScCount * 128 * 4;   // 8 floats of block reductions
@@ -64,6 +66,17 @@ static_assert(kSmemBytes <= 232448, "over the 227 KB shared-memory limit of a CT
 constexpr uint32_t kColCB = 0, kColDM = 128, kColDC = 256, kColDB = 384;   // phase 1 / phase 2 accumulators
 constexpr uint32_t kColG = 0, kColGi = 64, kColDhC = 128, kColY2 = 192;    // phase 2, over the consumed CB / dM
 
+// Optional phase timeline (development builds only, -DBM_BWD_TRACE): thread 0 of CTA 0 records clock64() at the
+// phase boundaries of its first tiles into prm.trace[tile][event].
+#ifdef BM_BWD_TRACE
+#define BWD_TRACE(ev)                                                                    \
+    do {                                                                                 \
+        if (blockIdx.x == 0 && tid == 0 && ntile < 64) prm.trace[ntile * 16 + (ev)] = clock64(); \
+    } while (0)
+#else
+#define BWD_TRACE(ev) do { } while (0)
+#endif
+
 struct Bars {
     uint64_t ld_full, mma1, mma2;
     uint32_t tmem_base;
@@ -72,6 +85,7 @@ struct Bars {
 
 struct alignas(64) BwdParams {
     CUtensorMap tm_x, tm_dy, tm_b, tm_c;
+    CUtensorMap tm_dx, tm_db, tm_dc;   // float32 gradient tiles, boxes of [128 rows x 32 floats]
     const float* sc;             // [b, s, h] column scale: dt (Mamba-2), scale (Mamba-3 single), NULL = 1
     const float* a;              // [h] (Mamba-2: the step's log decay is dt a)
     const float* da;             // [b, s, h] log decay per step (Mamba-3)
@@ -90,6 +104,7 @@ struct alignas(64) BwdParams {
     float* dd;
     float* dh0;
     int* status;
+    long long* trace;            // development builds only
     int* handoff_flags;          // [grid] warps of CTA c that have stored the dh its first piece ends with
     float* handoff;              // [grid][P][R]
     int B, S, St, H, G, NT, num_units, log2m;   // S counts fused (time x rank) rows, St time steps
@@ -97,18 +112,22 @@ struct alignas(64) BwdParams {
     int plain_bc;                // one head per group: dB / dC rows are stored, not reduce-added
 };
 
-// L2 prefetch of one tile of a 4-D tensor map / of one 128-byte line.
+// L2 prefetch of one tile of a 4-D tensor map.
 __device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* m, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(m), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
                  : "memory");
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-__device__ __forceinline__ void bulk_store_row(float* dst, const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+// One float32 box [128 rows x 32 floats] from shared memory to its place in a gradient tensor: plain store, or
+// reduce-add (rows past the end of the tensor are clipped by the copy engine).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* m, const void* src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(m),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
 }
-__device__ __forceinline__ void bulk_add_row(float* dst, const void* src, uint32_t bytes) {
-    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes)
+__device__ __forceinline__ void bulk_load_1d(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
 
@@ -150,6 +169,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
         tma_prefetch_desc(&prm.tm_dy);
         tma_prefetch_desc(&prm.tm_b);
         tma_prefetch_desc(&prm.tm_c);
+        tma_prefetch_desc(&prm.tm_dx);
+        tma_prefetch_desc(&prm.tm_db);
+        tma_prefetch_desc(&prm.tm_dc);
     }
     if (warp == 2) {
         tmem_alloc(&bars->tmem_base, 512);
@@ -163,6 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
     const int hpg = prm.H / prm.G;
     const float log2e = 1.4426950408889634f;
     uint32_t phase = 0;   // every barrier completes once per tile
+    int ntile = 0;        // tiles this CTA has started (trace index)
 
     // tiles [lo, hi) of the global (unit-major) tile sequence: share_q per CTA, one more for the first share_r
     const int cta = blockIdx.x, extra = cta < prm.share_r ? cta : prm.share_r;
@@ -198,11 +221,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
         }
         float da_acc = 0.f, dd_acc = 0.f;   // Mamba-2: dA (warp 0) and per-thread partials of dD
 
-        for (int i = i_hi - 1; i >= i_lo; --i, phase ^= 1) {
+        for (int i = i_hi - 1; i >= i_lo; --i, phase ^= 1, ++ntile) {
             const int s0 = i * T, left = prm.S - s0;
+            BWD_TRACE(0);
             // ---- loads of the tile
             if (tid == 0) {
-                mbar_expect_tx(&bars->ld_full, 6 * kPanel);
+                mbar_expect_tx(&bars->ld_full, 6 * kPanel + P * R * 4);
+                bulk_load_1d(smem + kOffHin, prm.chunk_states + (((int64_t)b * prm.NT + i) * prm.H + h) * P * R, P * R * 4, &bars->ld_full);
                 tma_load_4d(smem + kOffX, &prm.tm_x, &bars->ld_full, 0, h, s0, b);
                 tma_load_4d(smem + kOffDy, &prm.tm_dy, &bars->ld_full, 0, h, s0, b);
                 tma_load_4d(smem + kOffB, &prm.tm_b, &bars->ld_full, 0, g, s0, b);
@@ -217,11 +242,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                     tma_prefetch_4d(&prm.tm_c, 0, g, s0 - T, b);
                     tma_prefetch_4d(&prm.tm_c, 64, g, s0 - T, b);
                 }
-            }
-            if (i > i_lo && lane < 4) {   // and the state entering it: 64 rows of 512 bytes, 4 lines per row
-                const float* nx = prm.chunk_states + (((int64_t)b * prm.NT + i - 1) * prm.H + h) * P * R;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) prefetch_l2(nx + (int64_t)(warp * 4 + j) * R + lane * 32);
             }
             // ---- per-row scalars (warp 1): log2-domain cumulative decay and the factors derived from it
             if (warp == 1) {
@@ -267,27 +287,31 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                     sc[kScPgs * 128 + t] = 0.f;
                 }
             }
-            // ---- the state entering the tile -> bf16 operand [r][p]; dh -> bf16 operand [r][p]; <dh, h_in> over
-            // this thread's 16 elements
-            float dot = 0.f;
+            // ---- dh -> bf16 operand [r][p]
             {
-                float hin[16];
-                const float* cs = prm.chunk_states + (((int64_t)b * prm.NT + i) * prm.H + h) * P * R;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) hin[j] = cs[(int64_t)(16 * pq + j) * R + row];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) dot = fmaf(dh[j], hin[j], dot);
-                uint4 v0, v1, w0, w1;
-                v0 = make_uint4(pack_bf16x2(hin[0], hin[1]), pack_bf16x2(hin[2], hin[3]), pack_bf16x2(hin[4], hin[5]), pack_bf16x2(hin[6], hin[7]));
-                v1 = make_uint4(pack_bf16x2(hin[8], hin[9]), pack_bf16x2(hin[10], hin[11]), pack_bf16x2(hin[12], hin[13]), pack_bf16x2(hin[14], hin[15]));
-                w0 = make_uint4(pack_bf16x2(dh[0], dh[1]), pack_bf16x2(dh[2], dh[3]), pack_bf16x2(dh[4], dh[5]), pack_bf16x2(dh[6], dh[7]));
-                w1 = make_uint4(pack_bf16x2(dh[8], dh[9]), pack_bf16x2(dh[10], dh[11]), pack_bf16x2(dh[12], dh[13]), pack_bf16x2(dh[14], dh[15]));
-                *reinterpret_cast<uint4*>(smem + kOffH + sw128_offset(row, 2 * pq)) = v0;
-                *reinterpret_cast<uint4*>(smem + kOffH + sw128_offset(row, 2 * pq + 1)) = v1;
+                const uint4 w0 = make_uint4(pack_bf16x2(dh[0], dh[1]), pack_bf16x2(dh[2], dh[3]), pack_bf16x2(dh[4], dh[5]), pack_bf16x2(dh[6], dh[7]));
+                const uint4 w1 = make_uint4(pack_bf16x2(dh[8], dh[9]), pack_bf16x2(dh[10], dh[11]), pack_bf16x2(dh[12], dh[13]), pack_bf16x2(dh[14], dh[15]));
                 *reinterpret_cast<uint4*>(smem + kOffDh + sw128_offset(row, 2 * pq)) = w0;
                 *reinterpret_cast<uint4*>(smem + kOffDh + sw128_offset(row, 2 * pq + 1)) = w1;
             }
+            BWD_TRACE(1);
             if (cta_wait_failed(&bars->ld_full, phase)) goto timed_out;   // also publishes the scalars
+            BWD_TRACE(2);
+            // ---- the state entering the tile (float32 [p][r], just landed) -> bf16 operand [r][p]; <dh, h_in> over this
+            // thread's 16 elements
+            float dot = 0.f;
+            {
+                const float* hs32 = reinterpret_cast<const float*>(smem + kOffHin);
+                float hin[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) hin[j] = hs32[(16 * pq + j) * R + row];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) dot = fmaf(dh[j], hin[j], dot);
+                const uint4 v0 = make_uint4(pack_bf16x2(hin[0], hin[1]), pack_bf16x2(hin[2], hin[3]), pack_bf16x2(hin[4], hin[5]), pack_bf16x2(hin[6], hin[7]));
+                const uint4 v1 = make_uint4(pack_bf16x2(hin[8], hin[9]), pack_bf16x2(hin[10], hin[11]), pack_bf16x2(hin[12], hin[13]), pack_bf16x2(hin[14], hin[15]));
+                *reinterpret_cast<uint4*>(smem + kOffH + sw128_offset(row, 2 * pq)) = v0;
+                *reinterpret_cast<uint4*>(smem + kOffH + sw128_offset(row, 2 * pq + 1)) = v1;
+            }
             // ---- e dY (this thread: 16 elements of row `row`); x and dy of those elements stay in registers
             uint4 xr[2], dyr[2];
             {
@@ -324,7 +348,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 for (int k = 0; k < 4; ++k) umma_ss(tmem + kColDM, desc_advance(ddy, k * 32), desc_advance(dxd, k * 32), id128, k > 0);
                 umma_commit(&bars->mma1);
             }
+            BWD_TRACE(3);
             if (cta_wait_failed(&bars->mma1, phase)) goto timed_out;
+            BWD_TRACE(4);
             tc_fence_after();
             // ---- mask pass: columns [32 pq, 32 pq + 32) of row `row`.  Entry (t, s): an earlier step takes
             // w = exp(c_t - c_s) sc_s, the same step takes the row's same-step weight, later steps 0.
@@ -429,6 +455,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
             tc_fence_before();
             fence_proxy_async_smem();
             __syncthreads();
+            BWD_TRACE(5);
             // ---- phase 2
             if (tid == 0) {
                 tc_fence_after();
@@ -476,7 +503,9 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 }
                 umma_commit(&bars->mma2);
             }
+            BWD_TRACE(6);
             if (cta_wait_failed(&bars->mma2, phase)) goto timed_out;
+            BWD_TRACE(7);
             tc_fence_after();
             // ---- epilogue (operand buffers are free now: staging aliases them)
             {
@@ -485,13 +514,13 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 tmem_wait_ld();
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4)
-                    *reinterpret_cast<uint4*>(smem + kOffStC + row * kRowC + pq * 128 + c4 * 16) =
+                    *reinterpret_cast<uint4*>(smem + kOffStC + pq * kPanel + sw128_offset(row, c4)) =
                         make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
                 tmem_ld32(lane_addr + kColDB + 32 * pq, acc);
                 tmem_wait_ld();
 #pragma unroll
                 for (int c4 = 0; c4 < 8; ++c4)
-                    *reinterpret_cast<uint4*>(smem + kOffStB + row * kRowC + pq * 128 + c4 * 16) =
+                    *reinterpret_cast<uint4*>(smem + kOffStB + pq * kPanel + sw128_offset(row, c4)) =
                         make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
                 // dx: 16 columns of row `row`; dy . Y2 and x . Gi for the decay / scale gradients
                 uint32_t gg[16], gi[16], dc16[16], y2[16];
@@ -526,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 }
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4)
-                    *reinterpret_cast<float4*>(smem + kOffStX + row * kRowX + pq * 64 + c4 * 16) =
+                    *reinterpret_cast<float4*>(smem + kOffStX + (pq >> 1) * kPanel + sw128_offset(row, (pq & 1) * 4 + c4)) =
                         make_float4(dxo[4 * c4], dxo[4 * c4 + 1], dxo[4 * c4 + 2], dxo[4 * c4 + 3]);
                 // the readout term joins the weighted row sum of Z this thread stored in the mask pass
                 sc[(kScPa + pq) * 128 + row] += sc[kScE * 128 + row] * pin;
@@ -541,22 +570,27 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 tc_fence_before();
                 fence_proxy_async_smem();
                 __syncthreads();
+                BWD_TRACE(8);
                 if (lane == 0) atomicAdd(&red[0], dot * decay);
-                // gradient rows leave: dx by a bulk copy, dB / dC by a bulk reduce-add into the group's rows (a
-                // plain copy when every head has its own)
-                if (tid < 128 && tid < left) {
-                    const int64_t tok = (int64_t)b * prm.S + s0 + tid;
-                    bulk_store_row(prm.dx + (tok * prm.H + h) * P, smem + kOffStX + tid * kRowX, P * 4);
-                    if (prm.plain_bc) {
-                        bulk_store_row(prm.dc + (tok * prm.G + g) * R, smem + kOffStC + tid * kRowC, R * 4);
-                        bulk_store_row(prm.db + (tok * prm.G + g) * R, smem + kOffStB + tid * kRowC, R * 4);
-                    } else {
-                        bulk_add_row(prm.dc + (tok * prm.G + g) * R, smem + kOffStC + tid * kRowC, R * 4);
-                        bulk_add_row(prm.db + (tok * prm.G + g) * R, smem + kOffStB + tid * kRowC, R * 4);
+                // gradient tiles leave as TMA boxes: dx stored, dB / dC reduce-added into the group's rows (stored when
+                // every head has its own); ten copies per tile, issued by one thread
+                if (tid == 32) {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) tma_store_4d(&prm.tm_dx, smem + kOffStX + k * kPanel, 32 * k, h, s0, b);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        if (prm.plain_bc) {
+                            tma_store_4d(&prm.tm_dc, smem + kOffStC + k * kPanel, 32 * k, g, s0, b);
+                            tma_store_4d(&prm.tm_db, smem + kOffStB + k * kPanel, 32 * k, g, s0, b);
+                        } else {
+                            tma_reduce_add_4d(&prm.tm_dc, smem + kOffStC + k * kPanel, 32 * k, g, s0, b);
+                            tma_reduce_add_4d(&prm.tm_db, smem + kOffStB + k * kPanel, 32 * k, g, s0, b);
+                        }
                     }
                     tma_store_commit();
                 }
                 __syncthreads();
+                BWD_TRACE(9);
                 // ---- scalar gradients (warp 0, four consecutive rows per lane):
                 //   d(log decay)_row = sum_{t >= row} [rowsum_t - sc_t colZ_t] + sum_{s < row} k_s sc_s (x_s . Gi_s)
                 //                      + exp(c_end) <dh, h_in>
@@ -628,8 +662,10 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                     }
                 }
                 // the staging tiles must have been read before the next tile's loads overwrite them
-                if (tid < 128) tma_store_wait_read<0>();
+                BWD_TRACE(10);
+                if (tid == 32) tma_store_wait_read<0>();
                 __syncthreads();
+                BWD_TRACE(11);
             }
         }
         // ---- end of this CTA's tiles of the unit: dh0 at the start of the unit, else the hand-over; dA, dD
@@ -663,7 +699,7 @@ timed_out:
             for (uint32_t n = 0; n < kWaitBudget && !mbar_try_wait(bs[k], phase); ++n) {}
     }
 done:
-    if (tid < 128) tma_store_wait_all<0>();
+    if (tid == 32) tma_store_wait_all<0>();
     tc_fence_before();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tmem, 512);
@@ -694,7 +730,7 @@ BwdLayout bwd_layout(int batch, int64_t rows, int nheads, size_t fwd_bytes) {
     l.off_hf = align_up(l.off_y + (size_t)batch * rows * nheads * P * 2, 256);
     l.off_flags = align_up(l.off_hf + (size_t)batch * nheads * P * R * sizeof(float), 256);
     l.off_slots = l.off_flags + align_up((size_t)(sm_count() + 1) * sizeof(int), 256);
-    l.total = l.off_slots + (size_t)(sm_count() + 1) * P * R * sizeof(float);
+    l.total = l.off_slots + (size_t)(sm_count() + 1) * P * R * sizeof(float) + 64 * 16 * sizeof(long long);
     return l;
 }
 
@@ -741,6 +777,15 @@ int32_t launch(BwdParams& prm, const void* x, const void* dy, const void* bmat, 
             !make_tensor_map_bf16(&prm.tm_c, cmat, 4, dims, strides, box, 128, &err))
             return fail(BM_ERR_CUDA, "tensor map (b/c): %s", err);
     }
+    {
+        const uint32_t box32[4] = {32, 1, (uint32_t)T, 1};
+        const uint64_t dx_dims[4] = {(uint64_t)P, H, S, B}, dx_str[3] = {(uint64_t)P * 4, H * P * 4, S * H * P * 4};
+        const uint64_t bc_dims[4] = {(uint64_t)R, G, S, B}, bc_str[3] = {(uint64_t)R * 4, G * R * 4, S * G * R * 4};
+        if (!make_tensor_map_f32(&prm.tm_dx, prm.dx, 4, dx_dims, dx_str, box32, 128, &err) ||
+            !make_tensor_map_f32(&prm.tm_db, prm.db, 4, bc_dims, bc_str, box32, 128, &err) ||
+            !make_tensor_map_f32(&prm.tm_dc, prm.dc, 4, bc_dims, bc_str, box32, 128, &err))
+            return fail(BM_ERR_CUDA, "tensor map (gradients): %s", err);
+    }
     prm.status = reinterpret_cast<int*>(w);
     prm.B = batch, prm.S = (int)rows, prm.H = nheads, prm.G = ngroups;
     prm.NT = (int)cdiv(rows, T);
@@ -759,6 +804,7 @@ int32_t launch(BwdParams& prm, const void* x, const void* dy, const void* bmat, 
     prm.share_r = (int)((int64_t)prm.num_units * prm.NT % grid);
     prm.handoff_flags = reinterpret_cast<int*>(w + l.off_flags);
     prm.handoff = reinterpret_cast<float*>(w + l.off_slots);
+    prm.trace = reinterpret_cast<long long*>(w + l.total - 64 * 16 * sizeof(long long));
     if (int32_t r = check_cuda(cudaMemsetAsync(prm.handoff_flags, 0, l.off_slots - l.off_flags, stream), "cudaMemsetAsync(flags)")) return r;
     ssd_bwd_tc_kernel<kMode><<<grid, kThreads, kSmemBytes, stream>>>(prm);
     return check_launch("ssd_bwd_tc_kernel");

@@ -19,6 +19,9 @@ namespace tc {
 // or the encode call fails.
 bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
                           const uint32_t* box, int swizzle_bytes, const char** err);
+// The same for float32 tensors (gradient tiles written or reduce-added by TMA).
+bool make_tensor_map_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                          const uint32_t* box, int swizzle_bytes, const char** err);
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------

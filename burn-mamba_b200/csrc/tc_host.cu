@@ -24,8 +24,21 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+static bool make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
+                            const uint64_t* strides, const uint32_t* box, int swizzle_bytes, const char** err);
+
 bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
                           const uint32_t* box, int swizzle_bytes, const char** err) {
+    return make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides, box, swizzle_bytes, err);
+}
+
+bool make_tensor_map_f32(CUtensorMap* out, const void* base, int rank, const uint64_t* dims, const uint64_t* strides,
+                         const uint32_t* box, int swizzle_bytes, const char** err) {
+    return make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, rank, dims, strides, box, swizzle_bytes, err);
+}
+
+static bool make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, const void* base, int rank, const uint64_t* dims,
+                            const uint64_t* strides, const uint32_t* box, int swizzle_bytes, const char** err) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) {
         *err = "cuTensorMapEncodeTiled not available from the driver";
@@ -39,7 +52,7 @@ bool make_tensor_map_bf16(CUtensorMap* out, const void* base, int rank, const ui
         e[i] = 1;
         if (i + 1 < rank) s[i] = strides[i];
     }
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
+    CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, e,
                     CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
                     : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
