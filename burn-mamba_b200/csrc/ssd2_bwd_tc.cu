@@ -80,7 +80,6 @@ constexpr uint32_t kColG = 0, kColGi = 64, kColDhC = 128, kColY2 = 192;    // ph
 struct Bars {
     uint64_t ld_full, mma1, mma2;
     uint32_t tmem_base;
-    uint32_t failed;
 };
 
 struct alignas(64) BwdParams {
@@ -163,7 +162,6 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
         mbar_init(&bars->ld_full, 1);
         mbar_init(&bars->mma1, 1);
         mbar_init(&bars->mma2, 1);
-        bars->failed = 0;
         fence_mbar_init();
         tma_prefetch_desc(&prm.tm_x);
         tma_prefetch_desc(&prm.tm_dy);
