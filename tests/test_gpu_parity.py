@@ -610,6 +610,22 @@ def test_ssd3_tensor_path_matches_oracle(bm, b, s, h, m, double, fused, strong):
     assert rel_l2(host(y), want_y) <= 2e-2 and rel_l2(host(hf), want_h) <= 2e-2
 
 
+@pytest.mark.parametrize("m,rope", [(4, 128), (4, 64), (1, 96), (2, 128)])
+def test_ssd3_tensor_path_rotation_in_kernel_with_units_cut_between_ctas(bm, m, rope):
+    """More units than SMs (tile ranges cut units between CTAs, the rotating warpgroups walk one tile ahead across
+    those cuts), full and partial rope_dim, all three MIMO ranks: the in-kernel rotation against the float32 path,
+    which rotates at load, on the same raw B / C and angles."""
+    BF = torch.bfloat16
+    cfg = inputs.ssd3_single(seed=75 + m, batch=2, seqlen=96, nheads=160, headdim=64, state_rank=128, mimo_rank=m, h0_std=0.1)
+    ang = dev(np.ascontiguousarray(cfg["angles"][..., :rope // 2]))
+    a = (dev(cfg["v"], BF), dev(cfg["da"]), dev(cfg["b"], BF), dev(cfg["c"], BF), dev(cfg["gamma"]), dev(cfg["scale"]),
+         dev(cfg["h0"]))
+    y, hf = bm.ops.ssd3_single_fwd(*a, chunk_len=32, path="tensor", check_status=True, angles=ang, rope_dim=rope)
+    ye, he = bm.ops.ssd3_single_fwd(*a, chunk_len=32, path="exact", angles=ang, rope_dim=rope)
+    assert torch.isfinite(y.float()).all()
+    assert rel_l2(host(y), host(ye)) <= 2e-2 and rel_l2(host(hf), host(he)) <= 2e-2
+
+
 def test_ssd3_tensor_path_refuses_what_it_does_not_cover(bm):
     cfg = inputs.ssd3_single(seed=71, batch=1, seqlen=16, nheads=2, headdim=16, state_rank=32, mimo_rank=3)
     t = {k: dev(cfg[k]) for k in ("v", "da", "b", "c", "gamma", "scale")}
