@@ -51,8 +51,11 @@ constexpr uint32_t kOffDh = 12 * kPanel;      // dh bf16 [r][p]
 constexpr uint32_t kOperandBytes = 13 * kPanel;   // 208 KB
 // output staging aliases the operand area once the MMAs of phase 2 have completed: float32 tiles as TMA boxes of
 // [128 rows x 32 floats] with 128-byte swizzle (one panel each): 4 for dC, 4 for dB, 2 for dx
-constexpr uint32_t kOffStC = 0, kOffStB = 4 * kPanel, kOffStX = 8 * kPanel;
-static_assert(kOffStX + 2 * kPanel <= kOperandBytes, "staging does not fit the operand area");
+// dx (written while the dC / dB MMAs still run) goes where only M lived, which G has finished reading by then; dC
+// and dB (written after all MMAs) take the X, dY, e dY, B, C and dCB buffers
+constexpr uint32_t kOffStC = 0, kOffStX = kOffM;
+__host__ __device__ constexpr uint32_t stage_b_box(int k) { return k < 3 ? (4 + k) * kPanel : kOffDcb; }
+static_assert(kOffM == 7 * kPanel && kOffDcb == 9 * kPanel, "staging map assumes this operand layout");
 // the float32 state entering the tile is bulk-copied into the (not yet written) M area and read from there
 constexpr uint32_t kOffHin = kOffM;
 constexpr uint32_t kOffSc = kOperandBytes;    // per-tile scalars, float[128] each
@@ -78,7 +81,7 @@ constexpr uint32_t kColG = 0, kColGi = 64, kColDhC = 128, kColY2 = 192;    // ph
 #endif
 
 struct Bars {
-    uint64_t ld_full, mma1, mma2;
+    uint64_t ld_full, mma1, mma2, mma3;
     uint32_t tmem_base;
 };
 
@@ -162,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
         mbar_init(&bars->ld_full, 1);
         mbar_init(&bars->mma1, 1);
         mbar_init(&bars->mma2, 1);
+        mbar_init(&bars->mma3, 1);
         fence_mbar_init();
         tma_prefetch_desc(&prm.tm_x);
         tma_prefetch_desc(&prm.tm_dy);
@@ -463,6 +467,24 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 const uint32_t id_kk = umma_idesc_bf16(128, 128, false, false), id_kmn = umma_idesc_bf16(128, 128, false, true);
                 const uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);
                 const uint32_t id64_mm = umma_idesc_bf16(128, 64, true, true), id64_kmn = umma_idesc_bf16(128, 64, false, true);
+                // G = M^T dY, Gi = B dh, dhC = C^T (e dY), Y2 = C h_in^T
+                {
+                    const uint64_t dm_ = umma_desc_mnmajor(m_sm, kPanel), dy_ = umma_desc_mnmajor(dy_sm, kPanel);
+#pragma unroll 1
+                    for (int k = 0; k < 8; ++k) umma_ss(tmem + kColG, desc_advance(dm_, k * 2048), desc_advance(dy_, k * 2048), id64_mm, k > 0);
+                    const uint64_t db_ = umma_desc_kmajor(b_sm), dh_ = umma_desc_mnmajor(dh_sm, kPanel);
+#pragma unroll 1
+                    for (int k = 0; k < 8; ++k)
+                        umma_ss(tmem + kColGi, desc_advance(db_, (k >> 2) * kPanel + (k & 3) * 32), desc_advance(dh_, k * 2048), id64_kmn, k > 0);
+                    const uint64_t dc_ = umma_desc_mnmajor(c_sm, kPanel), de_ = umma_desc_mnmajor(dye_sm, kPanel);
+#pragma unroll 1
+                    for (int k = 0; k < 8; ++k) umma_ss(tmem + kColDhC, desc_advance(dc_, k * 2048), desc_advance(de_, k * 2048), id64_mm, k > 0);
+                    const uint64_t dck = umma_desc_kmajor(c_sm), dhm = umma_desc_mnmajor(h_sm, kPanel);
+#pragma unroll 1
+                    for (int k = 0; k < 8; ++k)
+                        umma_ss(tmem + kColY2, desc_advance(dck, (k >> 2) * kPanel + (k & 3) * 32), desc_advance(dhm, k * 2048), id64_kmn, k > 0);
+                }
+                umma_commit(&bars->mma2);   // the four 64-wide products: their epilogue runs while dC / dB are computed
                 // dC = dCB B + (e dY) h_in^T
                 {
                     const uint64_t da_ = umma_desc_kmajor(dcb_sm), db_ = umma_desc_mnmajor(b_sm, kPanel);
@@ -482,44 +504,14 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
 #pragma unroll 1
                     for (int k = 0; k < 4; ++k) umma_ss(tmem + kColDB, desc_advance(dx_, k * 32), desc_advance(dh_, k * 32), id_kk, true);
                 }
-                // G = M^T dY, Gi = B dh, dhC = C^T (e dY), Y2 = C h_in^T
-                {
-                    const uint64_t dm_ = umma_desc_mnmajor(m_sm, kPanel), dy_ = umma_desc_mnmajor(dy_sm, kPanel);
-#pragma unroll 1
-                    for (int k = 0; k < 8; ++k) umma_ss(tmem + kColG, desc_advance(dm_, k * 2048), desc_advance(dy_, k * 2048), id64_mm, k > 0);
-                    const uint64_t db_ = umma_desc_kmajor(b_sm), dh_ = umma_desc_mnmajor(dh_sm, kPanel);
-#pragma unroll 1
-                    for (int k = 0; k < 8; ++k)
-                        umma_ss(tmem + kColGi, desc_advance(db_, (k >> 2) * kPanel + (k & 3) * 32), desc_advance(dh_, k * 2048), id64_kmn, k > 0);
-                    const uint64_t dc_ = umma_desc_mnmajor(c_sm, kPanel), de_ = umma_desc_mnmajor(dye_sm, kPanel);
-#pragma unroll 1
-                    for (int k = 0; k < 8; ++k) umma_ss(tmem + kColDhC, desc_advance(dc_, k * 2048), desc_advance(de_, k * 2048), id64_mm, k > 0);
-                    const uint64_t dck = umma_desc_kmajor(c_sm), dhm = umma_desc_mnmajor(h_sm, kPanel);
-#pragma unroll 1
-                    for (int k = 0; k < 8; ++k)
-                        umma_ss(tmem + kColY2, desc_advance(dck, (k >> 2) * kPanel + (k & 3) * 32), desc_advance(dhm, k * 2048), id64_kmn, k > 0);
-                }
-                umma_commit(&bars->mma2);
+                umma_commit(&bars->mma3);
             }
             BWD_TRACE(6);
             if (cta_wait_failed(&bars->mma2, phase)) goto timed_out;
             BWD_TRACE(7);
             tc_fence_after();
-            // ---- epilogue (operand buffers are free now: staging aliases them)
+            // ---- epilogue of the 64-wide products (dC / dB are still being computed: only the M buffer is free yet)
             {
-                uint32_t acc[32];
-                tmem_ld32(lane_addr + kColDC + 32 * pq, acc);
-                tmem_wait_ld();
-#pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4)
-                    *reinterpret_cast<uint4*>(smem + kOffStC + pq * kPanel + sw128_offset(row, c4)) =
-                        make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
-                tmem_ld32(lane_addr + kColDB + 32 * pq, acc);
-                tmem_wait_ld();
-#pragma unroll
-                for (int c4 = 0; c4 < 8; ++c4)
-                    *reinterpret_cast<uint4*>(smem + kOffStB + pq * kPanel + sw128_offset(row, c4)) =
-                        make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
                 // dx: 16 columns of row `row`; dy . Y2 and x . Gi for the decay / scale gradients
                 uint32_t gg[16], gi[16], dc16[16], y2[16];
                 tmem_ld16(lane_addr + kColG + 16 * pq, gg);
@@ -564,6 +556,22 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                 for (int j = 0; j < 16; ++j) dh[j] = fmaf(decay, dh[j], __uint_as_float(dc16[j]));
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                // ---- dC and dB, once their MMAs have completed
+                if (cta_wait_failed(&bars->mma3, phase)) goto timed_out;
+                tc_fence_after();
+                uint32_t acc[32];
+                tmem_ld32(lane_addr + kColDC + 32 * pq, acc);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4)
+                    *reinterpret_cast<uint4*>(smem + kOffStC + pq * kPanel + sw128_offset(row, c4)) =
+                        make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
+                tmem_ld32(lane_addr + kColDB + 32 * pq, acc);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4)
+                    *reinterpret_cast<uint4*>(smem + stage_b_box(pq) + sw128_offset(row, c4)) =
+                        make_uint4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
                 if (tid == 0) red[0] = 0.f;
                 tc_fence_before();
                 fence_proxy_async_smem();
@@ -579,10 +587,10 @@ __global__ void __launch_bounds__(kThreads, 1) ssd_bwd_tc_kernel(const __grid_co
                     for (int k = 0; k < 4; ++k) {
                         if (prm.plain_bc) {
                             tma_store_4d(&prm.tm_dc, smem + kOffStC + k * kPanel, 32 * k, g, s0, b);
-                            tma_store_4d(&prm.tm_db, smem + kOffStB + k * kPanel, 32 * k, g, s0, b);
+                            tma_store_4d(&prm.tm_db, smem + stage_b_box(k), 32 * k, g, s0, b);
                         } else {
                             tma_reduce_add_4d(&prm.tm_dc, smem + kOffStC + k * kPanel, 32 * k, g, s0, b);
-                            tma_reduce_add_4d(&prm.tm_db, smem + kOffStB + k * kPanel, 32 * k, g, s0, b);
+                            tma_reduce_add_4d(&prm.tm_db, smem + stage_b_box(k), 32 * k, g, s0, b);
                         }
                     }
                     tma_store_commit();
@@ -692,8 +700,8 @@ timed_out:
         atomicExch(prm.status, (int)BM_ERR_TIMEOUT);
         // what this thread may still have in flight (loads, MMAs of the current tile) before shared memory and
         // TMEM go back; bounded again
-        uint64_t* bs[3] = {&bars->ld_full, &bars->mma1, &bars->mma2};
-        for (int k = 0; k < 3; ++k)
+        uint64_t* bs[4] = {&bars->ld_full, &bars->mma1, &bars->mma2, &bars->mma3};
+        for (int k = 0; k < 4; ++k)
             for (uint32_t n = 0; n < kWaitBudget && !mbar_try_wait(bs[k], phase); ++n) {}
     }
 done:
