@@ -18,6 +18,7 @@
 // formed as powers of one exponential instead of one exponential per state.
 #include "common.cuh"
 #include "tc_common.cuh"
+#include <type_traits>
 
 using namespace bm;
 using bm::tc::fma2;
@@ -35,6 +36,23 @@ constexpr int PFO = 4;        // the same for the output kernel, which has fewer
 __device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
+// 2^x and 1/x on the special-function unit, denormals flushed: one instruction each (the plain forms carry range
+// fix-ups around them, a few instructions per call, which this loop pays per token).
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_ftz(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
+// exp(x) for x <= 0 (a decay factor): underflows to zero where the exact value is below the normal range.
+__device__ __forceinline__ float exp_decay(float x) { return ex2_ftz(x * kLog2e); }
+// x / (1 + exp(-x)); the denominator is at least 1, so the reciprocal needs no range handling.
+__device__ __forceinline__ float silu_scan(float x) { return x * rcp_ftz(1.f + ex2_ftz(-x * kLog2e)); }
 
 struct Scratch {
     float* h_loc;   // [b, nseg, NS, i]  end state of every segment run from zero
@@ -62,22 +80,23 @@ struct Decay {
         }
         ramp = __all_sync(0xffffffffu, r);   // one code path per warp
     }
+    template <bool kRamp>
     __device__ __forceinline__ void factors(float delta, uint64_t (&p)[NS / 2]) const {
-        if (ramp) {
-            const float e1 = __expf(delta * a[0]), e2 = e1 * e1;
+        if (kRamp) {
+            const float e1 = exp_decay(delta * a[0]), e2 = e1 * e1;
             const uint64_t step = pair_f32(e2, e2);
             p[0] = pair_f32(e1, e2);
 #pragma unroll
             for (int k = 1; k < NS / 2; ++k) p[k] = mul2(p[k - 1], step);
         } else {
 #pragma unroll
-            for (int k = 0; k < NS / 2; ++k) p[k] = pair_f32(__expf(delta * a[2 * k]), __expf(delta * a[2 * k + 1]));
+            for (int k = 0; k < NS / 2; ++k) p[k] = pair_f32(exp_decay(delta * a[2 * k]), exp_decay(delta * a[2 * k + 1]));
         }
     }
 };
 
 // Level 1: segment summaries (all segments but the last, whose end state nobody needs from a zero start).
-template <typename T>
+template <typename T, bool kSoftplus>
 __global__ void __launch_bounds__(CPB, 6) selscan1_summary_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
     __shared__ __align__(16) float bsm[SEG * NS];
     const int I = a.d_inner, S = a.seqlen;
@@ -91,42 +110,67 @@ __global__ void __launch_bounds__(CPB, 6) selscan1_summary_kernel(bm_selscan1_ar
     const int i = active ? tile * CPB + threadIdx.x : I - 1;
     Decay dec;
     dec.init(a.a + (int64_t)i * NS);
-    const float dbias = (a.delta_softplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    const float dbias = (kSoftplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
     uint64_t h[NS / 2];
 #pragma unroll
     for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(0.f, 0.f);
     float dsum = 0.f;
-    const int64_t g0 = ((int64_t)b * S + t0) * I + i;
-    // tokens are taken PF at a time: their loads are issued together, then the recurrence runs over them
-#pragma unroll 1
-    for (int tb = 0; tb < nt; tb += PF) {
-        T draw[PF], uraw[PF];
+    const T* pd = static_cast<const T*>(a.delta) + ((int64_t)b * S + t0) * I + i;
+    const T* pu = static_cast<const T*>(a.u) + ((int64_t)b * S + t0) * I + i;
+    const uint32_t Iu = (uint32_t)I;
+    auto walk = [&](auto ramp_c) {
+        constexpr bool kRamp = decltype(ramp_c)::value;
+        auto token = [&](int t, T draw, T uraw) {
+            float delta = to_f32(draw);
+            if (kSoftplus) delta = softplus_stock(delta + dbias);
+            const float du = delta * to_f32(uraw);
+            dsum += delta;
+            uint64_t p[NS / 2];
+            dec.template factors<kRamp>(delta, p);
+            const uint64_t du2 = pair_f32(du, du);
+            const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
 #pragma unroll
-        for (int j = 0; j < PF; ++j) {
-            const int64_t gi = g0 + (int64_t)min(tb + j, nt - 1) * I;
-            draw[j] = static_cast<const T*>(a.delta)[gi];
-            uraw[j] = static_cast<const T*>(a.u)[gi];
-        }
+            for (int k = 0; k < NS / 4; ++k) {
+                const ulonglong2 bv = bp[k];
+                h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+                h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+            }
+        };
+        // whole blocks of PF tokens: the loads of the next block are issued before the recurrence runs over this one
+        const int nfull = nt - nt % PF;
+        T dn[PF], un[PF];
+        if (nfull > 0) {
 #pragma unroll
-        for (int j = 0; j < PF; ++j) {
-            if (tb + j < nt) {
-                float delta = to_f32(draw[j]);
-                if (a.delta_softplus) delta = softplus_stock(delta + dbias);
-                const float du = delta * to_f32(uraw[j]);
-                dsum += delta;
-                uint64_t p[NS / 2];
-                dec.factors(delta, p);
-                const uint64_t du2 = pair_f32(du, du);
-                const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + (tb + j) * NS);
-#pragma unroll
-                for (int k = 0; k < NS / 4; ++k) {
-                    const ulonglong2 bv = bp[k];
-                    h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
-                    h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
-                }
+            for (int j = 0; j < PF; ++j) {
+                dn[j] = pd[j * Iu];
+                un[j] = pu[j * Iu];
             }
         }
-    }
+#pragma unroll 1
+        for (int tb = 0; tb < nfull; tb += PF) {
+            T draw[PF], uraw[PF];
+#pragma unroll
+            for (int j = 0; j < PF; ++j) {
+                draw[j] = dn[j];
+                uraw[j] = un[j];
+            }
+            pd += PF * Iu;
+            pu += PF * Iu;
+            if (tb + PF < nfull) {
+#pragma unroll
+                for (int j = 0; j < PF; ++j) {
+                    dn[j] = pd[j * Iu];
+                    un[j] = pu[j * Iu];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PF; ++j) token(tb + j, draw[j], uraw[j]);
+        }
+        // the ragged end of a sequence that is no multiple of PF
+#pragma unroll 1
+        for (int t = nfull; t < nt; ++t) token(t, pd[(uint32_t)(t - nfull) * Iu], pu[(uint32_t)(t - nfull) * Iu]);
+    };
+    if (dec.ramp) walk(std::true_type{}); else walk(std::false_type{});
     if (!active) return;
     float* hl = ws.h_loc + (((int64_t)b * nseg + seg) * NS) * I + i;
 #pragma unroll
@@ -155,7 +199,7 @@ __global__ void selscan1_carry_kernel(bm_selscan1_args a, Scratch ws, int nseg) 
 }
 
 // Level 3: outputs.  With nseg == 1 the entering state is h0 itself and levels 1-2 are skipped.
-template <typename T>
+template <typename T, bool kGate, bool kSoftplus>
 __global__ void __launch_bounds__(CPB, 6) selscan1_output_kernel(bm_selscan1_args a, Scratch ws, int nseg) {
     __shared__ __align__(16) float bsm[SEG * NS];
     __shared__ __align__(16) float csm[SEG * NS];
@@ -170,7 +214,7 @@ __global__ void __launch_bounds__(CPB, 6) selscan1_output_kernel(bm_selscan1_arg
     const int i = active ? tile * CPB + threadIdx.x : I - 1;
     Decay dec;
     dec.init(a.a + (int64_t)i * NS);
-    const float dbias = (a.delta_softplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    const float dbias = (kSoftplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
     const float dskip = a.d ? a.d[i] : 0.f;
     uint64_t h[NS / 2];
     if (nseg > 1) {
@@ -183,46 +227,82 @@ __global__ void __launch_bounds__(CPB, 6) selscan1_output_kernel(bm_selscan1_arg
         for (int k = 0; k < NS / 2; ++k) h[k] = h0 ? pair_f32(h0[2 * k], h0[2 * k + 1]) : pair_f32(0.f, 0.f);
     }
     const int64_t g0 = ((int64_t)b * S + t0) * I + i;
-#pragma unroll 1
-    for (int tb = 0; tb < nt; tb += PFO) {
-        T draw[PFO], uraw[PFO], zraw[PFO];
+    const T* pd = static_cast<const T*>(a.delta) + g0;
+    const T* pu = static_cast<const T*>(a.u) + g0;
+    const T* pz = kGate ? static_cast<const T*>(a.z) + g0 : nullptr;
+    T* py = static_cast<T*>(a.y) + g0;
+    const uint32_t Iu = (uint32_t)I;
+    auto walk = [&](auto ramp_c) {
+        constexpr bool kRamp = decltype(ramp_c)::value;
+        auto token = [&](int t, T draw, T uraw, T zraw, T* yp) {
+            float delta = to_f32(draw);
+            if (kSoftplus) delta = softplus_stock(delta + dbias);
+            const float u = to_f32(uraw);
+            const float du = delta * u;
+            uint64_t p[NS / 2];
+            dec.template factors<kRamp>(delta, p);
+            const uint64_t du2 = pair_f32(du, du);
+            const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
+            const ulonglong2* cp = reinterpret_cast<const ulonglong2*>(csm + t * NS);
+            uint64_t acc0, acc1;
 #pragma unroll
-        for (int j = 0; j < PFO; ++j) {
-            const int64_t gi = g0 + (int64_t)min(tb + j, nt - 1) * I;
-            draw[j] = static_cast<const T*>(a.delta)[gi];
-            uraw[j] = static_cast<const T*>(a.u)[gi];
-            if (a.z) zraw[j] = static_cast<const T*>(a.z)[gi];
-        }
+            for (int k = 0; k < NS / 4; ++k) {
+                const ulonglong2 bv = bp[k], cv = cp[k];
+                h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+                h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+                acc0 = k == 0 ? mul2(h[0], cv.x) : fma2(h[2 * k], cv.x, acc0);
+                acc1 = k == 0 ? mul2(h[1], cv.y) : fma2(h[2 * k + 1], cv.y, acc1);
+            }
+            float s0, s1, s2, s3;
+            unpair(acc0, s0, s1);
+            unpair(acc1, s2, s3);
+            float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
+            if (kGate) y *= silu_scan(to_f32(zraw));
+            if (active) *yp = from_f32<T>(y);
+        };
+        // whole blocks of PFO tokens: the loads of the next block are issued before the recurrence runs over this one
+        const int nfull = nt - nt % PFO;
+        T dn[PFO], un[PFO], zn[PFO];
+        if (nfull > 0) {
 #pragma unroll
-        for (int j = 0; j < PFO; ++j) {
-            if (tb + j < nt) {
-                float delta = to_f32(draw[j]);
-                if (a.delta_softplus) delta = softplus_stock(delta + dbias);
-                const float u = to_f32(uraw[j]);
-                const float du = delta * u;
-                uint64_t p[NS / 2];
-                dec.factors(delta, p);
-                const uint64_t du2 = pair_f32(du, du);
-                const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + (tb + j) * NS);
-                const ulonglong2* cp = reinterpret_cast<const ulonglong2*>(csm + (tb + j) * NS);
-                uint64_t acc0 = pair_f32(0.f, 0.f), acc1 = pair_f32(0.f, 0.f);
-#pragma unroll
-                for (int k = 0; k < NS / 4; ++k) {
-                    const ulonglong2 bv = bp[k], cv = cp[k];
-                    h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
-                    h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
-                    acc0 = fma2(h[2 * k], cv.x, acc0);
-                    acc1 = fma2(h[2 * k + 1], cv.y, acc1);
-                }
-                float s0, s1, s2, s3;
-                unpair(acc0, s0, s1);
-                unpair(acc1, s2, s3);
-                float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
-                if (a.z) y *= silu_fast(to_f32(zraw[j]));
-                if (active) static_cast<T*>(a.y)[g0 + (int64_t)(tb + j) * I] = from_f32<T>(y);
+            for (int j = 0; j < PFO; ++j) {
+                dn[j] = pd[j * Iu];
+                un[j] = pu[j * Iu];
+                if (kGate) zn[j] = pz[j * Iu];
             }
         }
-    }
+#pragma unroll 1
+        for (int tb = 0; tb < nfull; tb += PFO) {
+            T draw[PFO], uraw[PFO], zraw[PFO];
+#pragma unroll
+            for (int j = 0; j < PFO; ++j) {
+                draw[j] = dn[j];
+                uraw[j] = un[j];
+                if (kGate) zraw[j] = zn[j];
+            }
+            pd += PFO * Iu;
+            pu += PFO * Iu;
+            if (kGate) pz += PFO * Iu;
+            if (tb + PFO < nfull) {
+#pragma unroll
+                for (int j = 0; j < PFO; ++j) {
+                    dn[j] = pd[j * Iu];
+                    un[j] = pu[j * Iu];
+                    if (kGate) zn[j] = pz[j * Iu];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < PFO; ++j) token(tb + j, draw[j], uraw[j], zraw[j], py + j * Iu);
+            py += PFO * Iu;
+        }
+        // the ragged end of a sequence that is no multiple of PFO
+#pragma unroll 1
+        for (int t = nfull; t < nt; ++t) {
+            const uint32_t o = (uint32_t)(t - nfull) * Iu;
+            token(t, pd[o], pu[o], kGate ? pz[o] : T(), py + o);
+        }
+    };
+    if (dec.ramp) walk(std::true_type{}); else walk(std::false_type{});
     if (active && seg == nseg - 1) {
         float* hf = a.h_final + ((int64_t)b * I + i) * NS;
 #pragma unroll
@@ -249,19 +329,310 @@ size_t scratch_layout(const bm_selscan1_args* a, Scratch* ws, void* base) {
     return 2 * align_up(n_h, 256) + n_d;
 }
 
-template <typename T>
+template <typename T, bool kGate, bool kSoftplus>
 int32_t launch_par(const bm_selscan1_args& a, const Scratch& ws, cudaStream_t st) {
     const int nseg = (int)cdiv(a.seqlen, SEG);
     const int ntile = (int)cdiv(a.d_inner, CPB);
     if (nseg > 1) {
-        selscan1_summary_kernel<T><<<(unsigned)((int64_t)a.batch * ntile * (nseg - 1)), CPB, 0, st>>>(a, ws, nseg);
+        selscan1_summary_kernel<T, kSoftplus><<<(unsigned)((int64_t)a.batch * ntile * (nseg - 1)), CPB, 0, st>>>(a, ws, nseg);
         if (int32_t e = check_launch("selscan1_summary")) return e;
         const int64_t total = (int64_t)a.batch * NS * a.d_inner;
         selscan1_carry_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(a, ws, nseg);
         if (int32_t e = check_launch("selscan1_carry")) return e;
     }
-    selscan1_output_kernel<T><<<(unsigned)((int64_t)a.batch * ntile * nseg), CPB, 0, st>>>(a, ws, nseg);
+    selscan1_output_kernel<T, kGate, kSoftplus><<<(unsigned)((int64_t)a.batch * ntile * nseg), CPB, 0, st>>>(a, ws, nseg);
     return check_launch("selscan1_output");
+}
+
+// The gate and the softplus of delta are compiled in or out, so the token loop carries no per-token branch on them.
+template <typename T>
+int32_t dispatch_par(const bm_selscan1_args& a, const Scratch& ws, cudaStream_t st) {
+    const bool gate = a.z != nullptr, sp = a.delta_softplus != 0;
+    if (gate) return sp ? launch_par<T, true, true>(a, ws, st) : launch_par<T, true, false>(a, ws, st);
+    return sp ? launch_par<T, false, true>(a, ws, st) : launch_par<T, false, false>(a, ws, st);
+}
+
+
+// ---------------------------------------------------------------------------------------------------------
+// The same two passes for bf16 with the token rows staged by TMA.  In the kernels above every thread fetches its
+// own u / delta / z element of each token and has to hold the next tokens' values in registers while it works
+// on these; at 80 registers there is room for one block of four tokens, and the loads end up close to their
+// use.  Here one thread issues, per block of kTok tokens, one tiled copy per tensor ([kTok tokens x 128
+// channels], 3-D map over [b][s][d_inner]) two blocks ahead of the block being consumed, all threads wait on
+// the block's mbarrier and read their column from shared memory.  Rows past the sequence and columns past
+// d_inner are zero-filled by the copy.  A wait is bounded; if it ever ran out, the block's rows would be read
+// straight from global memory.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kTok = 8;        // tokens per staged block
+constexpr int kStg = 3;        // blocks in flight + being consumed
+using bf16 = __nv_bfloat16;
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+            tc::smem_u32(dst)),
+        "l"(m), "r"(tc::smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// Bounded wait of a whole warp on a block's barrier; false if the budget ran out for any lane.
+__device__ __forceinline__ bool wait_block(uint64_t* bar, uint32_t parity) {
+    bool landed = true;
+    uint32_t n = 0;
+#pragma unroll 1
+    while (!tc::mbar_try_wait(bar, parity))
+        if (++n >= tc::kWaitBudget) {
+            landed = false;
+            break;
+        }
+    return __all_sync(0xffffffffu, landed);
+}
+
+template <bool kSoftplus>
+__global__ void __launch_bounds__(CPB, 6)
+selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __grid_constant__ CUtensorMap tm_d,
+                            const __grid_constant__ CUtensorMap tm_u) {
+    __shared__ __align__(128) bf16 stg[kStg][2][kTok][CPB];
+    __shared__ __align__(16) float bsm[SEG * NS];
+    __shared__ uint64_t bars[kStg];
+    const int I = a.d_inner, S = a.seqlen, tid = threadIdx.x;
+    const int ntile = (I + CPB - 1) / CPB;
+    const int seg = blockIdx.x % (nseg - 1), tile = (blockIdx.x / (nseg - 1)) % ntile, b = blockIdx.x / ((nseg - 1) * ntile);
+    const int t0 = seg * SEG, nt = min(SEG, S - t0);
+    const int nblk = (nt + kTok - 1) / kTok;
+    if (tid == 0) {
+        for (int k = 0; k < kStg; ++k) tc::mbar_init(&bars[k], 1);
+        tc::fence_mbar_init();
+    }
+    __syncthreads();
+    auto issue = [&](int k) {
+        if (tid == 0 && k < nblk) {
+            const int sidx = k % kStg;
+            tc::mbar_expect_tx(&bars[sidx], 2 * kTok * CPB * 2);
+            tma_load_3d(&stg[sidx][0][0][0], &tm_d, &bars[sidx], tile * CPB, t0 + k * kTok, b);
+            tma_load_3d(&stg[sidx][1][0][0], &tm_u, &bars[sidx], tile * CPB, t0 + k * kTok, b);
+        }
+    };
+    issue(0);
+    issue(1);
+    stage_rows<bf16>(bsm, a.b, (int64_t)b * S + t0, nt);
+    const bool active = tile * CPB + tid < I;
+    const int i = active ? tile * CPB + tid : I - 1;
+    Decay dec;
+    dec.init(a.a + (int64_t)i * NS);
+    const float dbias = (kSoftplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    uint64_t h[NS / 2];
+#pragma unroll
+    for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(0.f, 0.f);
+    float dsum = 0.f;
+    const bf16* pd = static_cast<const bf16*>(a.delta) + ((int64_t)b * S + t0) * I + i;
+    const bf16* pu = static_cast<const bf16*>(a.u) + ((int64_t)b * S + t0) * I + i;
+    const uint32_t Iu = (uint32_t)I;
+    auto walk = [&](auto ramp_c) {
+        constexpr bool kRamp = decltype(ramp_c)::value;
+        auto token = [&](int t, bf16 draw, bf16 uraw) {
+            float delta = to_f32(draw);
+            if (kSoftplus) delta = softplus_stock(delta + dbias);
+            const float du = delta * to_f32(uraw);
+            dsum += delta;
+            uint64_t p[NS / 2];
+            dec.template factors<kRamp>(delta, p);
+            const uint64_t du2 = pair_f32(du, du);
+            const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
+#pragma unroll
+            for (int k = 0; k < NS / 4; ++k) {
+                const ulonglong2 bv = bp[k];
+                h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+                h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+            }
+        };
+#pragma unroll 1
+        for (int k = 0; k < nblk; ++k) {
+            __syncthreads();   // block k - 1 is consumed by every thread (and, for k = 0, the B rows are staged)
+            issue(k + 2);
+            const int sidx = k % kStg, tb = k * kTok;
+            const bool landed = wait_block(&bars[sidx], (k / kStg) & 1);
+            if (landed && tb + kTok <= nt) {
+#pragma unroll
+                for (int j = 0; j < kTok; ++j) token(tb + j, stg[sidx][0][j][tid], stg[sidx][1][j][tid]);
+            } else {
+#pragma unroll 1
+                for (int j = 0; j < kTok && tb + j < nt; ++j) {
+                    const uint32_t o = (uint32_t)(tb + j) * Iu;
+                    token(tb + j, landed ? stg[sidx][0][j][tid] : pd[o], landed ? stg[sidx][1][j][tid] : pu[o]);
+                }
+            }
+        }
+    };
+    if (dec.ramp) walk(std::true_type{}); else walk(std::false_type{});
+    if (!active) return;
+    float* hl = ws.h_loc + (((int64_t)b * nseg + seg) * NS) * I + i;
+#pragma unroll
+    for (int k = 0; k < NS / 2; ++k) {
+        float lo, hi;
+        unpair(h[k], lo, hi);
+        hl[(int64_t)(2 * k) * I] = lo;
+        hl[(int64_t)(2 * k + 1) * I] = hi;
+    }
+    ws.dsum[((int64_t)b * nseg + seg) * I + i] = dsum;
+}
+
+template <bool kGate, bool kSoftplus>
+__global__ void __launch_bounds__(CPB, 6)
+selscan1_output_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __grid_constant__ CUtensorMap tm_d,
+                           const __grid_constant__ CUtensorMap tm_u, const __grid_constant__ CUtensorMap tm_z) {
+    constexpr int NT = kGate ? 3 : 2;   // staged tensors
+    __shared__ __align__(128) bf16 stg[kStg][NT][kTok][CPB];
+    __shared__ __align__(16) float bsm[SEG * NS];
+    __shared__ __align__(16) float csm[SEG * NS];
+    __shared__ uint64_t bars[kStg];
+    const int I = a.d_inner, S = a.seqlen, tid = threadIdx.x;
+    const int ntile = (I + CPB - 1) / CPB;
+    const int seg = blockIdx.x % nseg, tile = (blockIdx.x / nseg) % ntile, b = blockIdx.x / (nseg * ntile);
+    const int t0 = seg * SEG, nt = min(SEG, S - t0);
+    const int nblk = (nt + kTok - 1) / kTok;
+    if (tid == 0) {
+        for (int k = 0; k < kStg; ++k) tc::mbar_init(&bars[k], 1);
+        tc::fence_mbar_init();
+    }
+    __syncthreads();
+    auto issue = [&](int k) {
+        if (tid == 0 && k < nblk) {
+            const int sidx = k % kStg;
+            tc::mbar_expect_tx(&bars[sidx], NT * kTok * CPB * 2);
+            tma_load_3d(&stg[sidx][0][0][0], &tm_d, &bars[sidx], tile * CPB, t0 + k * kTok, b);
+            tma_load_3d(&stg[sidx][1][0][0], &tm_u, &bars[sidx], tile * CPB, t0 + k * kTok, b);
+            if (kGate) tma_load_3d(&stg[sidx][NT - 1][0][0], &tm_z, &bars[sidx], tile * CPB, t0 + k * kTok, b);
+        }
+    };
+    issue(0);
+    issue(1);
+    stage_rows<bf16>(bsm, a.b, (int64_t)b * S + t0, nt);
+    stage_rows<bf16>(csm, a.c, (int64_t)b * S + t0, nt);
+    const bool active = tile * CPB + tid < I;
+    const int i = active ? tile * CPB + tid : I - 1;
+    Decay dec;
+    dec.init(a.a + (int64_t)i * NS);
+    const float dbias = (kSoftplus && a.delta_bias) ? a.delta_bias[i] : 0.f;
+    const float dskip = a.d ? a.d[i] : 0.f;
+    uint64_t h[NS / 2];
+    if (nseg > 1) {
+        const float* hi_ = ws.h_in + (((int64_t)b * nseg + seg) * NS) * I + i;
+#pragma unroll
+        for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(hi_[(int64_t)(2 * k) * I], hi_[(int64_t)(2 * k + 1) * I]);
+    } else {
+        const float* h0 = a.h0 ? a.h0 + ((int64_t)b * I + i) * NS : nullptr;
+#pragma unroll
+        for (int k = 0; k < NS / 2; ++k) h[k] = h0 ? pair_f32(h0[2 * k], h0[2 * k + 1]) : pair_f32(0.f, 0.f);
+    }
+    const int64_t g0 = ((int64_t)b * S + t0) * I + i;
+    const bf16* pd = static_cast<const bf16*>(a.delta) + g0;
+    const bf16* pu = static_cast<const bf16*>(a.u) + g0;
+    const bf16* pz = kGate ? static_cast<const bf16*>(a.z) + g0 : nullptr;
+    bf16* py = static_cast<bf16*>(a.y) + g0;
+    const uint32_t Iu = (uint32_t)I;
+    auto walk = [&](auto ramp_c) {
+        constexpr bool kRamp = decltype(ramp_c)::value;
+        auto token = [&](int t, bf16 draw, bf16 uraw, bf16 zraw, bf16* yp) {
+            float delta = to_f32(draw);
+            if (kSoftplus) delta = softplus_stock(delta + dbias);
+            const float u = to_f32(uraw);
+            const float du = delta * u;
+            uint64_t p[NS / 2];
+            dec.template factors<kRamp>(delta, p);
+            const uint64_t du2 = pair_f32(du, du);
+            const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
+            const ulonglong2* cp = reinterpret_cast<const ulonglong2*>(csm + t * NS);
+            uint64_t acc0, acc1;
+#pragma unroll
+            for (int k = 0; k < NS / 4; ++k) {
+                const ulonglong2 bv = bp[k], cv = cp[k];
+                h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
+                h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+                acc0 = k == 0 ? mul2(h[0], cv.x) : fma2(h[2 * k], cv.x, acc0);
+                acc1 = k == 0 ? mul2(h[1], cv.y) : fma2(h[2 * k + 1], cv.y, acc1);
+            }
+            float s0, s1, s2, s3;
+            unpair(acc0, s0, s1);
+            unpair(acc1, s2, s3);
+            float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
+            if (kGate) y *= silu_scan(to_f32(zraw));
+            if (active) *yp = from_f32<bf16>(y);
+        };
+#pragma unroll 1
+        for (int k = 0; k < nblk; ++k) {
+            __syncthreads();   // block k - 1 is consumed by every thread (and, for k = 0, the B / C rows are staged)
+            issue(k + 2);
+            const int sidx = k % kStg, tb = k * kTok;
+            const bool landed = wait_block(&bars[sidx], (k / kStg) & 1);
+            if (landed && tb + kTok <= nt) {
+#pragma unroll
+                for (int j = 0; j < kTok; ++j)
+                    token(tb + j, stg[sidx][0][j][tid], stg[sidx][1][j][tid], stg[sidx][NT - 1][j][tid], py + j * Iu);
+            } else {
+#pragma unroll 1
+                for (int j = 0; j < kTok && tb + j < nt; ++j) {
+                    const uint32_t o = (uint32_t)(tb + j) * Iu;
+                    token(tb + j, landed ? stg[sidx][0][j][tid] : pd[o], landed ? stg[sidx][1][j][tid] : pu[o],
+                          !kGate ? bf16() : landed ? stg[sidx][NT - 1][j][tid] : pz[o], py + j * Iu);
+                }
+            }
+            py += kTok * Iu;
+        }
+    };
+    if (dec.ramp) walk(std::true_type{}); else walk(std::false_type{});
+    if (active && seg == nseg - 1) {
+        float* hf = a.h_final + ((int64_t)b * I + i) * NS;
+#pragma unroll
+        for (int k = 0; k < NS / 2; ++k) {
+            float lo, hi;
+            unpair(h[k], lo, hi);
+            hf[2 * k] = lo;
+            hf[2 * k + 1] = hi;
+        }
+    }
+}
+
+// The staged kernels cover bf16 with d_inner a multiple of 8 (rows of the tensor map start 16-byte aligned) and at
+// least one full channel tile; everything else runs on the kernels above.
+bool staged_ok(const bm_selscan1_args& a) {
+    return a.dtype == BM_DTYPE_BF16 && a.d_inner % 8 == 0 && a.d_inner >= CPB && aligned16(a.u) && aligned16(a.delta) &&
+           (a.z == nullptr || aligned16(a.z));
+}
+
+bool token_map(CUtensorMap* tm, const bm_selscan1_args& a, const void* base) {
+    const char* err = nullptr;
+    const uint64_t dims[3] = {(uint64_t)a.d_inner, (uint64_t)a.seqlen, (uint64_t)a.batch};
+    const uint64_t strides[2] = {(uint64_t)a.d_inner * 2, (uint64_t)a.seqlen * a.d_inner * 2};
+    const uint32_t box[3] = {(uint32_t)CPB, (uint32_t)kTok, 1};
+    return tc::make_tensor_map_bf16(tm, base, 3, dims, strides, box, 0, &err);
+}
+
+template <bool kGate, bool kSoftplus>
+int32_t launch_staged(const bm_selscan1_args& a, const Scratch& ws, const CUtensorMap& tm_d, const CUtensorMap& tm_u,
+                      const CUtensorMap& tm_z, cudaStream_t st) {
+    const int nseg = (int)cdiv(a.seqlen, SEG);
+    const int ntile = (int)cdiv(a.d_inner, CPB);
+    if (nseg > 1) {
+        selscan1_summary_tma_kernel<kSoftplus><<<(unsigned)((int64_t)a.batch * ntile * (nseg - 1)), CPB, 0, st>>>(a, ws, nseg, tm_d, tm_u);
+        if (int32_t e = check_launch("selscan1_summary_tma")) return e;
+        const int64_t total = (int64_t)a.batch * NS * a.d_inner;
+        selscan1_carry_kernel<<<(unsigned)cdiv(total, 256), 256, 0, st>>>(a, ws, nseg);
+        if (int32_t e = check_launch("selscan1_carry")) return e;
+    }
+    selscan1_output_tma_kernel<kGate, kSoftplus><<<(unsigned)((int64_t)a.batch * ntile * nseg), CPB, 0, st>>>(a, ws, nseg, tm_d, tm_u, tm_z);
+    return check_launch("selscan1_output_tma");
+}
+
+// Returns BM_OK after launching, or -1 when the tensor maps could not be made (the caller then takes the other kernels).
+int32_t dispatch_staged(const bm_selscan1_args& a, const Scratch& ws, cudaStream_t st) {
+    CUtensorMap tm_d, tm_u, tm_z;
+    if (!token_map(&tm_d, a, a.delta) || !token_map(&tm_u, a, a.u)) return -1;
+    const bool gate = a.z != nullptr, sp = a.delta_softplus != 0;
+    if (gate && !token_map(&tm_z, a, a.z)) return -1;
+    if (!gate) tm_z = tm_u;
+    if (gate) return sp ? launch_staged<true, true>(a, ws, tm_d, tm_u, tm_z, st) : launch_staged<true, false>(a, ws, tm_d, tm_u, tm_z, st);
+    return sp ? launch_staged<false, true>(a, ws, tm_d, tm_u, tm_z, st) : launch_staged<false, false>(a, ws, tm_d, tm_u, tm_z, st);
 }
 
 }  // namespace
@@ -287,5 +658,9 @@ extern "C" int32_t bm_selscan1_fwd_ws(const bm_selscan1_args* a, void* workspace
         return fail(BM_ERR_WORKSPACE_TOO_SMALL, "workspace of %zu bytes given, %zu needed", workspace_bytes, need);
     if (need > 0 && !aligned16(workspace)) return fail(BM_ERR_BAD_ALIGNMENT, "workspace is not 16-byte aligned");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return a->dtype == BM_DTYPE_F32 ? launch_par<float>(*a, ws, st) : launch_par<__nv_bfloat16>(*a, ws, st);
+    if (staged_ok(*a)) {
+        const int32_t e = dispatch_staged(*a, ws, st);
+        if (e >= 0) return e;
+    }
+    return a->dtype == BM_DTYPE_F32 ? dispatch_par<float>(*a, ws, st) : dispatch_par<__nv_bfloat16>(*a, ws, st);
 }

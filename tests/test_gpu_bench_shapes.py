@@ -146,6 +146,37 @@ def test_selscan1_general_decay_matrix_and_initial_state_long_sequence(bm):
     assert rel_l2(host(y), want_y) <= 1e-4 and rel_l2(host(hf), want_h) <= 1e-4
 
 
+@pytest.mark.parametrize("gate,softplus,ramp", [(True, False, True), (False, True, False), (True, True, False),
+                                                 (False, False, True)])
+def test_selscan1_rows_staged_by_tma_ragged_length_and_partial_channel_tile_bf16(bm, gate, softplus, ramp):
+    """bf16 with d_inner a multiple of 8 takes the kernels that stage the token rows by TMA: a length that is no multiple
+    of the staged block (8) nor of the segment (128), a last channel tile of 72 of 128 channels, a general decay matrix,
+    the fused softplus, the gate on and off, a non-zero initial state; equal to the kernels that load through registers
+    (float32 run of the same bf16-rounded inputs) and to the oracle."""
+    from oracle.numerics import softplus_stock
+    cfg = inputs.selscan1(seed=7, batch=2, seqlen=333, d_inner=200, state_rank=16)
+    rng = np.random.default_rng(11)
+    a = cfg["a"] if ramp else -np.exp(rng.uniform(-1.0, 2.0, cfg["a"].shape)).astype(np.float32)
+    h0 = (0.3 * rng.standard_normal(cfg["h0"].shape)).astype(np.float32)
+    u, bb, cc, z = (bf16_round(cfg[k]) for k in ("u", "b", "c", "z"))
+    if softplus:
+        raw = bf16_round(rng.standard_normal(cfg["delta"].shape).astype(np.float32))
+        bias = rng.standard_normal(200).astype(np.float32)
+        delta = softplus_stock(raw + bias)
+    else:
+        raw, bias, delta = bf16_round(cfg["delta"]), None, bf16_round(cfg["delta"])
+    want_y, want_h = mamba1.selective_scan(delta, a, bb, cc, cfg["d"], u, h0, dtype=np.float64)
+    if gate:
+        want_y = want_y * silu(z.astype(np.float64))
+    kw = dict(z=dev(z, BF) if gate else None, h0=dev(h0), delta_bias=None if bias is None else dev(bias),
+              delta_softplus=softplus)
+    y, hf = bm.ops.selscan1_fwd(dev(u, BF), dev(raw, BF), dev(a), dev(bb, BF), dev(cc, BF), dev(cfg["d"]), **kw)
+    kw32 = dict(kw, z=dev(z) if gate else None)
+    y32, hf32 = bm.ops.selscan1_fwd(dev(u), dev(raw), dev(a), dev(bb), dev(cc), dev(cfg["d"]), **kw32)
+    assert rel_l2(host(y), want_y) <= 1e-2 and rel_l2(host(hf), want_h) <= 1e-4
+    assert rel_l2(host(y), host(y32)) <= 1e-2 and rel_l2(host(hf), host(hf32)) <= 1e-5
+
+
 # ------------------------------------------------------------------ Mamba-3 single SSD at its configuration
 def _c5(seed, batch, seqlen, nheads):
     cfg = inputs.ssd3_single(seed=seed, batch=batch, seqlen=seqlen, nheads=nheads, headdim=64, state_rank=128,
