@@ -67,6 +67,18 @@ __device__ __forceinline__ void stage_rows(float* dst, const void* src, int64_t 
     for (int e = threadIdx.x; e < nt * NS; e += blockDim.x) dst[e] = to_f32(s[e]);
 }
 
+// The same for bf16 rows with 16-byte loads (a token's NS = 16 entries are two of them; the entry points require
+// 16-byte aligned tensors): the whole segment is in flight at once.
+__device__ __forceinline__ void stage_rows_vec(float* dst, const void* src, int64_t row0, int nt) {
+    const uint4* s = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + row0 * NS);
+    for (int e = threadIdx.x; e < nt * 2; e += blockDim.x) {
+        const uint4 v = s[e];
+        const float2 f0 = tc::unpack_bf16x2(v.x), f1 = tc::unpack_bf16x2(v.y), f2 = tc::unpack_bf16x2(v.z), f3 = tc::unpack_bf16x2(v.w);
+        reinterpret_cast<float4*>(dst)[2 * e] = make_float4(f0.x, f0.y, f1.x, f1.y);
+        reinterpret_cast<float4*>(dst)[2 * e + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    }
+}
+
 // Per-token decay factors exp(delta A[n]) of one channel as 8 packed pairs.
 struct Decay {
     float a[NS];
@@ -74,9 +86,13 @@ struct Decay {
     __device__ __forceinline__ void init(const float* arow) {
         bool r = true;
 #pragma unroll
+        for (int q = 0; q < NS / 4; ++q) {
+            const float4 v = reinterpret_cast<const float4*>(arow)[q];
+            a[4 * q] = v.x, a[4 * q + 1] = v.y, a[4 * q + 2] = v.z, a[4 * q + 3] = v.w;
+        }
+#pragma unroll
         for (int n = 0; n < NS; ++n) {
-            a[n] = arow[n];
-            r &= fabsf(a[n] - (float)(n + 1) * arow[0]) <= 1e-6f * fabsf(a[n]);
+            r &= fabsf(a[n] - (float)(n + 1) * a[0]) <= 1e-6f * fabsf(a[n]);
         }
         ramp = __all_sync(0xffffffffu, r);   // one code path per warp
     }
@@ -191,10 +207,24 @@ __global__ void selscan1_carry_kernel(bm_selscan1_args a, Scratch ws, int nseg) 
     const int i = idx % I, n = (idx / I) % NS, b = idx / ((int64_t)I * NS);
     const float an = a.a[(int64_t)i * NS + n];
     float h = a.h0 ? a.h0[((int64_t)b * I + i) * NS + n] : 0.f;
-    for (int seg = 0; seg < nseg; ++seg) {
-        const int64_t o = (((int64_t)b * nseg + seg) * NS + n) * I + i;
-        ws.h_in[o] = h;
-        if (seg + 1 < nseg) h = fmaf(h, __expf(an * ws.dsum[((int64_t)b * nseg + seg) * I + i]), ws.h_loc[o]);
+    // the segments' maps do not depend on h: eight of them are fetched together, then applied in order
+    constexpr int CB = 8;
+    for (int seg0 = 0; seg0 < nseg; seg0 += CB) {
+        float ds[CB], hl[CB];
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+            const int seg = min(seg0 + j, nseg - 1);
+            ds[j] = ws.dsum[((int64_t)b * nseg + seg) * I + i];
+            hl[j] = ws.h_loc[(((int64_t)b * nseg + seg) * NS + n) * I + i];
+        }
+#pragma unroll
+        for (int j = 0; j < CB; ++j) {
+            const int seg = seg0 + j;
+            if (seg < nseg) {
+                ws.h_in[(((int64_t)b * nseg + seg) * NS + n) * I + i] = h;
+                if (seg + 1 < nseg) h = fmaf(h, __expf(an * ds[j]), hl[j]);
+            }
+        }
     }
 }
 
@@ -415,7 +445,7 @@ selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gr
     };
     issue(0);
     issue(1);
-    stage_rows<bf16>(bsm, a.b, (int64_t)b * S + t0, nt);
+    stage_rows_vec(bsm, a.b, (int64_t)b * S + t0, nt);
     const bool active = tile * CPB + tid < I;
     const int i = active ? tile * CPB + tid : I - 1;
     Decay dec;
@@ -507,8 +537,8 @@ selscan1_output_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gri
     };
     issue(0);
     issue(1);
-    stage_rows<bf16>(bsm, a.b, (int64_t)b * S + t0, nt);
-    stage_rows<bf16>(csm, a.c, (int64_t)b * S + t0, nt);
+    stage_rows_vec(bsm, a.b, (int64_t)b * S + t0, nt);
+    stage_rows_vec(csm, a.c, (int64_t)b * S + t0, nt);
     const bool active = tile * CPB + tid < I;
     const int i = active ? tile * CPB + tid : I - 1;
     Decay dec;
