@@ -96,6 +96,20 @@ struct Decay {
         }
         ramp = __all_sync(0xffffffffu, r);   // one code path per warp
     }
+    // exp(x A[n]) * du: the weight of a token's input in a state x = sum(delta) further on.
+    template <bool kRamp>
+    __device__ __forceinline__ void weights(float x, float du, uint64_t (&q)[NS / 2]) const {
+        if (kRamp) {
+            const float w1 = exp_decay(x * a[0]), w2 = w1 * w1;
+            const uint64_t step = pair_f32(w2, w2);
+            q[0] = pair_f32(w1 * du, w2 * du);
+#pragma unroll
+            for (int k = 1; k < NS / 2; ++k) q[k] = mul2(q[k - 1], step);
+        } else {
+#pragma unroll
+            for (int k = 0; k < NS / 2; ++k) q[k] = pair_f32(exp_decay(x * a[2 * k]) * du, exp_decay(x * a[2 * k + 1]) * du);
+        }
+    }
     template <bool kRamp>
     __device__ __forceinline__ void factors(float delta, uint64_t (&p)[NS / 2]) const {
         if (kRamp) {
@@ -418,6 +432,9 @@ __device__ __forceinline__ bool wait_block(uint64_t* bar, uint32_t parity) {
     return __all_sync(0xffffffffu, landed);
 }
 
+// Summary pass.  The end state of a segment run from zero is sum_t exp(A[n] * (sum of delta after t)) du_t B_t[n], so
+// the segment is walked from its last token to its first with the running sum of delta: per token one weight
+// ladder and one multiply-add per state, without the state recurrence's own multiply.
 template <bool kSoftplus>
 __global__ void __launch_bounds__(CPB, 6)
 selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __grid_constant__ CUtensorMap tm_d,
@@ -435,12 +452,13 @@ selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gr
         tc::fence_mbar_init();
     }
     __syncthreads();
+    // step k of the walk takes block nblk - 1 - k
     auto issue = [&](int k) {
         if (tid == 0 && k < nblk) {
-            const int sidx = k % kStg;
+            const int sidx = k % kStg, row = t0 + (nblk - 1 - k) * kTok;
             tc::mbar_expect_tx(&bars[sidx], 2 * kTok * CPB * 2);
-            tma_load_3d(&stg[sidx][0][0][0], &tm_d, &bars[sidx], tile * CPB, t0 + k * kTok, b);
-            tma_load_3d(&stg[sidx][1][0][0], &tm_u, &bars[sidx], tile * CPB, t0 + k * kTok, b);
+            tma_load_3d(&stg[sidx][0][0][0], &tm_d, &bars[sidx], tile * CPB, row, b);
+            tma_load_3d(&stg[sidx][1][0][0], &tm_u, &bars[sidx], tile * CPB, row, b);
         }
     };
     issue(0);
@@ -454,7 +472,7 @@ selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gr
     uint64_t h[NS / 2];
 #pragma unroll
     for (int k = 0; k < NS / 2; ++k) h[k] = pair_f32(0.f, 0.f);
-    float dsum = 0.f;
+    float dsuf = 0.f;   // sum of delta over the tokens after the current one
     const bf16* pd = static_cast<const bf16*>(a.delta) + ((int64_t)b * S + t0) * I + i;
     const bf16* pu = static_cast<const bf16*>(a.u) + ((int64_t)b * S + t0) * I + i;
     const uint32_t Iu = (uint32_t)I;
@@ -463,31 +481,29 @@ selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gr
         auto token = [&](int t, bf16 draw, bf16 uraw) {
             float delta = to_f32(draw);
             if (kSoftplus) delta = softplus_stock(delta + dbias);
-            const float du = delta * to_f32(uraw);
-            dsum += delta;
-            uint64_t p[NS / 2];
-            dec.template factors<kRamp>(delta, p);
-            const uint64_t du2 = pair_f32(du, du);
+            uint64_t q[NS / 2];
+            dec.template weights<kRamp>(dsuf, delta * to_f32(uraw), q);
+            dsuf += delta;
             const ulonglong2* bp = reinterpret_cast<const ulonglong2*>(bsm + t * NS);
 #pragma unroll
             for (int k = 0; k < NS / 4; ++k) {
                 const ulonglong2 bv = bp[k];
-                h[2 * k] = fma2(h[2 * k], p[2 * k], mul2(du2, bv.x));
-                h[2 * k + 1] = fma2(h[2 * k + 1], p[2 * k + 1], mul2(du2, bv.y));
+                h[2 * k] = fma2(q[2 * k], bv.x, h[2 * k]);
+                h[2 * k + 1] = fma2(q[2 * k + 1], bv.y, h[2 * k + 1]);
             }
         };
 #pragma unroll 1
         for (int k = 0; k < nblk; ++k) {
-            __syncthreads();   // block k - 1 is consumed by every thread (and, for k = 0, the B rows are staged)
+            __syncthreads();   // the block of step k - 1 is consumed by every thread (and, for k = 0, the B rows are staged)
             issue(k + 2);
-            const int sidx = k % kStg, tb = k * kTok;
+            const int sidx = k % kStg, tb = (nblk - 1 - k) * kTok;
             const bool landed = wait_block(&bars[sidx], (k / kStg) & 1);
             if (landed && tb + kTok <= nt) {
 #pragma unroll
-                for (int j = 0; j < kTok; ++j) token(tb + j, stg[sidx][0][j][tid], stg[sidx][1][j][tid]);
+                for (int j = kTok - 1; j >= 0; --j) token(tb + j, stg[sidx][0][j][tid], stg[sidx][1][j][tid]);
             } else {
 #pragma unroll 1
-                for (int j = 0; j < kTok && tb + j < nt; ++j) {
+                for (int j = min(kTok, nt - tb) - 1; j >= 0; --j) {
                     const uint32_t o = (uint32_t)(tb + j) * Iu;
                     token(tb + j, landed ? stg[sidx][0][j][tid] : pd[o], landed ? stg[sidx][1][j][tid] : pu[o]);
                 }
@@ -504,7 +520,7 @@ selscan1_summary_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gr
         hl[(int64_t)(2 * k) * I] = lo;
         hl[(int64_t)(2 * k + 1) * I] = hi;
     }
-    ws.dsum[((int64_t)b * nseg + seg) * I + i] = dsum;
+    ws.dsum[((int64_t)b * nseg + seg) * I + i] = dsuf;
 }
 
 template <bool kGate, bool kSoftplus>
