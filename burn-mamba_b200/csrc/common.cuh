@@ -55,9 +55,23 @@ __device__ __forceinline__ float softplus_f32(float x) { return x > 18.f ? x : l
 __device__ __forceinline__ float softplus_stock(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 // x / (1 + exp(-x)) (src/modules/activation/silu.rs:24-27)
 __device__ __forceinline__ float silu_f32(float x) { return x / (1.f + expf(-x)); }
+// 2^x and 1/x on the special-function unit, denormals flushed: one instruction each (the plain approximate forms
+// carry range fix-ups around them, a few instructions per call, which a streaming loop pays per element).
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_ftz(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 // The same gate with the hardware exponential and reciprocal (about 1e-6 relative): for the streaming kernels
 // that evaluate it once per element of a large activation tensor, where the exact division is most of the work.
-__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.f + __expf(-x)); }
+// The denominator is at least 1, so the reciprocal needs no range handling; far out on the negative side the
+// result is flushed to zero where the exact value is below 1e-36.
+__device__ __forceinline__ float silu_fast(float x) { return x * rcp_ftz(1.f + ex2_ftz(x * -1.4426950408889634f)); }
 // theta - round(theta / 2pi) * 2pi (src/modules/misc/rope.rs:23-27)
 __device__ __forceinline__ float wrap_angle(float t) {
     const float two_pi = 6.28318530717958647692f;

@@ -36,23 +36,9 @@ constexpr int PFO = 4;        // the same for the output kernel, which has fewer
 __device__ __forceinline__ void unpair(uint64_t v, float& lo, float& hi) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-// 2^x and 1/x on the special-function unit, denormals flushed: one instruction each (the plain forms carry range
-// fix-ups around them, a few instructions per call, which this loop pays per token).
-__device__ __forceinline__ float ex2_ftz(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float rcp_ftz(float x) {
-    float y;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 constexpr float kLog2e = 1.4426950408889634f;
 // exp(x) for x <= 0 (a decay factor): underflows to zero where the exact value is below the normal range.
 __device__ __forceinline__ float exp_decay(float x) { return ex2_ftz(x * kLog2e); }
-// x / (1 + exp(-x)); the denominator is at least 1, so the reciprocal needs no range handling.
-__device__ __forceinline__ float silu_scan(float x) { return x * rcp_ftz(1.f + ex2_ftz(-x * kLog2e)); }
 
 struct Scratch {
     float* h_loc;   // [b, nseg, NS, i]  end state of every segment run from zero
@@ -301,7 +287,7 @@ __global__ void __launch_bounds__(CPB, 6) selscan1_output_kernel(bm_selscan1_arg
             unpair(acc0, s0, s1);
             unpair(acc1, s2, s3);
             float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
-            if (kGate) y *= silu_scan(to_f32(zraw));
+            if (kGate) y *= silu_fast(to_f32(zraw));
             if (active) *yp = from_f32<T>(y);
         };
         // whole blocks of PFO tokens: the loads of the next block are issued before the recurrence runs over this one
@@ -602,7 +588,7 @@ selscan1_output_tma_kernel(bm_selscan1_args a, Scratch ws, int nseg, const __gri
             unpair(acc0, s0, s1);
             unpair(acc1, s2, s3);
             float y = fmaf(dskip, u, (s0 + s1) + (s2 + s3));
-            if (kGate) y *= silu_scan(to_f32(zraw));
+            if (kGate) y *= silu_fast(to_f32(zraw));
             if (active) *yp = from_f32<bf16>(y);
         };
 #pragma unroll 1
