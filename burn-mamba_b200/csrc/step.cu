@@ -226,9 +226,11 @@ __device__ __forceinline__ float rot_elem(const float* row, const float* cs_sm, 
     return self;
 }
 
-__global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
+// kM: the MIMO rank when it is 1, 2 or 4 (the loops over m are then resolved at compile time), 0 for any other rank.
+template <int kM>
+__global__ void __launch_bounds__(256, 2) step3_kernel(bm_step3_args a) {
     extern __shared__ float sm[];
-    const int R = a.state_rank, P = a.headdim, M = a.mimo_rank, H = a.nheads;
+    const int R = a.state_rank, P = a.headdim, M = kM ? kM : a.mimo_rank, H = a.nheads;
     const int na_alloc = max(a.rope_dim / 2, 1), na = a.rope_dim / 2;
     float* ang = sm;                 // [na_alloc] new wrapped angle
     float* cosv = ang + na_alloc;    // [na_alloc]
@@ -236,9 +238,47 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
     float* bs = sm + ((3 * na_alloc + 3) & ~3);  // [M][R] rotated B (16-byte aligned for 128-bit reads)
     float* cs = bs + M * R;          // [M][R] rotated C
     float* bp = cs + M * R;          // [M][R] previous rotated B
+    float* braw = bp + M * R;        // [M][R] this step's B as given
+    float* craw = braw + M * R;      // [M][R] this step's C as given
     const int bh = blockIdx.x, b = bh / H, h = bh % H, tid = threadIdx.x;
-    const float dt = a.dt[bh];
+    const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const bool pairwise = M == 1;
+    float* st = a.state + (int64_t)bh * P * R;
+    const bool fast = R % 4 == 0 && R <= 128 && M <= 4;
+    constexpr int NB = 8;
+    const int r4 = lane * 4;
+    const bool act = r4 < R;
+    // (0) Everything the step reads from global memory is requested before anything waits on it: the first batch of
+    // state rows of this warp (with P <= 64 the only one) and its per-row scalars, the raw B / C rows, the previous B,
+    // the angle inputs.  The rotation below then works from shared memory, so the CTA pays one memory latency, not
+    // one per phase.
+    float4 hv[NB];
+    float xl = 0.f, xpl = 0.f, mxl[4] = {1.f, 1.f, 1.f, 1.f};
+    auto fetch_rows = [&](int p0) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+            hv[j] = (p0 + j < P && act) ? ld4(st + (int64_t)(p0 + j) * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        // per-row scalars: lane j of the warp fetches those of row p0 + j, later they are broadcast
+        const int prow = p0 + (lane & (NB - 1));
+        const bool plive = prow < P;
+        xl = plive ? a.x[(int64_t)bh * P + prow] : 0.f;
+        xpl = plive ? a.v_state[(int64_t)bh * P + prow] : 0.f;
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+            mxl[m] = (m < M && plive && a.mimo_x) ? a.mimo_x[((int64_t)h * M + m) * P + prow] : 1.f;
+    };
+    if (fast && warp * NB < P) fetch_rows(warp * NB);
+    const float dt = a.dt[bh];
+    const float alpha = a.alpha[bh], beta = a.beta[bh], gamma = a.gamma[bh];
+    // (row m, column r) loops run m outside and r over the threads: no division by the runtime R per element
+    for (int m = 0; m < M; ++m) {
+        const int64_t row = (((int64_t)b * M + m) * H + h) * R;
+        for (int r = tid; r < R; r += blockDim.x) {
+            braw[m * R + r] = a.b[row + r];
+            craw[m * R + r] = a.c[row + r];
+            bp[m * R + r] = a.k_state[row + r];
+        }
+    }
     // (1a) angle := wrap(angle + dt * range * pi * tanh(rot)) (src/mamba3/rotation/mod.rs:559-567, :744-747)
     for (int j = tid; j < na_alloc; j += blockDim.x) {
         float inc = dt * (tanhf(a.rot[(int64_t)b * na_alloc + j]) * (a.range * 3.14159265358979323846f));
@@ -247,29 +287,21 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
         sincosf(th, &sinv[j], &cosv[j]);
     }
     __syncthreads();
-    // (1b) rotate B and C, stage the previous B
-    for (int e = tid; e < M * R; e += blockDim.x) {
-        int m = e / R, r = e % R;
-        int64_t row = (((int64_t)b * M + m) * H + h) * R;
-        bs[e] = rot_elem(a.b + row, cosv, sinv, r, R, na * 2, pairwise);
-        cs[e] = rot_elem(a.c + row, cosv, sinv, r, R, na * 2, pairwise);
-        bp[e] = a.k_state[row + r];
-    }
+    // (1b) rotate B and C
+    for (int m = 0; m < M; ++m)
+        for (int r = tid; r < R; r += blockDim.x) {
+            bs[m * R + r] = rot_elem(braw + m * R, cosv, sinv, r, R, na * 2, pairwise);
+            cs[m * R + r] = rot_elem(craw + m * R, cosv, sinv, r, R, na * 2, pairwise);
+        }
     __syncthreads();
     // (2) state rows
-    const float alpha = a.alpha[bh], beta = a.beta[bh], gamma = a.gamma[bh];
-    const int lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    float* st = a.state + (int64_t)bh * P * R;
-    if (R % 4 == 0 && R <= 128 && M <= 4) {
+    if (fast) {
         // Fast path: a lane owns 4 consecutive state columns of every row (one 128-bit load / store per
         // row) and keeps its slice of the rotated B / C and of the previous B in registers.  The warp
         // works on NB rows at a time: all NB row loads are issued before the first is used, so that each
         // warp keeps NB x 512 bytes in flight, and the NB x 4 per-lane partial outputs are reduced with
         // one transposing butterfly (31 shuffles instead of 5 per value); lane 4 j + m then holds
         // y[row j][m].
-        constexpr int NB = 8;
-        const int r4 = lane * 4;
-        const bool act = r4 < R;
         float4 bq[4], cq[4], pq[4];
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
@@ -279,29 +311,24 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
             pq[m] = on ? ld4(bp + m * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         for (int p0 = warp * NB; p0 < P; p0 += NB * nwarps) {
-            float4 hv[NB];
-#pragma unroll
-            for (int j = 0; j < NB; ++j)
-                hv[j] = (p0 + j < P && act) ? ld4(st + (int64_t)(p0 + j) * R + r4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            // per-row scalars: lane j of the warp fetches those of row p0 + j, then they are broadcast
+            if (p0 != warp * NB) fetch_rows(p0);
             const int prow = p0 + (lane & (NB - 1));
             const bool plive = prow < P;
-            const float xl = plive ? a.x[(int64_t)bh * P + prow] : 0.f;
-            const float xpl = plive ? a.v_state[(int64_t)bh * P + prow] : 0.f;
-            float mxl[4];
+            // the row's input coefficients, formed once by the lane that fetched its scalars
+            float gl[4], btl[4];
 #pragma unroll
-            for (int m = 0; m < 4; ++m)
-                mxl[m] = (m < M && plive && a.mimo_x) ? a.mimo_x[((int64_t)h * M + m) * P + prow] : 1.f;
+            for (int m = 0; m < 4; ++m) {
+                gl[m] = gamma * xl * mxl[m];
+                btl[m] = beta * xpl * mxl[m];
+            }
             float v[NB * 4];
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
-                const float xr = __shfl_sync(0xffffffffu, xl, j), xp = __shfl_sync(0xffffffffu, xpl, j);
                 float4 h4 = make_float4(alpha * hv[j].x, alpha * hv[j].y, alpha * hv[j].z, alpha * hv[j].w);
 #pragma unroll
                 for (int m = 0; m < 4; ++m) {
-                    const float mx = __shfl_sync(0xffffffffu, mxl[m], j);
                     if (m < M) {
-                        const float g = gamma * xr * mx, bt = beta * xp * mx;
+                        const float g = __shfl_sync(0xffffffffu, gl[m], j), bt = __shfl_sync(0xffffffffu, btl[m], j);
                         h4.x = fmaf(g, bq[m].x, fmaf(bt, pq[m].x, h4.x));
                         h4.y = fmaf(g, bq[m].y, fmaf(bt, pq[m].y, h4.y));
                         h4.z = fmaf(g, bq[m].z, fmaf(bt, pq[m].z, h4.z));
@@ -365,10 +392,8 @@ __global__ void __launch_bounds__(256) step3_kernel(bm_step3_args a) {
     }
     // (3) cache roll: k_state := rotated B, angle := new angle (all reads of the old values are done:
     // bp / ang were staged before the barrier above)
-    for (int e = tid; e < M * R; e += blockDim.x) {
-        int m = e / R, r = e % R;
-        a.k_state[(((int64_t)b * M + m) * H + h) * R + r] = bs[e];
-    }
+    for (int m = 0; m < M; ++m)
+        for (int r = tid; r < R; r += blockDim.x) a.k_state[(((int64_t)b * M + m) * H + h) * R + r] = bs[m * R + r];
     for (int j = tid; j < na_alloc; j += blockDim.x) a.angle[(int64_t)bh * na_alloc + j] = ang[j];
 }
 
@@ -465,9 +490,15 @@ extern "C" int32_t bm_step3(const bm_step3_args* a, void* stream) {
     BM_REQUIRE_PTR(a->gamma);
     BM_REQUIRE_PTR(a->y);
     BM_OPTIONAL_PTR(a->mimo_x);
-    size_t smem = (((3 * (size_t)(a->rope_dim / 2 > 1 ? a->rope_dim / 2 : 1) + 3) & ~(size_t)3) + 3 * (size_t)a->mimo_rank * a->state_rank) * sizeof(float);
+    size_t smem = (((3 * (size_t)(a->rope_dim / 2 > 1 ? a->rope_dim / 2 : 1) + 3) & ~(size_t)3) + 5 * (size_t)a->mimo_rank * a->state_rank) * sizeof(float);
     BM_REQUIRE(smem <= 48 * 1024, BM_ERR_UNSUPPORTED, "mimo_rank * state_rank too large for the step kernel");
     int64_t bh = (int64_t)a->batch * a->nheads;
-    step3_kernel<<<(unsigned)bh, 256, smem, static_cast<cudaStream_t>(stream)>>>(*a);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (a->mimo_rank) {
+        case 1: step3_kernel<1><<<(unsigned)bh, 256, smem, st>>>(*a); break;
+        case 2: step3_kernel<2><<<(unsigned)bh, 256, smem, st>>>(*a); break;
+        case 4: step3_kernel<4><<<(unsigned)bh, 256, smem, st>>>(*a); break;
+        default: step3_kernel<0><<<(unsigned)bh, 256, smem, st>>>(*a); break;
+    }
     return check_launch("step3");
 }
