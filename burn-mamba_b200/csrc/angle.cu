@@ -112,34 +112,60 @@ __global__ void __launch_bounds__(kStThreads) angle_chunk_staged_kernel(bm_angle
     extern __shared__ float ash[];
     const int A = a.nangles, H = a.nheads, S = a.seqlen;
     const int Hp = (H + 3) & ~3;                        // dt rows padded to 16 bytes
+    const int Ap = (A + 3) & ~3;                        // so that the dt block starts 16-byte aligned
     float* vs = ash;                                    // [kChunk][A]  range * pi * tanh(rot)
-    float* ds = ash + kChunk * A;                       // [kChunk][Hp] dt
+    float* ds = ash + kChunk * Ap;                      // [kChunk][Hp] dt
     const int c = blockIdx.x % nchunks, b = blockIdx.x / nchunks;
     const int t0 = c * kChunk, nt = min(kChunk, S - t0);
     const float scale = a.range * 3.14159265358979323846f;
     const float* rot = a.rot + ((int64_t)b * S + t0) * A;
     const float* dt = a.dt + ((int64_t)b * S + t0) * H;
     for (int e = threadIdx.x; e < nt * A; e += kStThreads) vs[e] = tanhf(rot[e]) * scale;
-    for (int e = threadIdx.x; e < nt * H; e += kStThreads) ds[(e / H) * Hp + e % H] = dt[e];
+    // dt rows: a warp per token row, so the padded layout needs no division per element
+    for (int t = threadIdx.x >> 5; t < nt; t += kStThreads / 32)
+        for (int h = threadIdx.x & 31; h < Hp; h += 32) ds[t * Hp + h] = h < H ? dt[t * H + h] : 0.f;
     __syncthreads();
     const int j = threadIdx.x % A, ngrp = kStThreads / A;
     if ((int)threadIdx.x >= ngrp * A) return;
     const int64_t carry_row = (int64_t)chunk_last_row(c, S) * H * A;
+    const uint32_t Au = (uint32_t)A, row_stride = (uint32_t)H * Au;
     for (int hb = threadIdx.x / A; hb < nhb; hb += ngrp) {
         const int h0 = hb * kHB;
         float* th = a.theta + (int64_t)b * S * H * A + (int64_t)h0 * A + j;
         float run[kHB];
 #pragma unroll
         for (int k = 0; k < kHB; ++k) run[k] = (kWrite && h0 + k < H) ? th[carry_row + (int64_t)k * A] : 0.f;
-        for (int t = 0; t < nt; ++t) {
-            const float v = vs[t * A + j];
-            float* tr = th + (int64_t)(t0 + t) * H * A;
+        float* tr = th + (int64_t)t0 * H * A;           // row of the token being written, advanced by one row per token
+        const float* vp = vs + j;
+        const float* dp = ds + h0;                      // h0 is a multiple of kHB = 8 and Hp of 4: 16-byte aligned
+        if (h0 + kHB <= H) {
+            // whole block of heads: two 128-bit broadcast reads of dt per token, no guards, stores at fixed offsets
+#pragma unroll 4
+            for (int t = 0; t < nt; ++t) {
+                const float v = vp[t * A];
+                const float4 d0 = *reinterpret_cast<const float4*>(dp + t * Hp);
+                const float4 d1 = *reinterpret_cast<const float4*>(dp + t * Hp + 4);
+                run[0] = fmaf(d0.x, v, run[0]), run[1] = fmaf(d0.y, v, run[1]);
+                run[2] = fmaf(d0.z, v, run[2]), run[3] = fmaf(d0.w, v, run[3]);
+                run[4] = fmaf(d1.x, v, run[4]), run[5] = fmaf(d1.y, v, run[5]);
+                run[6] = fmaf(d1.z, v, run[6]), run[7] = fmaf(d1.w, v, run[7]);
+                if (kWrite) {
 #pragma unroll
-            for (int k = 0; k < kHB; ++k) {
-                if (h0 + k < H) {
-                    run[k] = fmaf(ds[t * Hp + h0 + k], v, run[k]);
-                    if (kWrite) tr[(int64_t)k * A] = run[k];
+                    for (int k = 0; k < kHB; ++k) tr[k * Au] = run[k];
+                    tr += row_stride;
                 }
+            }
+        } else {
+            for (int t = 0; t < nt; ++t) {
+                const float v = vp[t * A];
+#pragma unroll
+                for (int k = 0; k < kHB; ++k) {
+                    if (h0 + k < H) {
+                        run[k] = fmaf(dp[t * Hp + k], v, run[k]);
+                        if (kWrite) tr[k * Au] = run[k];
+                    }
+                }
+                tr += row_stride;
             }
         }
         if (!kWrite) {
@@ -167,7 +193,7 @@ extern "C" int32_t bm_angle_cumsum(const bm_angle_cumsum_args* a, void* stream) 
     const int nhb = (a->nheads + kHB - 1) / kHB;
     const int64_t per_chunk = (int64_t)a->batch * nchunks * nhb * a->nangles;
     const int64_t per_lane = (int64_t)a->batch * a->nheads * a->nangles;
-    const size_t smem = (size_t)kChunk * (a->nangles + ((a->nheads + 3) & ~3)) * sizeof(float);
+    const size_t smem = (size_t)kChunk * (((a->nangles + 3) & ~3) + ((a->nheads + 3) & ~3)) * sizeof(float);
     const bool staged = a->nangles <= kStThreads && smem <= 48 * 1024 && (int64_t)a->batch * nchunks <= INT32_MAX;
     const unsigned sgrid = (unsigned)((int64_t)a->batch * nchunks);
     if (staged) angle_chunk_staged_kernel<false><<<sgrid, kStThreads, smem, st>>>(*a, nchunks, nhb);
