@@ -272,7 +272,38 @@ __global__ void conv_window_kernel(bm_conv1d_silu_args a) {
 constexpr int NT = 128;            // threads per row
 constexpr int MAXV = 8;            // vectors of 8 per thread: rows up to 8192 wide
 
+// Eight consecutive elements as they come from memory (16 bytes of bf16, 32 of float32): what a thread holds of a
+// row whose loads are all issued before the first is used.
 template <typename T>
+struct Raw8;
+template <>
+struct Raw8<__nv_bfloat16> {
+    uint4 w;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { w = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void unpack(float (&v)[VEC]) const {
+        const uint32_t q[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q[j]));
+            v[2 * j] = f.x, v[2 * j + 1] = f.y;
+        }
+    }
+};
+template <>
+struct Raw8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    }
+    __device__ __forceinline__ void unpack(float (&v)[VEC]) const {
+        v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    }
+};
+
+// NV = vectors of 8 per thread the row needs (ceil(width / (8 NT))), so that nothing is held for columns the row
+// does not have.  Every load of the row (x, the gate, the weight) is issued before the first value is used: the CTA
+// waits on memory once, not once per vector and again after the reduction.
+template <typename T, int NV>
 __global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args a) {
     __shared__ float red[NT / 32];
     const int64_t row = blockIdx.x;
@@ -281,22 +312,29 @@ __global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args
     const T* zr = a.z ? static_cast<const T*>(a.z) + row * a.z_stride : nullptr;
     const T* gr = static_cast<const T*>(a.gamma);
     T* orow = static_cast<T*>(a.out) + row * (int64_t)D;
-    const bool gate_first = zr != nullptr && !a.norm_before_gate;
-    Vec8<T> xv[MAXV];
+    const bool gate = zr != nullptr, gate_first = gate && !a.norm_before_gate;
+    Raw8<T> xraw[NV], zraw[NV], graw[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = min((i * NT + (int)threadIdx.x) * VEC, D - VEC);   // the last vector is fetched again where the row ends
+        xraw[i].load(xr + c);
+        if (gate) zraw[i].load(zr + c);
+        graw[i].load(gr + c);
+    }
+    float xv[NV][VEC];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-        const int c = (i * NT + threadIdx.x) * VEC;
-        if (c < D) {
-            xv[i].load(xr + c);
+    for (int i = 0; i < NV; ++i) {
+        xraw[i].unpack(xv[i]);
+        if ((i * NT + (int)threadIdx.x) * VEC < D) {
             if (gate_first) {
-                Vec8<T> zv;
-                zv.load(zr + c);
+                float zv[VEC];
+                zraw[i].unpack(zv);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) xv[i].v[j] *= silu_fast(zv.v[j]);
+                for (int j = 0; j < VEC; ++j) xv[i][j] *= silu_fast(zv[j]);
             }
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) ss = fmaf(xv[i].v[j], xv[i].v[j], ss);
+            for (int j = 0; j < VEC; ++j) ss = fmaf(xv[i][j], xv[i][j], ss);
         }
     }
 #pragma unroll
@@ -308,21 +346,37 @@ __global__ void __launch_bounds__(NT) rmsnorm_gated_kernel(bm_rmsnorm_gated_args
     for (int i = 0; i < NT / 32; ++i) tot += red[i];
     const float inv = rsqrtf(tot / (float)D + a.eps);
 #pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int c = (i * NT + threadIdx.x) * VEC;
         if (c < D) {
-            Vec8<T> gv, ov;
-            gv.load(gr + c);
+            float gv[VEC];
+            graw[i].unpack(gv);
+            Vec8<T> ov;
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) ov.v[j] = xv[i].v[j] * inv * gv.v[j];
-            if (zr != nullptr && a.norm_before_gate) {
-                Vec8<T> zv;
-                zv.load(zr + c);
+            for (int j = 0; j < VEC; ++j) ov.v[j] = xv[i][j] * inv * gv[j];
+            if (gate && !gate_first) {
+                float zv[VEC];
+                zraw[i].unpack(zv);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) ov.v[j] *= silu_fast(zv.v[j]);
+                for (int j = 0; j < VEC; ++j) ov.v[j] *= silu_fast(zv[j]);
             }
             ov.store(orow + c);
         }
+    }
+}
+
+template <typename T>
+void launch_rmsnorm(const bm_rmsnorm_gated_args& a, cudaStream_t st) {
+    const unsigned rows = (unsigned)a.rows;
+    switch ((a.width + NT * VEC - 1) / (NT * VEC)) {
+        case 1: rmsnorm_gated_kernel<T, 1><<<rows, NT, 0, st>>>(a); break;
+        case 2: rmsnorm_gated_kernel<T, 2><<<rows, NT, 0, st>>>(a); break;
+        case 3: rmsnorm_gated_kernel<T, 3><<<rows, NT, 0, st>>>(a); break;
+        case 4: rmsnorm_gated_kernel<T, 4><<<rows, NT, 0, st>>>(a); break;
+        case 5: rmsnorm_gated_kernel<T, 5><<<rows, NT, 0, st>>>(a); break;
+        case 6: rmsnorm_gated_kernel<T, 6><<<rows, NT, 0, st>>>(a); break;
+        case 7: rmsnorm_gated_kernel<T, 7><<<rows, NT, 0, st>>>(a); break;
+        default: rmsnorm_gated_kernel<T, 8><<<rows, NT, 0, st>>>(a); break;
     }
 }
 
@@ -532,8 +586,8 @@ extern "C" int32_t bm_rmsnorm_gated(const bm_rmsnorm_gated_args* a, void* stream
     BM_REQUIRE_PTR(a->out);
     BM_OPTIONAL_PTR(a->z);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (a->dtype == BM_DTYPE_F32) rmsnorm_gated_kernel<float><<<(unsigned)a->rows, NT, 0, st>>>(*a);
-    else rmsnorm_gated_kernel<__nv_bfloat16><<<(unsigned)a->rows, NT, 0, st>>>(*a);
+    if (a->dtype == BM_DTYPE_F32) launch_rmsnorm<float>(*a, st);
+    else launch_rmsnorm<__nv_bfloat16>(*a, st);
     return check_launch("rmsnorm_gated");
 }
 
