@@ -388,29 +388,26 @@ void launch_rmsnorm(const bm_rmsnorm_gated_args& a, cudaStream_t st) {
 //  src/mamba3/rotation/mod.rs:653-679 + src/modules/misc/rope.rs:50-170: rotation of the leading rope_dim entries
 //  by the cumulative angles, pairs (2j, 2j+1) when `pairwise`, else (j, j + r/2)).
 // One CTA per token.  The raw rows [m, g, r] of B and C (a few KB) are normalised once into shared memory; then
-// one thread per (head, group of 8 pairs) forms cos / sin of its angles once and writes its 16 entries of every
-// rank of both tensors: 16-byte stores, consecutive threads on consecutive chunks.
+// one thread per (head, group of 4 pairs) forms cos / sin of its angles once and writes its 8 entries of every
+// rank of both tensors, consecutive threads on consecutive chunks.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__device__ __forceinline__ void store8(T* dst, const float (&v)[8]);
+__device__ __forceinline__ void store4(T* dst, const float (&v)[4]);
 template <>
-__device__ __forceinline__ void store8<float>(float* dst, const float (&v)[8]) {
-    reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
-    reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+__device__ __forceinline__ void store4<float>(float* dst, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
 }
 template <>
-__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[8]) {
-    __nv_bfloat162 p[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) p[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(p);
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[4]) {
+    __nv_bfloat162 p[2] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3])};
+    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<uint2*>(p);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256, 4) mamba3_bc_prep_kernel(bm_mamba3_bc_prep_args a) {
     extern __shared__ float nrm[];   // [2][m * g][r]: normalised B rows, then C rows
     const int M = a.mimo_rank, G = a.ngroups, H = a.nheads, Rk = a.state_rank;
-    const int rows = M * G, half = Rk / 2, na = a.rope_dim / 2, ngrp = half / 8;
+    const int rows = M * G, half = Rk / 2, na = a.rope_dim / 2, ngrp = half / 4;
     const int64_t tok = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     // ---- RMS norm of the 2 m g raw rows, one warp per row
@@ -431,56 +428,49 @@ __global__ void __launch_bounds__(256, 4) mamba3_bc_prep_kernel(bm_mamba3_bc_pre
         for (int e = lane; e < Rk; e += 32) nrm[(int64_t)rw * Rk + e] *= inv * gam[e];
     }
     __syncthreads();
-    // ---- heads: bias, rotation, store
+    // ---- heads: bias, rotation, store.  A thread takes 4 pairs of one head: one 16-byte read per half of the normalised
+    // row and of the bias, so that the 16 threads of a head read 256 contiguous bytes with each instruction (at 8 pairs
+    // per thread every 16-byte read skipped the next 16 bytes and a warp's read spread over twice the lines).
     const int hpg = H / G;
     for (int idx = threadIdx.x; idx < H * ngrp; idx += blockDim.x) {
-        const int h = idx / ngrp, j0 = (idx % ngrp) * 8, g = h / hpg;
-        float cs[8], sn[8], th[8];
-        if (a.angles != nullptr && j0 + 8 <= na && (na & 3) == 0) {
-            const float4* ap = reinterpret_cast<const float4*>(a.angles + (tok * H + h) * na + j0);
-            const float4 t0 = ap[0], t1 = ap[1];
-            th[0] = t0.x, th[1] = t0.y, th[2] = t0.z, th[3] = t0.w, th[4] = t1.x, th[5] = t1.y, th[6] = t1.z, th[7] = t1.w;
+        const int h = idx / ngrp, j0 = (idx % ngrp) * 4, g = h / hpg;
+        float cs[4], sn[4], th[4];
+        if (a.angles != nullptr && j0 + 4 <= na && (na & 3) == 0) {
+            const float4 t0 = *reinterpret_cast<const float4*>(a.angles + (tok * H + h) * na + j0);
+            th[0] = t0.x, th[1] = t0.y, th[2] = t0.z, th[3] = t0.w;
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) th[j] = (a.angles != nullptr && j0 + j < na) ? a.angles[(tok * H + h) * na + j0 + j] : 0.f;
+            for (int j = 0; j < 4; ++j) th[j] = (a.angles != nullptr && j0 + j < na) ? a.angles[(tok * H + h) * na + j0 + j] : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) __sincosf(wrap_angle(th[j]), &sn[j], &cs[j]);
-        const int o_lo = a.pairwise ? 2 * j0 : j0, o_hi = a.pairwise ? 2 * j0 + 8 : j0 + half;
+        for (int j = 0; j < 4; ++j) __sincosf(wrap_angle(th[j]), &sn[j], &cs[j]);
+        const int o_lo = a.pairwise ? 2 * j0 : j0, o_hi = a.pairwise ? 2 * j0 + 4 : j0 + half;
         for (int m = 0; m < M; ++m) {
 #pragma unroll
             for (int isc = 0; isc < 2; ++isc) {
                 const float* nr = nrm + ((int64_t)isc * rows + m * G + g) * Rk;
                 const float* bias = (isc ? a.c_bias : a.b_bias) + ((int64_t)h * M + m) * Rk;
-                float lo[8], hi[8];
-#pragma unroll
-                for (int q4 = 0; q4 < 2; ++q4) {   // 16-byte loads: shared memory and the (cache-resident) bias
-                    const float4 nl = reinterpret_cast<const float4*>(nr + o_lo)[q4], nh = reinterpret_cast<const float4*>(nr + o_hi)[q4];
-                    const float4 bl = __ldg(reinterpret_cast<const float4*>(bias + o_lo) + q4);
-                    const float4 bh = __ldg(reinterpret_cast<const float4*>(bias + o_hi) + q4);
-                    lo[4 * q4] = nl.x + bl.x, lo[4 * q4 + 1] = nl.y + bl.y, lo[4 * q4 + 2] = nl.z + bl.z, lo[4 * q4 + 3] = nl.w + bl.w;
-                    hi[4 * q4] = nh.x + bh.x, hi[4 * q4 + 1] = nh.y + bh.y, hi[4 * q4 + 2] = nh.z + bh.z, hi[4 * q4 + 3] = nh.w + bh.w;
-                }
-                float olo[8], ohi[8];
-                if (a.pairwise) {   // lo, hi hold 16 consecutive entries: pair j = entries (2j, 2j + 1)
-                    float* both[2] = {lo, hi};
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float x0 = both[j >> 2][2 * (j & 3)], x1 = both[j >> 2][2 * (j & 3) + 1];
-                        float* out = j < 4 ? olo : ohi;
-                        out[2 * (j & 3)] = cs[j] * x0 - sn[j] * x1;
-                        out[2 * (j & 3) + 1] = sn[j] * x0 + cs[j] * x1;
-                    }
+                const float4 nl = *reinterpret_cast<const float4*>(nr + o_lo), nh = *reinterpret_cast<const float4*>(nr + o_hi);
+                const float4 bl = __ldg(reinterpret_cast<const float4*>(bias + o_lo));
+                const float4 bh = __ldg(reinterpret_cast<const float4*>(bias + o_hi));
+                const float lo[4] = {nl.x + bl.x, nl.y + bl.y, nl.z + bl.z, nl.w + bl.w};
+                const float hi[4] = {nh.x + bh.x, nh.y + bh.y, nh.z + bh.z, nh.w + bh.w};
+                float olo[4], ohi[4];
+                if (a.pairwise) {   // lo, hi hold 8 consecutive entries: pair j = entries (2j, 2j + 1)
+                    olo[0] = cs[0] * lo[0] - sn[0] * lo[1], olo[1] = sn[0] * lo[0] + cs[0] * lo[1];
+                    olo[2] = cs[1] * lo[2] - sn[1] * lo[3], olo[3] = sn[1] * lo[2] + cs[1] * lo[3];
+                    ohi[0] = cs[2] * hi[0] - sn[2] * hi[1], ohi[1] = sn[2] * hi[0] + cs[2] * hi[1];
+                    ohi[2] = cs[3] * hi[2] - sn[3] * hi[3], ohi[3] = sn[3] * hi[2] + cs[3] * hi[3];
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < 4; ++j) {
                         olo[j] = cs[j] * lo[j] - sn[j] * hi[j];
                         ohi[j] = sn[j] * lo[j] + cs[j] * hi[j];
                     }
                 }
                 T* dst = static_cast<T*>(isc ? a.c_out : a.b_out) + ((tok * M + m) * H + h) * Rk;
-                store8<T>(dst + o_lo, olo);
-                store8<T>(dst + o_hi, ohi);
+                store4<T>(dst + o_lo, olo);
+                store4<T>(dst + o_hi, ohi);
             }
         }
     }
