@@ -173,6 +173,8 @@ __global__ void __launch_bounds__(kCtThreads, 4) conv1d_silu_tma_kernel(bm_conv1
     issue(0);
     issue(1);
     const int cg = tid & 15, tg = tid >> 4;   // 8-channel vector inside the tile, group of 8 tokens
+    float w[K][VEC], bias[VEC];
+    int ct_loaded = -1;
     for (int k = 0;; ++k) {
         const int tile = blockIdx.x + k * gridDim.x;
         if (tile >= ntiles) break;
@@ -182,12 +184,17 @@ __global__ void __launch_bounds__(kCtThreads, 4) conv1d_silu_tma_kernel(bm_conv1
         const int c0 = ct * kCtCh + cg * VEC, t0 = tt * kCtTok;
         const bool live = c0 < V;
         const int cc = live ? c0 : 0;
-        float w[K][VEC], bias[VEC];
+        // taps and bias of this thread's 8 channels: fetched when the channel tile changes.  The host sizes the grid as a
+        // multiple of the channel tiles per row where it can, so that a CTA keeps one channel tile for all its tiles
+        // (fetched per tile, these scalar reads at a 128-byte stride between threads were 7/8 of the kernel's L1 traffic).
+        if (ct != ct_loaded) {
+            ct_loaded = ct;
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-            bias[j] = a.bias ? a.bias[cc + j] : 0.f;
+            for (int j = 0; j < VEC; ++j) {
+                bias[j] = a.bias ? a.bias[cc + j] : 0.f;
 #pragma unroll
-            for (int kk = 0; kk < K; ++kk) w[kk][j] = a.weight[(int64_t)(cc + j) * K + kk];
+                for (int kk = 0; kk < K; ++kk) w[kk][j] = a.weight[(int64_t)(cc + j) * K + kk];
+            }
         }
         T* dst;
         int64_t dstride;
@@ -518,7 +525,8 @@ extern "C" int32_t bm_conv1d_silu_fwd(const bm_conv1d_silu_args* a, void* stream
                     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
                     if (sms <= 0) sms = 148;
                 }
-                const int grid2 = (int)std::min<int64_t>(ntiles, 4 * (int64_t)sms);
+                int grid2 = (int)std::min<int64_t>(ntiles, 4 * (int64_t)sms);
+                if (grid2 > n_ctile) grid2 -= grid2 % n_ctile;   // a CTA then keeps one channel tile (tile index = CTA + k * grid)
                 const size_t smem = (size_t)kCtStages * kCtStageBytes + kCtStages * sizeof(uint64_t);
                 cudaError_t e = cudaSuccess;
                 switch (a->kernel) {
