@@ -16,6 +16,8 @@
 // as float32 and read as warp-wide broadcasts.  When a channel's decay row is the S4D-real ramp
 // A[n] = (n + 1) A[0] (the reference's initialisation, src/mamba1/mamba1.rs:184-194), exp(delta A[n]) is
 // formed as powers of one exponential instead of one exponential per state.
+// Two sets of kernels: the first fetches u / delta / z through registers (float32, any width); the second, for bf16
+// with d_inner a multiple of 8, has the token rows staged by TMA and walks the summary pass backwards (further down).
 #include "common.cuh"
 #include "tc_common.cuh"
 #include <type_traits>
