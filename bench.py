@@ -14,7 +14,9 @@ every rank generates and runs only its own units (whole batch rows for N = 2, 4,
 data-path collective, and `value` = 32 768 tokens / max-over-ranks time ("scaling": "strong").  The
 same line also carries `replicated` (every rank runs the whole problem: the weak-scaling figure) and
 `head_split` (N/2 batch rows, each row's heads on two ranks, y all-gathered along heads over NCCL and
-compared bit for bit with the one-GPU result).
+compared bit for bit with the one-GPU result) and `sequence_parallel` (one long sequence cut along time over the
+ranks: zero-state pass, all-gather of the slice maps, second pass from the folded entering state; compared with the
+one-GPU run of the whole sequence).
 
 The timed region is repeated `--regions` times (each region: barrier, K back-to-back launches between
 two CUDA events, barrier; per region the maximum over ranks); ms_per_step is the median region, min and
@@ -436,6 +438,7 @@ def run_ours(args):
     if world > 1 and not args.profile:
         line["replicated"] = replicated_leg(torch, dist, bm, dev, c, params, timed, world)
         line["head_split"] = head_split_leg(torch, dist, bm, dev, c, params, timed, rank, world)
+        line["sequence_parallel"] = sequence_parallel_leg(torch, dist, bm, dev, c, rank, world)
     if rank == 0:
         extra = not args.profile and world == 1
         line["cpu_baseline"] = None if args.profile else cpu_baseline(budget_s=20.0, one_thread=True)
@@ -474,6 +477,54 @@ def replicated_leg(torch, dist, bm, dev, c, params, timed, world):
     ms = statistics.median(timed(fn, 20, regions=5)) / 20
     return {"value": c["batch"] * c["seqlen"] * world / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "scaling": "weak",
             "note": "every rank runs the whole problem; aggregate over ranks"}
+
+
+def sequence_parallel_leg(torch, dist, bm, dev, c, rank, world, seqlen=131072, batch=2, iters=5):
+    """One sequence of `batch` x `seqlen` tokens (the configuration's heads) cut along time into `world` slices
+    (shard.ssd2_fwd_sequence_parallel): every rank runs its slice from zero, the slice end states and decays are
+    all-gathered over NCCL, every rank but the first runs its slice again from its folded entering state.  Timed as
+    the maximum over ranks; the result is compared with this rank's own one-GPU run of the whole sequence."""
+    H, P, R, G, Q = c["nheads"], c["headdim"], c["state_rank"], c["ngroups"], c["chunk_len"]
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(batch, seqlen, H, P, generator=g, device=dev).bfloat16()
+    dt = torch.exp(torch.rand(batch, seqlen, H, generator=g, device=dev) * 4.6 - 6.9)
+    a = -torch.exp(torch.rand(H, generator=g, device=dev) * 2.0)
+    b = torch.randn(batch, seqlen, G, R, generator=g, device=dev).bfloat16()
+    cc = torch.randn(batch, seqlen, G, R, generator=g, device=dev).bfloat16()
+    d = torch.ones(H, device=dev)
+    fwd = lambda x_, dt_, a_, b_, c_, d_, h0_, q: bm.ops.ssd2_fwd(x_, dt_, a_, b_, c_, d_, h0_, chunk_len=q, path="auto")
+    s_loc = seqlen // world
+    cut = slice(rank * s_loc, (rank + 1) * s_loc)
+    xs, dts, bs, cs = (t[:, cut].contiguous() for t in (x, dt, b, cc))
+    run = lambda: bm.shard.ssd2_fwd_sequence_parallel(fwd, xs, dts, a, bs, cs, d, None, Q, rank, world)
+    for _ in range(3):
+        y, hf = run()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        y, hf = run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    for _ in range(2):
+        y1, h1 = fwd(x, dt, a, b, cc, d, None, Q)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        y1, h1 = fwd(x, dt, a, b, cc, d, None, Q)
+    e1.record()
+    torch.cuda.synchronize()
+    one = e0.elapsed_time(e1) / iters
+    equal = torch.tensor([int(torch.equal(y, y1[:, cut])) and int(torch.allclose(hf, h1, rtol=1e-5, atol=1e-6))], device=dev)
+    dist.all_reduce(equal, op=dist.ReduceOp.MIN)
+    return {"batch": batch, "seqlen": seqlen, "slices": world, "ms": ms.item(), "one_gpu_ms": one,
+            "value": batch * seqlen / (ms.item() * 1e-3), "unit": "tokens/s",
+            "y_equal_to_one_gpu_bitwise": bool(equal.item()),
+            "exchange_bytes_per_rank": batch * H * P * R * 4 + batch * H * 4,
+            "note": "two passes on every rank but the first; the exchange does not grow with the sequence"}
 
 
 def head_split_leg(torch, dist, bm, dev, c, params, timed, rank, world):

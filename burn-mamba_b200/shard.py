@@ -7,6 +7,13 @@ split only when there are more ranks than rows.  The one collective this path ca
 all-gather of y along the head axis when a row's heads live on several ranks (the gated norm that
 follows the SSD in the block reduces over all of d_inner, src/mamba2/mamba2.rs:776).  Ranks that own
 whole rows exchange nothing.  Decode steps are never sharded.
+
+A single long sequence can also be cut along time (`ssd2_fwd_sequence_parallel`): the recurrence over a slice is
+an affine map of the entering state, h_out = decay * h_in + h_from_zero with decay = exp(A * sum(dt)) per
+(row, head), so every rank first runs its slice from a zero state, the ranks all-gather those two small tensors,
+each folds the maps of the ranks before it into its true entering state and runs its slice a second time from
+that state.  Two passes on every rank but the first: the exchange is [b, h, p, r] float32 per rank, independent
+of the sequence length.
 """
 from dataclasses import dataclass
 
@@ -182,3 +189,54 @@ def ssd2_fwd_sharded(fwd, x, dt, a, b, c, d, h0, chunk_len, rank, world, gather=
     if not gather:
         return parts
     return gather_heads(parts, parts_of_all, rank, world, h)
+
+
+def entering_state(h_locs, decays, rank):
+    """State entering slice `rank` of a sequence cut along time.  h_locs[k] [b, h, p, r]: the state slice k reaches
+    from its own start (slice 0 from the sequence's initial state, the others from zero); decays[k] [b, h]:
+    exp(A * sum of dt over slice k).  Folds the affine maps of slices 0 .. rank - 1 in order; for rank 0 returns None
+    (the caller's own initial state applies).  rank = len(h_locs) gives the state after the whole sequence."""
+    if rank == 0:
+        return None
+    h = h_locs[0]
+    for k in range(1, rank):
+        h = h * decays[k][:, :, None, None] + h_locs[k]
+    return h
+
+
+def slice_decay(dt, a):
+    """exp(A[h] * sum_t dt[b, t, h]) of one slice, float32 [b, h]; dt must be the step sizes the scan uses (after any
+    softplus / clamp)."""
+    import torch
+    return torch.exp(a.float()[None, :] * dt.float().sum(dim=1))
+
+
+def ssd2_fwd_sequence_parallel(fwd, x, dt, a, b, c, d, h0, chunk_len, rank, world, group=None):
+    """One SSD problem whose sequence is cut into `world` consecutive slices, this rank holding slice `rank`
+    (x [b, s_loc, h, p], dt [b, s_loc, h] as used by the scan, B / C [b, s_loc, g, r]).  `fwd` is an
+    ssd2_fwd-compatible callable; h0 is the initial state of the whole sequence (read by rank 0 only).
+    Returns (y of this slice, final state of the whole sequence).  One all-gather of the slice end states and decays;
+    every rank but the first runs its slice twice."""
+    import torch
+    import torch.distributed as dist
+
+    y, h_loc = fwd(x, dt, a, b, c, d, h0 if rank == 0 else None, chunk_len)
+    dec = slice_decay(dt, a)
+    if world == 1:
+        return y, h_loc
+    h_loc = h_loc.float().contiguous()
+    h_all = h_loc.new_empty((world,) + tuple(h_loc.shape))
+    d_all = dec.new_empty((world,) + tuple(dec.shape))
+    try:
+        dist.all_gather_into_tensor(h_all, h_loc, group=group)
+        dist.all_gather_into_tensor(d_all, dec.contiguous(), group=group)
+    except (RuntimeError, NotImplementedError):   # back ends without the flat form
+        hl, dl = list(h_all.unbind(0)), list(d_all.unbind(0))
+        dist.all_gather(hl, h_loc, group=group)
+        dist.all_gather(dl, dec.contiguous(), group=group)
+        h_all, d_all = torch.stack(hl), torch.stack(dl)
+    h_locs, decays = list(h_all.unbind(0)), list(d_all.unbind(0))
+    h_in = entering_state(h_locs, decays, rank)
+    if rank > 0:
+        y, _ = fwd(x, dt, a, b, c, d, h_in, chunk_len)
+    return y, entering_state(h_locs, decays, world)

@@ -42,6 +42,29 @@ def test_ssd2_tensor_path_full_sequence_matches_serial_oracle_and_float64_recurr
     assert rel_l2(host(y)[:, -128:], true_y[:, -128:]) <= 2e-2
 
 
+def test_sequence_slices_from_folded_entering_states_equal_the_whole_sequence_bf16(bm):
+    """The time-cut form of the prefill on one GPU: four slices of 1024 tokens run from zero, their maps folded into
+    the entering states (shard.entering_state / slice_decay), each slice run again from its state; y and the final
+    state against the single call over all 4096 tokens (tensor path, P 64, N 128, Q 256)."""
+    cfg = inputs.ssd2_prefill(seed=17, batch=2, seqlen=4096, nheads=4, headdim=64, state_rank=128, ngroups=1, h0_std=0.2)
+    x, b, c = (dev(bf16_round(cfg[k]), BF) for k in ("x", "b", "c"))
+    dt, a, d, h0 = dev(cfg["dt"]), dev(cfg["a"]), dev(cfg["d"]), dev(cfg["h0"])
+    fwd = lambda *t: bm.ops.ssd2_fwd(*t, chunk_len=256, path="tensor", check_status=True)
+    y_full, h_full = fwd(x, dt, a, b, c, d, h0)
+    world, s_loc = 4, 1024
+    cut = [slice(k * s_loc, (k + 1) * s_loc) for k in range(world)]
+    sl = lambda t, k: t[:, cut[k]].contiguous()
+    first = [fwd(sl(x, k), sl(dt, k), a, sl(b, k), sl(c, k), d, h0 if k == 0 else None) for k in range(world)]
+    h_locs = [hf for _, hf in first]
+    decays = [bm.shard.slice_decay(sl(dt, k), a) for k in range(world)]
+    ys = [first[0][0]]
+    for k in range(1, world):
+        ys.append(fwd(sl(x, k), sl(dt, k), a, sl(b, k), sl(c, k), d, bm.shard.entering_state(h_locs, decays, k))[0])
+    y = torch.cat(ys, dim=1)
+    assert rel_l2(host(y), host(y_full)) <= 1e-3
+    assert rel_l2(host(bm.shard.entering_state(h_locs, decays, world)), host(h_full)) <= 1e-5
+
+
 def test_ssd2_tensor_path_more_heads_than_sms_at_full_length(bm):
     """160 heads x L 4096 (more units than SMs, 32 tiles each): a random subset of heads against the oracle."""
     H = 160

@@ -98,3 +98,54 @@ def test_calls_merge_whole_rows_into_one_library_call():
     assert parts[0].calls() == [(0, 1, 0, 40)] and parts[1].calls() == [(0, 1, 40, 80)]
     ur = shard.UnitRange(40, 280, 80)   # half a row, two whole rows, half a row
     assert ur.calls() == [(0, 1, 40, 80), (1, 3, 0, 80), (3, 4, 0, 40)]
+
+
+def _seq_worker(rank, world, port, cfg, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        shard = _shard()
+        t = {k: torch.from_numpy(v) for k, v in cfg.items()}
+        s_loc = t["x"].shape[1] // world
+        cut = slice(rank * s_loc, (rank + 1) * s_loc)
+        y, hf = shard.ssd2_fwd_sequence_parallel(_oracle_fwd, t["x"][:, cut].contiguous(), t["dt"][:, cut].contiguous(),
+                                                 t["a"], t["b"][:, cut].contiguous(), t["c"][:, cut].contiguous(),
+                                                 t["d"], t["h0"], 16, rank, world)
+        q.put((rank, y.numpy(), hf.numpy()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_cut_along_time_equals_the_whole_sequence(world):
+    """Slices of one sequence on `world` gloo ranks: zero-state pass, all-gather of the slice maps, fold, second
+    pass from the true entering state; y of every slice and the final state equal the single call."""
+    from oracle import inputs, mamba2
+    cfg = inputs.ssd2_prefill(seed=33, batch=2, seqlen=32 * world, nheads=4, headdim=8, state_rank=8, ngroups=2, h0_std=0.2)
+    cfg = {k: cfg[k] for k in ("x", "dt", "a", "b", "c", "d", "h0")}
+    want_y, want_h = mamba2.ssd_serial(cfg["x"], cfg["dt"], cfg["a"], cfg["b"], cfg["c"], cfg["d"], cfg["h0"], 16)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000) + world
+    procs = [ctx.Process(target=_seq_worker, args=(r, world, port, cfg, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted((q.get(timeout=120) for _ in range(world)), key=lambda r: r[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    y = np.concatenate([g[1] for g in got], axis=1)
+    assert np.max(np.abs(y - want_y)) < 1e-5
+    for _, _, hf in got:                      # every rank ends with the state after the whole sequence
+        assert np.max(np.abs(hf - want_h)) < 1e-5
+
+
+def test_entering_state_folds_the_slice_maps_in_order():
+    shard = _shard()
+    rng = np.random.default_rng(0)
+    h = [torch.from_numpy(rng.standard_normal((2, 3, 4, 5)).astype(np.float32)) for _ in range(3)]
+    dcy = [torch.from_numpy(rng.uniform(0.1, 1.0, (2, 3)).astype(np.float32)) for _ in range(3)]
+    assert shard.entering_state(h, dcy, 0) is None
+    assert torch.equal(shard.entering_state(h, dcy, 1), h[0])
+    want = (h[0] * dcy[1][:, :, None, None] + h[1]) * dcy[2][:, :, None, None] + h[2]
+    assert torch.allclose(shard.entering_state(h, dcy, 3), want)
