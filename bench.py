@@ -493,8 +493,8 @@ def sequence_parallel_leg(torch, dist, bm, dev, c, rank, world, seqlen=131072, b
     cc = torch.randn(batch, seqlen, G, R, generator=g, device=dev).bfloat16()
     d = torch.ones(H, device=dev)
     fwd = lambda x_, dt_, a_, b_, c_, d_, h0_, q: bm.ops.ssd2_fwd(x_, dt_, a_, b_, c_, d_, h0_, chunk_len=q, path="auto")
-    s_loc = seqlen // world
-    cut = slice(rank * s_loc, (rank + 1) * s_loc)
+    cuts = bm.shard.sequence_cuts(seqlen, world, Q)   # rank 0 runs once and takes a double slice
+    cut = slice(*cuts[rank])
     xs, dts, bs, cs = (t[:, cut].contiguous() for t in (x, dt, b, cc))
     run = lambda: bm.shard.ssd2_fwd_sequence_parallel(fwd, xs, dts, a, bs, cs, d, None, Q, rank, world)
     for _ in range(3):
@@ -520,7 +520,7 @@ def sequence_parallel_leg(torch, dist, bm, dev, c, rank, world, seqlen=131072, b
     one = e0.elapsed_time(e1) / iters
     equal = torch.tensor([int(torch.equal(y, y1[:, cut])) and int(torch.allclose(hf, h1, rtol=1e-5, atol=1e-6))], device=dev)
     dist.all_reduce(equal, op=dist.ReduceOp.MIN)
-    return {"batch": batch, "seqlen": seqlen, "slices": world, "ms": ms.item(), "one_gpu_ms": one,
+    return {"batch": batch, "seqlen": seqlen, "slices": [hi - lo for lo, hi in cuts], "ms": ms.item(), "one_gpu_ms": one,
             "value": batch * seqlen / (ms.item() * 1e-3), "unit": "tokens/s",
             "y_equal_to_one_gpu_bitwise": bool(equal.item()),
             "exchange_bytes_per_rank": batch * H * P * R * 4 + batch * H * 4,

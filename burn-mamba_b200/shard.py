@@ -12,8 +12,8 @@ A single long sequence can also be cut along time (`ssd2_fwd_sequence_parallel`)
 an affine map of the entering state, h_out = decay * h_in + h_from_zero with decay = exp(A * sum(dt)) per
 (row, head), so every rank first runs its slice from a zero state, the ranks all-gather those two small tensors,
 each folds the maps of the ranks before it into its true entering state and runs its slice a second time from
-that state.  Two passes on every rank but the first: the exchange is [b, h, p, r] float32 per rank, independent
-of the sequence length.
+that state.  Two passes on every rank but the first (which therefore takes a slice twice as long,
+`sequence_cuts`): the exchange is [b, h, p, r] float32 per rank, independent of the sequence length.
 """
 from dataclasses import dataclass
 
@@ -191,6 +191,19 @@ def ssd2_fwd_sharded(fwd, x, dt, a, b, c, d, h0, chunk_len, rank, world, gather=
     return gather_heads(parts, parts_of_all, rank, world, h)
 
 
+def sequence_cuts(seqlen, world, align):
+    """[(start, stop)] of the `world` time slices of one sequence.  Rank 0 runs its slice once, every other rank
+    twice, so rank 0 gets two shares and the others one each (all ranks then do 2 / (world + 1) of the sequence's
+    work); cut points are multiples of `align` (the chunk length, so that slices start on tile boundaries)."""
+    if seqlen <= 0 or world <= 0 or align <= 0:
+        raise ValueError("seqlen, world, align must be positive")
+    blocks = -(-seqlen // align)
+    cuts = [0] + [min(blocks, round((i + 1) * blocks / (world + 1))) for i in range(1, world)] + [blocks]
+    for i in range(1, len(cuts)):
+        cuts[i] = max(cuts[i], cuts[i - 1])
+    return [(min(cuts[i] * align, seqlen), min(cuts[i + 1] * align, seqlen)) for i in range(world)]
+
+
 def entering_state(h_locs, decays, rank):
     """State entering slice `rank` of a sequence cut along time.  h_locs[k] [b, h, p, r]: the state slice k reaches
     from its own start (slice 0 from the sequence's initial state, the others from zero); decays[k] [b, h]:
@@ -200,7 +213,7 @@ def entering_state(h_locs, decays, rank):
         return None
     h = h_locs[0]
     for k in range(1, rank):
-        h = h * decays[k][:, :, None, None] + h_locs[k]
+        h = h_locs[k] + h * decays[k][:, :, None, None]
     return h
 
 
@@ -235,8 +248,11 @@ def ssd2_fwd_sequence_parallel(fwd, x, dt, a, b, c, d, h0, chunk_len, rank, worl
         dist.all_gather(hl, h_loc, group=group)
         dist.all_gather(dl, dec.contiguous(), group=group)
         h_all, d_all = torch.stack(hl), torch.stack(dl)
-    h_locs, decays = list(h_all.unbind(0)), list(d_all.unbind(0))
-    h_in = entering_state(h_locs, decays, rank)
-    if rank > 0:
-        y, _ = fwd(x, dt, a, b, c, d, h_in, chunk_len)
-    return y, entering_state(h_locs, decays, world)
+    # one fold over the ranks gives this rank's entering state (after the maps of the ranks before it; the second pass
+    # is launched as soon as it is known) and the state after the whole sequence
+    h = h_all[0]
+    for k in range(1, world):
+        if k == rank:
+            y, _ = fwd(x, dt, a, b, c, d, h.contiguous(), chunk_len)
+        h = torch.addcmul(h_all[k], h, d_all[k][:, :, None, None])
+    return y, h

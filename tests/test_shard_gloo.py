@@ -106,8 +106,7 @@ def _seq_worker(rank, world, port, cfg, q):
     try:
         shard = _shard()
         t = {k: torch.from_numpy(v) for k, v in cfg.items()}
-        s_loc = t["x"].shape[1] // world
-        cut = slice(rank * s_loc, (rank + 1) * s_loc)
+        cut = slice(*shard.sequence_cuts(t["x"].shape[1], world, 16)[rank])
         y, hf = shard.ssd2_fwd_sequence_parallel(_oracle_fwd, t["x"][:, cut].contiguous(), t["dt"][:, cut].contiguous(),
                                                  t["a"], t["b"][:, cut].contiguous(), t["c"][:, cut].contiguous(),
                                                  t["d"], t["h0"], 16, rank, world)
@@ -149,3 +148,15 @@ def test_entering_state_folds_the_slice_maps_in_order():
     assert torch.equal(shard.entering_state(h, dcy, 1), h[0])
     want = (h[0] * dcy[1][:, :, None, None] + h[1]) * dcy[2][:, :, None, None] + h[2]
     assert torch.allclose(shard.entering_state(h, dcy, 3), want)
+
+
+@pytest.mark.parametrize("seqlen,world,align", [(4096, 2, 256), (131072, 8, 256), (1000, 3, 128), (256, 4, 256), (96, 3, 16)])
+def test_sequence_cuts_cover_the_sequence_on_aligned_points_with_a_double_first_slice(seqlen, world, align):
+    shard = _shard()
+    cuts = shard.sequence_cuts(seqlen, world, align)
+    assert len(cuts) == world and cuts[0][0] == 0 and cuts[-1][1] == seqlen
+    for (a0, a1), (b0, b1) in zip(cuts[:-1], cuts[1:]):
+        assert a1 == b0 and a0 <= a1 and a1 % align == 0
+    if seqlen >= 4 * world * align:
+        lens = [b - a for a, b in cuts]
+        assert abs(lens[0] - 2 * lens[1]) <= 2 * align and max(lens[1:]) - min(lens[1:]) <= align
